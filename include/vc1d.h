@@ -1,0 +1,181 @@
+/*
+ * vc1d.h -- C ABI of the B200 (sm_100a) depthwise causal conv1d library that backs
+ * Viby's Canon A/B/C/D layers.
+ *
+ * Every entry point takes plain pointers and sizes.  All data pointers are DEVICE
+ * pointers owned by the caller; outputs are allocated by the caller; the library
+ * allocates nothing and launches on the stream handle it is given (a cudaStream_t
+ * cast to void*, NULL = the legacy default stream).  The caller guarantees that the
+ * device owning the buffers is the current CUDA device of the calling thread.
+ *
+ * Return value of every launcher: 0 on success, a negative VC1D_E_* code for an
+ * invalid argument (nothing was launched), or a positive cudaError_t value when the
+ * CUDA runtime refused the launch.  vc1d_status_string() names either kind.
+ *
+ * Tap convention (reference: model/model.py:604-666 and
+ * causal-conv1d-mps/causal_conv1d_mps/causal_conv1d.metal:160-179):
+ *     y[b,d,t] = act( bias[d] + sum_{w<W} weight[d,w] * x[b,d,t-(W-1-w)] ),  x[t<0] = 0
+ * accumulated in fp32 and rounded once to the I/O dtype.
+ */
+#ifndef VC1D_H_
+#define VC1D_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VC1D_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define VC1D_API __attribute__((visibility("default")))
+#else
+#define VC1D_API
+#endif
+
+/* element types */
+enum {
+    VC1D_F32 = 0,
+    VC1D_BF16 = 1,
+    VC1D_F16 = 2,
+    /* mask-only element types */
+    VC1D_U8 = 8,  /* also torch.bool */
+    VC1D_I32 = 9,
+    VC1D_I64 = 10
+};
+
+/* activation */
+enum { VC1D_ACT_NONE = 0, VC1D_ACT_SILU = 1 };
+
+/* error codes (negative); positive return values are cudaError_t */
+enum {
+    VC1D_OK = 0,
+    VC1D_E_NULL = -1,        /* a required pointer is NULL */
+    VC1D_E_DTYPE = -2,       /* unsupported element type */
+    VC1D_E_WIDTH = -3,       /* width not in {2,3,4} */
+    VC1D_E_SHAPE = -4,       /* negative size, state_len < width-1, ... */
+    VC1D_E_STRIDE = -5,      /* stride combination the kernels cannot address */
+    VC1D_E_STRUCT = -6,      /* struct_size does not match this library */
+    VC1D_E_ACTIVATION = -7,  /* unknown activation code */
+    VC1D_E_ALIAS = -8,       /* in-place use that the kernel cannot honour */
+    VC1D_E_TOO_LARGE = -9    /* size beyond what an entry point supports */
+};
+
+/* kernel selection override (0 = let the library choose) -- used by benches and tests */
+enum {
+    VC1D_KERNEL_AUTO = 0,
+    VC1D_KERNEL_CHANNEL_LAST = 1, /* 128-bit accesses along channels, register sliding window */
+    VC1D_KERNEL_TIME_MAJOR = 2,   /* 128-bit accesses along time ([B,D,T] contiguous) */
+    VC1D_KERNEL_GENERIC = 3,      /* scalar, any strides */
+    VC1D_KERNEL_TMA = 4           /* channel-last, TMA-staged tiles with (W-1)-row halo */
+};
+
+/*
+ * Prefill: causal_conv1d_fn.
+ * Replaces the external CUDA kernel the reference calls at model/model.py:460-466
+ * (signature mirrored at causal-conv1d-mps/causal_conv1d_mps/autograd.py:501-510), and,
+ * with the optional pointers set, the surrounding elementwise passes:
+ *   mask       -> model/model.py:454-457 (x * mask before the conv),
+ *   residual   -> model/model.py:491 / causal_conv1d.metal:334-336 (y += residual),
+ *   final_state-> model/model.py:470-489 (right-aligned last state_len masked inputs),
+ *   initial_state -> model/model.py:607-617 (history prepended instead of zeros).
+ *
+ * x, y: logical [batch, dim, seqlen]; element strides given per tensor, so both the
+ * channel-last view the model passes (strides T*D, 1, D) and contiguous [B,D,T] work.
+ * Masking zeroes INPUT rows (mask value 0) before the conv; outputs at masked
+ * positions are still produced.  A non-zero mask value multiplies the input row and
+ * the product is rounded to the I/O dtype, as `x * mask` does in the reference.
+ */
+typedef struct vc1d_prefill_args {
+    uint32_t struct_size;   /* sizeof(vc1d_prefill_args) */
+    int32_t dtype;          /* x, y, residual, states: VC1D_F32 | VC1D_BF16 | VC1D_F16 */
+    int32_t wdtype;         /* weight and bias: same as dtype, or VC1D_F32 */
+    int32_t activation;     /* VC1D_ACT_* */
+    int32_t batch, dim, seqlen, width;
+    const void* x;
+    void* y;
+    const void* weight;     /* [dim, width] */
+    const void* bias;       /* [dim] or NULL */
+    int64_t x_stride_b, x_stride_d, x_stride_t;   /* in elements */
+    int64_t y_stride_b, y_stride_d, y_stride_t;
+    int64_t w_stride_d, w_stride_w;
+    /* optional fused pieces (NULL = absent) */
+    const void* mask;       /* [batch, seqlen] */
+    int32_t mask_dtype;     /* VC1D_U8 | VC1D_I32 | VC1D_I64 | VC1D_F32 | VC1D_BF16 | VC1D_F16 */
+    int32_t skip_masked_loads; /* 1: rows whose mask is 0 are not read, they count as +0 */
+    int64_t mask_stride_b, mask_stride_t;
+    const void* residual;   /* added to y after the activation; may equal x */
+    int64_t r_stride_b, r_stride_d, r_stride_t;
+    const void* initial_state; /* [batch, dim, init_len] contiguous, last width-1 columns are history */
+    int32_t init_len;
+    int32_t state_len;      /* columns of final_state */
+    void* final_state;      /* [batch, dim, state_len] contiguous */
+    /* tuning / selection: 0 = automatic */
+    int32_t kernel;         /* VC1D_KERNEL_* */
+    int32_t rows_per_thread;
+    int32_t block_threads;
+    int32_t unroll;         /* rows a thread loads before computing: 0 auto, 4 or 8 */
+} vc1d_prefill_args;
+
+VC1D_API int vc1d_prefill(const vc1d_prefill_args* args, void* stream);
+
+/*
+ * Decode: causal_conv1d_update.
+ * Replaces the external CUDA kernel the reference calls at model/model.py:305-311 and
+ * the PyTorch single step at model/model.py:372-398:
+ *     cat = [conv_state | x];  y = act(bias + cat[..., -W:] . weight);
+ *     conv_state <- cat[..., -state_len:]   (in place)
+ * With cache_seqlens != NULL the state is the circular buffer of
+ * causal_conv1d.metal:586-664 instead: write position = cache_seqlens[b] % state_len,
+ * history read modulo state_len, nothing shifts.
+ * residual != 0 adds x to y after the activation (causal_conv1d.metal:655-658).
+ */
+typedef struct vc1d_update_args {
+    uint32_t struct_size;
+    int32_t dtype;          /* x, y, conv_state */
+    int32_t wdtype;
+    int32_t activation;
+    int32_t batch, dim, width, state_len;
+    const void* x;          /* [batch, dim] */
+    void* y;                /* [batch, dim] */
+    void* conv_state;       /* [batch, dim, state_len], updated in place */
+    const void* weight;
+    const void* bias;
+    int64_t x_stride_b, x_stride_d;
+    int64_t y_stride_b, y_stride_d;
+    int64_t s_stride_b, s_stride_d, s_stride_l;
+    int64_t w_stride_d, w_stride_w;
+    const int32_t* cache_seqlens; /* [batch] or NULL */
+    int32_t residual;
+    int32_t kernel;         /* VC1D_KERNEL_AUTO | VC1D_KERNEL_GENERIC */
+    int32_t block_threads;
+    int32_t reserved;
+} vc1d_update_args;
+
+VC1D_API int vc1d_update(const vc1d_update_args* args, void* stream);
+
+/* ABI version of the loaded library (VC1D_ABI_VERSION it was built with). */
+VC1D_API int vc1d_abi_version(void);
+
+/* sizeof() of the two argument structs as the library was built -- lets a binding
+ * verify its own struct layout before the first launch. */
+VC1D_API uint32_t vc1d_sizeof_prefill_args(void);
+VC1D_API uint32_t vc1d_sizeof_update_args(void);
+
+/* Name of a return code: VC1D_E_* or a cudaError_t.  Never NULL; static storage. */
+VC1D_API const char* vc1d_status_string(int status);
+
+/* Number of kernel launches this process has made through the library (all threads).
+ * The reference swallows kernel exceptions and silently falls back
+ * (model/model.py:314-317, 492-495); callers use this to prove the kernels ran. */
+VC1D_API uint64_t vc1d_launch_count(void);
+
+/* Name of the kernel the most recent launcher call on this thread selected
+ * ("channel_last", "time_major", "generic", "tma", "update_vec", "update_generic"). */
+VC1D_API const char* vc1d_last_kernel(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VC1D_H_ */

@@ -1,0 +1,129 @@
+"""The C-ABI shared library: loads, exports every symbol include/vc1d.h declares, agrees on the
+struct layouts and rejects bad arguments before touching CUDA.  No compute; runs without a GPU."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+import torch
+
+from viby_model_b200 import _cabi
+
+ROOT = Path(__file__).resolve().parent.parent
+HEADER = (ROOT / "include" / "vc1d.h").read_text()
+
+
+def declared_symbols():
+    return re.findall(r"VC1D_API\s+[\w\s\*]+?\b(vc1d_\w+)\s*\(", HEADER)
+
+
+def test_header_symbols_are_exported_and_bound():
+    names = declared_symbols()
+    assert len(names) >= 8
+    raw = C.CDLL(str(_cabi.library_path()))
+    for n in names:
+        assert hasattr(raw, n), f"{n} declared in include/vc1d.h but not exported"
+        assert n in _cabi.EXPORTS, f"{n} has no ctypes binding"
+    assert set(_cabi.EXPORTS) == set(names)
+
+
+def test_abi_version_and_struct_sizes():
+    assert _cabi.lib.vc1d_abi_version() == int(re.search(r"#define VC1D_ABI_VERSION (\d+)", HEADER).group(1))
+    assert _cabi.lib.vc1d_sizeof_prefill_args() == C.sizeof(_cabi.PrefillArgs)
+    assert _cabi.lib.vc1d_sizeof_update_args() == C.sizeof(_cabi.UpdateArgs)
+
+
+def test_enum_values_match_header():
+    for name in ("VC1D_F32", "VC1D_BF16", "VC1D_F16", "VC1D_U8", "VC1D_I32", "VC1D_I64", "VC1D_E_NULL",
+                 "VC1D_E_DTYPE", "VC1D_E_WIDTH", "VC1D_E_SHAPE", "VC1D_E_STRIDE", "VC1D_E_STRUCT",
+                 "VC1D_E_ACTIVATION", "VC1D_E_ALIAS", "VC1D_E_TOO_LARGE"):
+        m = re.search(rf"\b{name}\s*=\s*(-?\d+)", HEADER)
+        assert m, name
+        assert getattr(_cabi, name) == int(m.group(1)), name
+
+
+def _prefill_args(**kw):
+    a = _cabi.PrefillArgs()
+    a.struct_size = C.sizeof(_cabi.PrefillArgs)
+    a.dtype = _cabi.VC1D_BF16
+    a.wdtype = _cabi.VC1D_BF16
+    a.batch, a.dim, a.seqlen, a.width = 1, 8, 8, 4
+    for k, v in kw.items():
+        setattr(a, k, v)
+    return a
+
+
+def _update_args(**kw):
+    a = _cabi.UpdateArgs()
+    a.struct_size = C.sizeof(_cabi.UpdateArgs)
+    a.dtype = _cabi.VC1D_BF16
+    a.wdtype = _cabi.VC1D_BF16
+    a.batch, a.dim, a.width, a.state_len = 1, 8, 4, 3
+    for k, v in kw.items():
+        setattr(a, k, v)
+    return a
+
+
+@pytest.mark.parametrize(
+    "kw,code",
+    [
+        (dict(struct_size=4), _cabi.VC1D_E_STRUCT),
+        (dict(dtype=7), _cabi.VC1D_E_DTYPE),
+        (dict(wdtype=_cabi.VC1D_F16), _cabi.VC1D_E_DTYPE),
+        (dict(activation=5), _cabi.VC1D_E_ACTIVATION),
+        (dict(width=5), _cabi.VC1D_E_WIDTH),
+        (dict(width=1), _cabi.VC1D_E_WIDTH),
+        (dict(batch=-1), _cabi.VC1D_E_SHAPE),
+        (dict(kernel=9), _cabi.VC1D_E_SHAPE),
+        (dict(), _cabi.VC1D_E_NULL),  # x, y, weight are NULL
+        (dict(x=4096, y=4096, weight=64, x_stride_b=64, x_stride_d=1, x_stride_t=8, y_stride_b=64, y_stride_d=1,
+              y_stride_t=8), _cabi.VC1D_E_ALIAS),
+    ],
+)
+def test_prefill_rejects_bad_arguments_without_launching(kw, code):
+    before = _cabi.launch_count()
+    assert _cabi.lib.vc1d_prefill(C.byref(_prefill_args(**kw)), None) == code
+    assert _cabi.launch_count() == before
+
+
+@pytest.mark.parametrize(
+    "kw,code",
+    [
+        (dict(struct_size=4), _cabi.VC1D_E_STRUCT),
+        (dict(dtype=3), _cabi.VC1D_E_DTYPE),
+        (dict(width=7), _cabi.VC1D_E_WIDTH),
+        (dict(state_len=2), _cabi.VC1D_E_SHAPE),  # shorter than width-1
+        (dict(kernel=_cabi.KERNEL_TMA), _cabi.VC1D_E_SHAPE),
+        (dict(), _cabi.VC1D_E_NULL),
+    ],
+)
+def test_update_rejects_bad_arguments_without_launching(kw, code):
+    before = _cabi.launch_count()
+    assert _cabi.lib.vc1d_update(C.byref(_update_args(**kw)), None) == code
+    assert _cabi.launch_count() == before
+
+
+def test_null_struct_and_empty_inputs():
+    assert _cabi.lib.vc1d_prefill(None, None) == _cabi.VC1D_E_NULL
+    assert _cabi.lib.vc1d_update(None, None) == _cabi.VC1D_E_NULL
+    # empty tensors are a successful no-op: nothing is dereferenced or launched
+    assert _cabi.lib.vc1d_prefill(C.byref(_prefill_args(seqlen=0)), None) == _cabi.VC1D_OK
+    assert _cabi.lib.vc1d_prefill(C.byref(_prefill_args(batch=0)), None) == _cabi.VC1D_OK
+    assert _cabi.lib.vc1d_update(C.byref(_update_args(batch=0)), None) == _cabi.VC1D_OK
+
+
+def test_status_strings():
+    assert _cabi.status_string(0) == "ok"
+    for code in range(-9, 0):
+        assert _cabi.status_string(code).startswith("VC1D_E_")
+    assert "unknown" in _cabi.status_string(-100)
+    with pytest.raises(ValueError, match="VC1D_E_WIDTH"):
+        _cabi.check(_cabi.VC1D_E_WIDTH, "x")
+    with pytest.raises(RuntimeError):
+        _cabi.check(1, "x")  # cudaErrorInvalidValue
+
+
+def test_missing_library_fails_loudly(tmp_path, monkeypatch):
+    monkeypatch.setenv("VC1D_LIBRARY", str(tmp_path / "nope.so"))
+    with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
+        _cabi._load()

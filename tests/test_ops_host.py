@@ -1,0 +1,65 @@
+"""Host-side argument checking of the Python operators: the reference's error messages
+(causal-conv1d-mps/test.py:226-236, causal_conv1d_mps/__init__.py:107-135) and the refusal to
+compute anything on the CPU.  Runs without a GPU."""
+import pytest
+import torch
+
+import causal_conv1d
+import viby_model_b200 as V
+
+
+def test_drop_in_module_exports_the_two_reference_names():
+    # the reference imports exactly these (model/model.py:22-25)
+    assert causal_conv1d.causal_conv1d_fn is V.causal_conv1d_fn
+    assert causal_conv1d.causal_conv1d_update is V.causal_conv1d_update
+
+
+def test_dim_mismatch_message():
+    x = torch.randn(2, 4, 8)
+    w = torch.randn(5, 4)
+    with pytest.raises(ValueError, match="does not match"):
+        V.causal_conv1d_fn(x, w, None)
+
+
+def test_rank_message():
+    with pytest.raises(ValueError, match="Expected 3D input tensor"):
+        V.causal_conv1d_fn(torch.randn(4, 8), torch.randn(4, 4))
+    with pytest.raises(ValueError, match="Expected 2D weight tensor"):
+        V.causal_conv1d_fn(torch.randn(1, 4, 8), torch.randn(4, 1, 4))
+    with pytest.raises(ValueError, match="Expected 2D input tensor"):
+        V.causal_conv1d_update(torch.randn(2, 4, 8), torch.randn(2, 4, 3), torch.randn(4, 4))
+
+
+def test_bias_and_width_checks():
+    x = torch.randn(2, 4, 8)
+    with pytest.raises(ValueError, match="Bias dim 3 does not match"):
+        V.causal_conv1d_fn(x, torch.randn(4, 4), torch.randn(3))
+    with pytest.raises(ValueError, match="width must be 2, 3 or 4"):
+        V.causal_conv1d_fn(x, torch.randn(4, 5))
+
+
+def test_activation_and_seq_idx():
+    x = torch.randn(2, 4, 8)
+    w = torch.randn(4, 4)
+    with pytest.raises(NotImplementedError, match="activation must be None, silu, or swish"):
+        V.causal_conv1d_fn(x, w, activation="gelu")
+    with pytest.raises(NotImplementedError, match="seq_idx"):
+        V.causal_conv1d_fn(x, w, seq_idx=torch.zeros(2, 8, dtype=torch.int32))
+
+
+def test_update_shape_checks():
+    with pytest.raises(ValueError, match="doesn't match conv_state"):
+        V.causal_conv1d_update(torch.randn(2, 4), torch.randn(2, 5, 3), torch.randn(4, 4))
+    with pytest.raises(ValueError, match="shorter than width-1"):
+        V.causal_conv1d_update(torch.randn(2, 4), torch.randn(2, 4, 2), torch.randn(4, 4))
+    with pytest.raises(ValueError, match="does not match input dtype"):
+        V.causal_conv1d_update(torch.randn(2, 4), torch.randn(2, 4, 3).bfloat16(), torch.randn(4, 4))
+
+
+def test_cpu_tensors_are_refused_not_computed():
+    x = torch.randn(2, 4, 8)
+    with pytest.raises(ValueError, match="must be on a CUDA device"):
+        V.causal_conv1d_fn(x, torch.randn(4, 4))
+    with pytest.raises(ValueError, match="must be on a CUDA device"):
+        V.causal_conv1d_update(torch.randn(2, 4), torch.randn(2, 4, 3), torch.randn(4, 4))
+    assert V.launch_count() == 0 or not torch.cuda.is_available()

@@ -1,0 +1,374 @@
+"""Parity of causal_conv1d_fn (CUDA, through the C ABI) with the CPU oracle.
+
+The grid mirrors the reference's own kernel tests (causal-conv1d-mps/test.py:110-146:
+dtype x silu x bias x seqlen{1,2,8,...,256} x dim{64,128,256}, batch 2, seed 42; edge shapes
+:206-217; mask recipe :177-180), run for both memory layouts and every kernel of the library,
+then widens to the golden vectors made by the reference's CanonLayer and to the benchmark
+configurations at full size.
+"""
+import pytest
+import torch
+
+import viby_model_b200 as V
+from viby_model_b200 import workloads as WL
+from conftest import GOLDEN_CASES
+from oracle import canon_oracle as O
+from parity import assert_close_to_oracle, exact_fraction
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def make(B, D, T, W, dtype, has_bias, seed=42, layout="channel_last", wdtype=None):
+    g = torch.Generator().manual_seed(seed)
+    if layout == "channel_last":
+        x = torch.randn(B, T, D, generator=g).to(dtype).transpose(1, 2)  # [B,D,T] view, channel stride 1
+    else:
+        x = torch.randn(B, D, T, generator=g).to(dtype)
+    w = torch.randn(D, W, generator=g).to(wdtype or dtype)
+    b = torch.randn(D, generator=g).to(wdtype or dtype) if has_bias else None
+    return x, w, b
+
+
+def dev(t):
+    """Move to the GPU keeping the strides (a transposed view stays a transposed view)."""
+    if t is None:
+        return None
+    out = torch.empty_strided(t.shape, t.stride(), dtype=t.dtype, device=DEV)
+    out.copy_(t)
+    return out
+
+
+def run_both(x, w, b, act, **kw):
+    before = V.launch_count()
+    y = V.causal_conv1d_fn(dev(x), dev(w), dev(b), activation=act, **kw)
+    assert V.launch_count() == before + 1, "the CUDA kernel was not launched"
+    return y
+
+
+# ------------------------------------------------------------------------------------------------
+# the reference's grid
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("act", [None, "silu"])
+@pytest.mark.parametrize("has_bias", [False, True])
+@pytest.mark.parametrize("T", [1, 2, 8, 16, 32, 64, 128, 256])
+@pytest.mark.parametrize("D", [64, 128, 256])
+@pytest.mark.parametrize("layout", ["channel_last", "time_major"])
+def test_reference_grid(D, T, has_bias, act, dtype, layout):
+    x, w, b = make(2, D, T, 4, dtype, has_bias, layout=layout)
+    y = run_both(x, w, b, act)
+    ref = O.causal_conv1d_ref(x, w, b, act)
+    assert y.stride() == x.stride()
+    assert_close_to_oracle(y, ref, f"{layout} D{D} T{T}")
+    vec = 4 if dtype == torch.float32 else 8
+    if layout == "channel_last":
+        assert V.last_kernel() == "channel_last"
+    elif T % vec == 0:
+        assert V.last_kernel() == "time_major"
+    else:
+        assert V.last_kernel() == "generic"
+
+
+@pytest.mark.parametrize("kernel", ["channel_last", "generic"])
+@pytest.mark.parametrize("W", [2, 3, 4])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T", [1, 2, 3, 4, 5, 7, 9, 31, 33, 100])
+def test_widths_and_short_sequences(T, dtype, W, kernel):
+    x, w, b = make(3, 40, T, W, dtype, True, seed=7 + T)
+    y = run_both(x, w, b, "silu", kernel=kernel)
+    assert V.last_kernel() == kernel
+    assert_close_to_oracle(y, O.causal_conv1d_ref(x, w, b, "silu"), f"{kernel} W{W} T{T}")
+
+
+@pytest.mark.parametrize("W", [2, 3, 4])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T", [8, 64, 1000, 4096 + 64])
+def test_time_major_kernel(T, dtype, W):
+    x, w, b = make(2, 33, T, W, dtype, True, seed=T, layout="time_major")
+    y = run_both(x, w, b, "silu", kernel="time_major")
+    assert V.last_kernel() == "time_major"
+    assert_close_to_oracle(y, O.causal_conv1d_ref(x, w, b, "silu"), f"time_major W{W} T{T}")
+
+
+def test_edge_shapes_of_the_reference():
+    # causal-conv1d-mps/test.py:206-217
+    x, w, b = make(1, 1, 1, 4, torch.float32, True, layout="time_major")
+    y = run_both(x, w, b, None)
+    assert y.shape == (1, 1, 1)
+    assert_close_to_oracle(y, O.causal_conv1d_ref(x, w, b, None))
+    x, w, b = make(2, 3, 5, 4, torch.float32, False, layout="time_major")
+    y = run_both(x, w, None, None)
+    assert y.shape == (2, 3, 5)
+    assert_close_to_oracle(y, O.causal_conv1d_ref(x, w, None, None))
+
+
+def test_empty_inputs_launch_nothing():
+    before = V.launch_count()
+    for shape in ((0, 8, 4), (2, 0, 4), (2, 8, 0)):
+        x = torch.empty(shape, device=DEV, dtype=torch.bfloat16)
+        w = torch.zeros(shape[1], 4, device=DEV, dtype=torch.bfloat16)
+        y = V.causal_conv1d_fn(x, w)
+        assert y.shape == x.shape
+    assert V.launch_count() == before
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_odd_layouts_take_the_generic_kernel(dtype):
+    g = torch.Generator().manual_seed(3)
+    base = torch.randn(2, 50, 21, generator=g).to(dtype)  # dim 21: not a multiple of any vector width
+    x = base.transpose(1, 2)
+    w = torch.randn(21, 4, generator=g).to(dtype)
+    y = run_both(x, w, None, "silu")
+    assert V.last_kernel() == "generic"
+    assert_close_to_oracle(y, O.causal_conv1d_ref(x, w, None, "silu"))
+    # sliced (non-dense) input: every second channel and time step of a larger tensor
+    big = torch.randn(2, 16, 64, generator=g).to(dtype)
+    xs = big[:, ::2, ::2]
+    ws = torch.randn(8, 3, generator=g).to(dtype)
+    yd = V.causal_conv1d_fn(dev(big)[:, ::2, ::2], dev(ws), activation=None)
+    assert V.last_kernel() == "generic"
+    assert_close_to_oracle(yd, O.causal_conv1d_ref(xs, ws, None, None))
+
+
+def test_fp32_weights_with_16bit_activations():
+    # the reference's tests keep weight/bias in fp32 while x is bf16/f16 (test.py:133-136)
+    x, w, b = make(2, 64, 33, 4, torch.bfloat16, True, wdtype=torch.float32)
+    y = run_both(x, w, b, "silu")
+    assert_close_to_oracle(y, O.causal_conv1d_ref(x, w, b, "silu"))
+
+
+def test_non_contiguous_weight_view():
+    # CanonLayer passes weight[D,1,K].squeeze(1); also try a strided slice
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(2, 20, 64, generator=g).bfloat16().transpose(1, 2)
+    w3 = torch.randn(64, 1, 4, generator=g).bfloat16()
+    y = run_both(x, w3.squeeze(1), None, None)
+    assert_close_to_oracle(y, O.causal_conv1d_ref(x, w3.squeeze(1), None, None))
+    wide = torch.randn(64, 8, generator=g).bfloat16()
+    wd = dev(wide)[:, 1:8:2]
+    y = V.causal_conv1d_fn(dev(x), wd, activation="silu")
+    assert_close_to_oracle(y, O.causal_conv1d_ref(x, wide[:, 1:8:2], None, "silu"))
+
+
+# ------------------------------------------------------------------------------------------------
+# fused options
+# ------------------------------------------------------------------------------------------------
+def right_pad_mask(B, T, seed, dtype=torch.int64):
+    g = torch.Generator().manual_seed(seed)
+    m = torch.ones(B, T, dtype=dtype)
+    for b in range(B):
+        valid = int(torch.randint(max(T // 2, 1), max(T, 2), (1,), generator=g))
+        m[b, valid:] = 0
+    return m
+
+
+@pytest.mark.parametrize("kernel", ["channel_last", "generic"])
+@pytest.mark.parametrize("mask_dtype", [torch.int64, torch.bool, torch.int32, torch.uint8, torch.bfloat16,
+                                        torch.float32])
+@pytest.mark.parametrize("skip", [True, False])
+def test_mask_dtypes(mask_dtype, skip, kernel):
+    B, D, T = 3, 48, 70
+    x, w, b = make(B, D, T, 4, torch.bfloat16, True, seed=11)
+    m = right_pad_mask(B, T, 12).to(mask_dtype)
+    y = run_both(x, w, b, "silu", attention_mask=dev(m), skip_masked_loads=skip, kernel=kernel)
+    ref = O.causal_conv1d_ref(x, w, b, "silu", attention_mask=m)
+    assert_close_to_oracle(y, ref, f"mask {mask_dtype} skip={skip}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kind", ["left", "holes", "all_zero", "fraction"])
+def test_mask_patterns(kind, dtype):
+    B, D, T = 4, 32, 45
+    x, w, b = make(B, D, T, 4, dtype, True, seed=21)
+    g = torch.Generator().manual_seed(22)
+    if kind == "left":
+        m = torch.ones(B, T, dtype=torch.int64)
+        for i in range(B):
+            m[i, : int(torch.randint(0, T // 2, (1,), generator=g))] = 0
+    elif kind == "holes":
+        m = (torch.rand(B, T, generator=g) > 0.3).to(torch.int64)
+    elif kind == "all_zero":
+        m = torch.zeros(B, T, dtype=torch.int64)
+    else:  # non-binary multiplier, rounded to the I/O dtype like `x * mask`
+        m = (torch.rand(B, T, generator=g) * 2).to(dtype)
+    for kernel in ("channel_last", "generic"):
+        y = run_both(x, w, b, "silu", attention_mask=dev(m), kernel=kernel)
+        assert_close_to_oracle(y, O.causal_conv1d_ref(x, w, b, "silu", attention_mask=m), f"{kind} {kernel}")
+
+
+@pytest.mark.parametrize("kernel", ["channel_last", "generic"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,L", [(1, 4), (2, 4), (3, 3), (4, 4), (5, 8), (40, 4), (40, 8), (40, 3), (7, 8)])
+def test_final_state_and_residual(T, L, dtype, kernel):
+    B, D = 3, 24
+    x, w, b = make(B, D, T, 4, dtype, True, seed=31 + T)
+    m = right_pad_mask(B, T, 32)
+    xd = dev(x)
+    y, st = V.causal_conv1d_fn(xd, dev(w), dev(b), activation="silu", attention_mask=dev(m), residual=True,
+                               return_final_states=True, state_len=L, kernel=kernel)
+    ref_y, ref_s = O.causal_conv1d_ref(x, w, b, "silu", attention_mask=m, residual=x, state_len=L)
+    assert_close_to_oracle(y, ref_y, "fused residual output")
+    assert st.shape == (B, D, L) and st.is_contiguous()
+    # bit-exact, sign of zero included: masked negative inputs are -0.0 in the reference
+    assert torch.equal(st.cpu().view(torch.int16 if dtype != torch.float32 else torch.int32),
+                       ref_s.view(torch.int16 if dtype != torch.float32 else torch.int32))
+
+
+@pytest.mark.parametrize("kernel", ["channel_last", "generic"])
+@pytest.mark.parametrize("W", [2, 3, 4])
+@pytest.mark.parametrize("T2", [1, 2, 5, 37])
+def test_initial_states_continue_a_sequence(T2, W, kernel):
+    B, D, T1 = 2, 32, 19
+    x, w, b = make(B, D, T1 + T2, W, torch.bfloat16, True, seed=41)
+    xd, wd, bd = dev(x), dev(w), dev(b)
+    y_full, s_full = V.causal_conv1d_fn(xd, wd, bd, activation="silu", return_final_states=True, state_len=W,
+                                        kernel=kernel)
+    y1, s1 = V.causal_conv1d_fn(xd[..., :T1], wd, bd, activation="silu", return_final_states=True, state_len=W,
+                                kernel=kernel)
+    y2, s2 = V.causal_conv1d_fn(xd[..., T1:], wd, bd, activation="silu", initial_states=s1,
+                                return_final_states=True, state_len=W, kernel=kernel)
+    assert torch.equal(torch.cat([y1, y2], -1), y_full)  # same kernel arithmetic: bit-identical
+    assert torch.equal(s2, s_full)
+    ref_y, ref_s = O.causal_conv1d_ref(x[..., T1:], w, b, "silu", initial_states=s1.cpu(), state_len=W)
+    assert_close_to_oracle(y2, ref_y)
+    assert torch.equal(s2.cpu(), ref_s)
+
+
+def test_default_final_state_is_width_minus_one_and_out_argument():
+    x, w, b = make(2, 16, 12, 4, torch.float32, False)
+    xd = dev(x)
+    out = torch.empty_like(xd)
+    fs = torch.empty(2, 16, 3, device=DEV)
+    y, st = V.causal_conv1d_fn(xd, dev(w), None, final_states_out=fs, out=out)
+    assert y is out and st is fs
+    assert torch.equal(st.cpu(), x[..., -3:].contiguous())
+
+
+def test_in_place_output_is_refused():
+    x, w, b = make(2, 16, 12, 4, torch.float32, False)
+    xd = dev(x)
+    with pytest.raises(ValueError, match="VC1D_E_ALIAS"):
+        V.causal_conv1d_fn(xd, dev(w), out=xd)
+
+
+def test_kernels_agree_bit_for_bit():
+    """All three prefill kernels accumulate in the same order: identical bits for the same input."""
+    g = torch.Generator().manual_seed(9)
+    xc = torch.randn(2, 64, 96, generator=g).bfloat16()  # [B,D,T] contiguous
+    w = torch.randn(64, 4, generator=g).bfloat16()
+    b = torch.randn(64, generator=g).bfloat16()
+    xd = xc.to(DEV)
+    y_tm = V.causal_conv1d_fn(xd, w.to(DEV), b.to(DEV), activation="silu", kernel="time_major")
+    y_g = V.causal_conv1d_fn(xd, w.to(DEV), b.to(DEV), activation="silu", kernel="generic")
+    x_cl = xd.transpose(1, 2).contiguous().transpose(1, 2)
+    y_cl = V.causal_conv1d_fn(x_cl, w.to(DEV), b.to(DEV), activation="silu", kernel="channel_last")
+    assert torch.equal(y_tm, y_g)
+    assert torch.equal(y_cl, y_g)
+
+
+# ------------------------------------------------------------------------------------------------
+# golden vectors made by the reference's CanonLayer
+# ------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("c", GOLDEN_CASES, ids=[repr(c) for c in GOLDEN_CASES])
+def test_golden_canon_layer_prefill(c):
+    """CanonLayer's CUDA branch rebuilt from the kernel (model/model.py:426-491): mask fused,
+    state of kernel_size columns, residual; compared with the recorded output of the
+    reference's PyTorch branch at the valid positions (the two branches differ at padded
+    positions by construction: masked vs unmasked residual)."""
+    x = c.get("x")
+    w = c.get("weight")
+    b = c.get("bias") if c.has("bias") else None
+    m = c.get("mask") if c.has("mask") else None
+    act = "silu" if c.activation else None
+    xd = dev(x)
+    y, st = V.causal_conv1d_fn(xd.transpose(1, 2), dev(w), dev(b), activation=act,
+                               attention_mask=dev(m), return_final_states=True, state_len=8)
+    out = (xd + y.transpose(1, 2)).cpu()
+    ref = c.get("prefill_cache_out")
+    valid = m.bool().unsqueeze(-1).expand_as(ref) if m is not None else torch.ones_like(ref, dtype=torch.bool)
+    if c.dtype == torch.float32:
+        assert torch.allclose(out[valid], ref[valid], rtol=1e-5, atol=1e-6)
+    else:
+        assert torch.allclose(out[valid].float(), ref[valid].float(), rtol=2 ** -6, atol=2 ** -6)
+    if c.T > 1:
+        assert torch.equal(st.cpu(), c.get("prefill_state"))
+
+
+# ------------------------------------------------------------------------------------------------
+# the benchmark configurations at full size
+# ------------------------------------------------------------------------------------------------
+def test_config1_canon_b_fp32_both_layouts():
+    cfg = WL.CANON_B_FP32
+    x_btd = WL.prefill_inputs(cfg)
+    w, b = WL.weights(cfg.cfg, cfg.dim, cfg.width, cfg.dtype)
+    ref = O.causal_conv1d_ref(x_btd.transpose(1, 2), w, b, None)
+    y = V.causal_conv1d_fn(x_btd.to(DEV).transpose(1, 2), w.to(DEV), b.to(DEV))
+    assert V.last_kernel() == "channel_last"
+    assert_close_to_oracle(y, ref, "cfg1 channel-last")
+    x_bdt = x_btd.transpose(1, 2).contiguous()
+    y2 = V.causal_conv1d_fn(x_bdt.to(DEV), w.to(DEV), b.to(DEV))
+    assert V.last_kernel() == "time_major"
+    assert_close_to_oracle(y2, ref.contiguous(), "cfg1 contiguous")
+
+
+@pytest.mark.parametrize("kernel", [None, "channel_last"])
+def test_config2_canon_d_prefill_bf16(kernel):
+    cfg = WL.CANON_D_PREFILL
+    x_btd = WL.prefill_inputs(cfg)
+    m = WL.attention_mask(cfg)
+    w, b = WL.weights(cfg.cfg, cfg.dim, cfg.width, cfg.dtype)
+    ref, ref_s = O.causal_conv1d_ref(x_btd.transpose(1, 2), w, b, "silu", attention_mask=m, state_len=4)
+    xd = x_btd.to(DEV)
+    y, st = V.causal_conv1d_fn(xd.transpose(1, 2), w.to(DEV), b.to(DEV), activation="silu",
+                               attention_mask=m.to(DEV), return_final_states=True, state_len=4, kernel=kernel)
+    assert_close_to_oracle(y, ref, "cfg2")
+    assert exact_fraction(y, ref) > 0.999
+    assert torch.equal(st.cpu(), ref_s)
+    # unfused flow of the reference's CUDA branch: mask multiply outside, plain kernel call
+    y_plain = V.causal_conv1d_fn((xd * m.to(DEV).unsqueeze(-1)).transpose(1, 2), w.to(DEV), b.to(DEV),
+                                 activation="silu")
+    assert torch.equal(y_plain, y)
+
+
+def test_config5_ragged_shard_properties():
+    """One GPU's share of the ragged sweep at 8 GPUs (64 sequences x 4096 x 3456): sampled
+    sequences against the oracle, plus properties that need no oracle at this size."""
+    cfg = WL.RAGGED_SWEEP
+    rows = list(WL.shard_rows(cfg.batch, 3, 8))
+    assert len(rows) == 64
+    x = WL.prefill_inputs(cfg, rows, device=DEV, generate_on="cuda")
+    m = WL.attention_mask(cfg, rows, device=DEV)
+    w, b = WL.weights(cfg.cfg, cfg.dim, cfg.width, cfg.dtype, device=DEV)
+    y = V.causal_conv1d_fn(x.transpose(1, 2), w, b, activation="silu", attention_mask=m)
+    lens = WL.sequence_lengths(cfg, rows)
+    # (1) sampled sequences vs the oracle
+    for i in (0, 17, 63):
+        ref = O.causal_conv1d_ref(x[i:i + 1].cpu().transpose(1, 2), w.cpu(), b.cpu(), "silu",
+                                  attention_mask=m[i:i + 1].cpu())
+        assert_close_to_oracle(y[i:i + 1], ref, f"cfg5 row {rows[i]} len {int(lens[i])}")
+    # (2) beyond len+W-1 every output is act(bias): constant along time
+    const = torch.nn.functional.silu(b.float()).to(cfg.dtype)
+    for i in range(len(rows)):
+        n = int(lens[i]) + cfg.width - 1
+        if n < cfg.seqlen:
+            tail = y[i, :, n:]
+            assert bool(((tail.float() - const.float()[:, None]).abs() <= 2 ** -7 * const.float().abs()[:, None]
+                         + 1e-6).all())
+    # (3) causality: changing the last valid token changes nothing before it
+    x2 = x.clone()
+    for i in range(len(rows)):
+        x2[i, int(lens[i]) - 1] += 1
+    y2 = V.causal_conv1d_fn(x2.transpose(1, 2), w, b, activation="silu", attention_mask=m)
+    for i in (1, 30, 62):
+        n = int(lens[i]) - 1
+        assert torch.equal(y2[i, :, :n], y[i, :, :n])
+        assert not torch.equal(y2[i, :, n], y[i, :, n])
+    # (4) garbage in padded rows is never observed
+    x3 = x.clone()
+    x3[~m.bool()] = float("nan")
+    y3 = V.causal_conv1d_fn(x3.transpose(1, 2), w, b, activation="silu", attention_mask=m)
+    assert torch.equal(y3, y)
+    # (5) sharding is invisible: a sub-batch gives the same bits
+    y_sub = V.causal_conv1d_fn(x[8:24].transpose(1, 2), w, b, activation="silu", attention_mask=m[8:24])
+    assert torch.equal(y_sub, y[8:24])

@@ -1,0 +1,170 @@
+"""Parity of causal_conv1d_update (CUDA, through the C ABI) with the CPU oracle: outputs within
+tolerance, conv_state bit-exact, for the shifting state at every supported length and the
+circular state of causal-conv1d-mps; then the decode configuration at full size."""
+import pytest
+import torch
+
+import viby_model_b200 as V
+from viby_model_b200 import workloads as WL
+from conftest import GOLDEN_CASES
+from oracle import canon_oracle as O
+from parity import assert_close_to_oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def bits(t):
+    return t.view(torch.int32 if t.dtype == torch.float32 else torch.int16)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("W", [2, 3, 4])
+@pytest.mark.parametrize("L", [1, 2, 3, 4, 5, 8, 11])
+@pytest.mark.parametrize("kernel", [None, "generic"])
+def test_update_steps(dtype, W, L, kernel):
+    if L < W - 1:
+        pytest.skip("state shorter than the history the taps need")
+    B, D = 5, 64
+    g = torch.Generator().manual_seed(100 + 10 * W + L)
+    w = (torch.rand(D, W, generator=g) - 0.5).to(dtype)
+    b = (torch.rand(D, generator=g) - 0.5).to(dtype)
+    state = torch.randn(B, D, L, generator=g).to(dtype)
+    sd = state.to(DEV)
+    wd, bd = w.to(DEV), b.to(DEV)
+    for step in range(6):
+        xt = torch.randn(B, D, generator=g).to(dtype)
+        before = V.launch_count()
+        y = V.causal_conv1d_update(xt.to(DEV), sd, wd, bd, activation="silu", kernel=kernel)
+        assert V.launch_count() == before + 1
+        ref = O.causal_conv1d_update_ref(xt, state, w, b, "silu")
+        assert_close_to_oracle(y, ref, f"step {step}")
+        assert torch.equal(bits(sd.cpu()), bits(state)), f"state after step {step}"
+    expect = "update_generic" if (kernel == "generic" or L not in (1, 2, 3, 4, 8)) else "update_vec"
+    assert V.last_kernel() == expect
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_update_odd_dim_and_no_bias_no_activation(dtype):
+    B, D, W, L = 3, 21, 4, 4
+    g = torch.Generator().manual_seed(5)
+    w = torch.randn(D, W, generator=g).to(dtype)
+    state = torch.randn(B, D, L, generator=g).to(dtype)
+    sd = state.to(DEV)
+    xt = torch.randn(B, D, generator=g).to(dtype)
+    y = V.causal_conv1d_update(xt.to(DEV), sd, w.to(DEV))
+    assert V.last_kernel() == "update_generic"
+    assert_close_to_oracle(y, O.causal_conv1d_update_ref(xt, state, w))
+    assert torch.equal(bits(sd.cpu()), bits(state))
+
+
+def test_update_state_moves_raw_bits():
+    """NaN payloads and signed zeros travel through the state unchanged."""
+    B, D, L = 2, 16, 4
+    state = torch.zeros(B, D, L, dtype=torch.bfloat16)
+    raw = bits(state)
+    raw[0, :, 1] = 0x7FA5  # NaN with a payload
+    raw[1, :, 2] = -0x8000  # -0.0
+    xt = torch.randn(B, D).bfloat16()
+    w = torch.randn(D, 4).bfloat16()
+    sd = state.to(DEV)
+    V.causal_conv1d_update(xt.to(DEV), sd, w.to(DEV))
+    got = bits(sd.cpu())
+    assert torch.equal(got[..., :3], raw[..., 1:])
+    assert torch.equal(got[..., 3], bits(xt))
+
+
+def test_update_accepts_trailing_singleton_and_strided_x():
+    B, D, L = 4, 64, 4
+    g = torch.Generator().manual_seed(8)
+    w = torch.randn(D, 4, generator=g).bfloat16()
+    state = torch.randn(B, D, L, generator=g).bfloat16()
+    x3 = torch.randn(B, 1, D, generator=g).bfloat16()
+    sd = state.to(DEV)
+    # the model hands over x[B,1,D].squeeze(1); also accept [B,D,1]
+    y = V.causal_conv1d_update(x3.to(DEV).squeeze(1), sd, w.to(DEV), activation="silu")
+    ref = O.causal_conv1d_update_ref(x3.squeeze(1), state, w, None, "silu")
+    assert_close_to_oracle(y, ref)
+    y2 = V.causal_conv1d_update(x3.to(DEV).transpose(1, 2), sd, w.to(DEV), activation="silu")
+    ref2 = O.causal_conv1d_update_ref(x3.squeeze(1), state, w, None, "silu")
+    assert y2.shape == (B, D, 1)
+    assert_close_to_oracle(y2.squeeze(-1), ref2)
+    assert torch.equal(bits(sd.cpu()), bits(state))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_circular_state_update(dtype):
+    """cache_seqlens mode (causal_conv1d.metal:586-664), per-sequence write positions."""
+    B, D, W, L = 4, 32, 4, 8
+    g = torch.Generator().manual_seed(17)
+    w = (torch.rand(D, W, generator=g) - 0.5).to(dtype)
+    b = (torch.rand(D, generator=g) - 0.5).to(dtype)
+    state = torch.randn(B, D, L, generator=g).to(dtype)
+    seqlens = torch.tensor([0, 3, 7, 12], dtype=torch.int32)
+    sd = state.to(DEV)
+    for step in range(10):
+        xt = torch.randn(B, D, generator=g).to(dtype)
+        y = V.causal_conv1d_update(xt.to(DEV), sd, w.to(DEV), b.to(DEV), activation="silu",
+                                   cache_seqlens=seqlens.to(DEV), residual=True)
+        ref = O.causal_conv1d_update_ref(xt, state, w, b, "silu", cache_seqlens=seqlens, residual=True)
+        assert V.last_kernel() == "update_generic"
+        assert_close_to_oracle(y, ref, f"circular step {step}")
+        assert torch.equal(bits(sd.cpu()), bits(state))
+        seqlens = seqlens + 1
+
+
+@pytest.mark.parametrize("c", [c for c in GOLDEN_CASES if c.T > 1], ids=lambda c: repr(c))
+def test_golden_decode_after_prefill(c):
+    """Prefill with the kernel, then the reference's recorded decode steps: the 8-wide state
+    must equal the reference's bit for bit after every step, outputs within tolerance."""
+    x = c.get("x")
+    w = c.get("weight")
+    b = c.get("bias") if c.has("bias") else None
+    m = c.get("mask") if c.has("mask") else None
+    act = "silu" if c.activation else None
+    wd = w.to(DEV)
+    bd = b.to(DEV) if b is not None else None
+    _, st = V.causal_conv1d_fn(x.to(DEV).transpose(1, 2), wd, bd, activation=act,
+                               attention_mask=m.to(DEV) if m is not None else None,
+                               return_final_states=True, state_len=8)
+    xs = c.get("decode_x")
+    for s in range(xs.shape[0]):
+        xt = xs[s].squeeze(1).to(DEV)
+        y = V.causal_conv1d_update(xt, st, wd, bd, activation=act)
+        out = (xt + y).cpu()
+        ref = c.get("decode_out")[s].squeeze(1)
+        if c.dtype == torch.float32:
+            assert torch.allclose(out, ref, rtol=1e-5, atol=1e-6)
+        else:
+            assert torch.allclose(out.float(), ref.float(), rtol=2 ** -6, atol=2 ** -6)
+        assert torch.equal(bits(st.cpu()), bits(c.get("decode_state")[s]))
+
+
+@pytest.mark.parametrize("L", [3, 4, 8])
+def test_config3_decode_1024_steps(L):
+    """batch 256, dim 960, width 4, bf16; conv_state seeded from a 512-token prefill; 1024
+    successive steps; every output checked, the final state bit-exact."""
+    cfg = WL.DECODE_CANON_B
+    w, b = WL.weights(cfg.cfg, cfg.dim, cfg.width, cfg.dtype)
+    pre = WL.decode_prefill(cfg)
+    toks = WL.decode_tokens(cfg)
+    wd, bd = w.to(DEV), b.to(DEV)
+    _, st = V.causal_conv1d_fn(pre.to(DEV).transpose(1, 2), wd, bd, return_final_states=True, state_len=L)
+    ref_state = pre.transpose(1, 2)[..., -L:].contiguous()
+    assert torch.equal(bits(st.cpu()), bits(ref_state))
+    toks_d = toks.to(DEV)
+    ys = torch.empty_like(toks_d)
+    before = V.launch_count()
+    for s in range(cfg.steps):
+        V.causal_conv1d_update(toks_d[s], st, wd, bd, out=ys[s])
+    assert V.launch_count() == before + cfg.steps
+    assert V.last_kernel() == "update_vec"
+    ys = ys.cpu()
+    for s in range(cfg.steps):
+        ref = O.causal_conv1d_update_ref(toks[s], ref_state, w, b)
+        assert_close_to_oracle(ys[s], ref, f"cfg3 step {s}")
+    assert torch.equal(bits(st.cpu()), bits(ref_state))
+    # decoding continues the prefill: the outputs equal a prefill over [prefill | tokens]
+    full = torch.cat([pre, toks.transpose(0, 1)], dim=1).to(DEV)
+    y_full = V.causal_conv1d_fn(full.transpose(1, 2), wd, bd)
+    assert torch.equal(y_full[..., cfg.prefill_len:].cpu(), ys.permute(1, 2, 0))

@@ -1,0 +1,22 @@
+"""B200 (sm_100a) depthwise causal conv1d for Viby's Canon A/B/C/D layers.
+
+Public surface:
+  causal_conv1d_fn, causal_conv1d_update  -- the CUDA slot of the reference's CanonLayer
+                                             (model/model.py:20-30, 305-311, 460-466)
+  launch_count, last_kernel               -- proof that the CUDA kernels ran
+
+The operators call hand-written CUDA kernels through the C ABI of include/vc1d.h
+(libvc1d.so, built by ``python -m viby_model_b200.build``).  Importing the package without
+that library raises ImportError: there is no CPU or PyTorch fallback.
+"""
+from ._cabi import last_kernel, launch_count, library_path
+from .ops import causal_conv1d_fn, causal_conv1d_update
+
+__all__ = [
+    "causal_conv1d_fn",
+    "causal_conv1d_update",
+    "launch_count",
+    "last_kernel",
+    "library_path",
+]
+__version__ = "0.1.0"

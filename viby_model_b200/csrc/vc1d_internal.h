@@ -1,0 +1,56 @@
+// Interface between the validating C-ABI layer (api.cu) and the per-kernel translation
+// units.  Each launcher receives arguments that api.cu has already validated and that
+// satisfy the layout preconditions listed beside it; it returns a cudaError_t.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/vc1d.h"
+
+namespace vc1d {
+
+// Number of SMs of the current device (cached per device ordinal).
+int sm_count();
+
+// Kernel launch bookkeeping shared by all launchers.
+void note_launch(const char* kernel_name);
+
+// Channel-last prefill: x/y (and residual) have channel stride 1, dim % vec == 0, every
+// base pointer and every batch/time stride is 16-byte aligned.
+cudaError_t launch_prefill_channel_last(const vc1d_prefill_args& a, cudaStream_t s);
+
+// Same preconditions as channel-last plus: no initial_state, dim*elem_size % 16 == 0
+// (tensor-map stride rule).  Stages (rows + halo) x channel tiles through shared memory
+// with cp.async.bulk.tensor.
+cudaError_t launch_prefill_tma(const vc1d_prefill_args& a, cudaStream_t s);
+bool tma_available();
+
+// Time-major prefill: x/y have time stride 1, seqlen % vec == 0, aligned rows, none of
+// mask / residual / initial_state / final_state.
+cudaError_t launch_prefill_time_major(const vc1d_prefill_args& a, cudaStream_t s);
+
+// Any strides, every option.
+cudaError_t launch_prefill_generic(const vc1d_prefill_args& a, cudaStream_t s);
+
+// Vectorised decode: x/y channel stride 1, conv_state strides (.., state_len, 1),
+// dim % vec == 0, aligned, state_len in {1,2,3,4,8}, no cache_seqlens.
+cudaError_t launch_update_vec(const vc1d_update_args& a, cudaStream_t s);
+bool update_vec_supports(int state_len, int width);
+
+// Any strides, shifting or circular state.
+cudaError_t launch_update_generic(const vc1d_update_args& a, cudaStream_t s);
+
+inline int elem_bytes(int dtype) {
+    switch (dtype) {
+        case VC1D_F32: return 4;
+        case VC1D_BF16: return 2;
+        case VC1D_F16: return 2;
+        case VC1D_U8: return 1;
+        case VC1D_I32: return 4;
+        case VC1D_I64: return 8;
+        default: return 0;
+    }
+}
+
+}  // namespace vc1d

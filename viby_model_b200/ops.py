@@ -1,0 +1,325 @@
+"""CUDA-slot operators of Viby's CanonLayer: ``causal_conv1d_fn`` and ``causal_conv1d_update``.
+
+Call signatures follow the reference's call sites (model/model.py:460-466 and 305-311) and
+its own mirror of the prefill signature (causal-conv1d-mps/causal_conv1d_mps/autograd.py:
+501-510).  Everything after the bare ``*`` is an extension that fuses work the reference's
+CanonLayer does in separate PyTorch passes around the kernel; with the extensions left at
+their defaults the functions are drop-in for the reference's CUDA branch.
+
+Host code only marshals pointers, sizes and strides into the C ABI (include/vc1d.h).
+There is no PyTorch or CPU implementation behind these functions.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple, Union
+
+import torch
+
+from . import _cabi
+
+_IO_DTYPES = {torch.float32: _cabi.VC1D_F32, torch.bfloat16: _cabi.VC1D_BF16, torch.float16: _cabi.VC1D_F16}
+_MASK_DTYPES = {
+    torch.bool: _cabi.VC1D_U8,
+    torch.uint8: _cabi.VC1D_U8,
+    torch.int32: _cabi.VC1D_I32,
+    torch.int64: _cabi.VC1D_I64,
+    torch.float32: _cabi.VC1D_F32,
+    torch.bfloat16: _cabi.VC1D_BF16,
+    torch.float16: _cabi.VC1D_F16,
+}
+
+
+def _activation_code(activation) -> int:
+    # reference: autograd.py:527-530 accepts None, "silu", "swish"; the BTD API passes a bool
+    if activation is None or activation is False:
+        return _cabi.VC1D_ACT_NONE
+    if activation is True or activation in ("silu", "swish"):
+        return _cabi.VC1D_ACT_SILU
+    raise NotImplementedError("activation must be None, silu, or swish")
+
+
+def _require_cuda(t: torch.Tensor, what: str) -> None:
+    if t.device.type != "cuda":
+        raise ValueError(f"{what} tensor must be on a CUDA device, got {t.device}")
+
+
+def _check_weight_shapes(weight: torch.Tensor, bias: Optional[torch.Tensor], dim: int) -> int:
+    """Shape checks with the reference's messages (causal_conv1d_mps/__init__.py:116-135)."""
+    if weight.dim() != 2:
+        raise ValueError(f"Expected 2D weight tensor (dim, width), got {weight.dim()}D")
+    weight_dim, width = weight.shape
+    if dim != weight_dim:
+        raise ValueError(f"Input dim {dim} does not match weight dim {weight_dim}")
+    if width not in (2, 3, 4):
+        raise ValueError(f"width must be 2, 3 or 4, got {width}")
+    if bias is not None:
+        if bias.dim() != 1:
+            raise ValueError(f"Expected 1D bias tensor, got {bias.dim()}D")
+        if bias.shape[0] != dim:
+            raise ValueError(f"Bias dim {bias.shape[0]} does not match input dim {dim}")
+    return width
+
+
+def _align_weights(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]):
+    """Weight/bias dtype: same as x, or float32 (converted in-kernel); bias follows weight."""
+    _require_cuda(weight, "Weight")
+    if weight.dtype != x.dtype and weight.dtype != torch.float32:
+        weight = weight.to(x.dtype)
+    if bias is not None:
+        _require_cuda(bias, "Bias")
+        if bias.dtype != weight.dtype:
+            bias = bias.to(weight.dtype)
+        if not bias.is_contiguous():
+            bias = bias.contiguous()
+    return weight, bias
+
+
+def _stream_handle(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def causal_conv1d_fn(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    seq_idx: Optional[torch.Tensor] = None,
+    initial_states: Optional[torch.Tensor] = None,
+    return_final_states: bool = False,
+    final_states_out: Optional[torch.Tensor] = None,
+    activation: Optional[str] = None,
+    *,
+    attention_mask: Optional[torch.Tensor] = None,
+    skip_masked_loads: bool = True,
+    residual: Union[None, bool, torch.Tensor] = None,
+    state_len: Optional[int] = None,
+    out: Optional[torch.Tensor] = None,
+    kernel: Optional[str] = None,
+    rows_per_thread: int = 0,
+    block_threads: int = 0,
+    unroll: int = 0,
+) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
+    """Depthwise causal conv1d over ``x[batch, dim, seqlen]`` (prefill).
+
+    ``y[b,d,t] = act(bias[d] + sum_w weight[d,w] * x[b,d,t-(W-1-w)])`` with zeros (or
+    ``initial_states``) left of t=0, fp32 accumulation, one rounding to ``x.dtype``.  ``x`` may
+    have any strides; the channel-last view ``x_btd.transpose(1, 2)`` that CanonLayer passes
+    (model/model.py:459) and contiguous ``[B,D,T]`` both take 128-bit vectorised kernels.
+    The result has the shape, dtype and (for dense inputs) the strides of ``x``.
+
+    Reference arguments (model/model.py:460-466; autograd.py:501-510):
+      weight ``[dim, width]`` (width 2..4), bias ``[dim]`` or None, activation None|"silu"|"swish",
+      ``seq_idx`` must be None (the reference never passes anything else),
+      ``initial_states[batch, dim, >=width-1]``: history used instead of zeros (its last width-1 columns),
+      ``return_final_states`` / ``final_states_out``: also return the last ``state_len`` inputs as
+      ``[batch, dim, state_len]`` (default state_len = width-1), right-aligned like
+      model/model.py:470-489.
+
+    Extensions (keyword-only), each replacing a separate PyTorch pass of CanonLayer.forward:
+      attention_mask ``[batch, seqlen]`` (bool / int / float): inputs are multiplied by the mask
+        before the conv (model/model.py:454-457); outputs at masked positions are still produced.
+        With ``skip_masked_loads`` rows whose mask is 0 are not read at all and count as +0
+        (identical results for finite inputs).
+      residual: a tensor shaped like ``x`` (or True for ``x`` itself) added after the activation,
+        with the same two roundings as ``x + y`` (model/model.py:491).
+      state_len: width of the returned final state (CanonLayer keeps ``kernel_size`` columns).
+      out: preallocated output; kernel / rows_per_thread / block_threads / unroll: tuning overrides.
+    """
+    if x.dim() != 3:
+        raise ValueError(f"Expected 3D input tensor (batch, dim, seqlen), got {x.dim()}D")
+    batch, dim, seqlen = x.shape
+    width = _check_weight_shapes(weight, bias, dim)
+    if x.dtype not in _IO_DTYPES:
+        raise ValueError(f"unsupported dtype {x.dtype}: expected float32, bfloat16 or float16")
+    if seq_idx is not None:
+        raise NotImplementedError("seq_idx is not supported")
+    act = _activation_code(activation)
+    _require_cuda(x, "Input")
+    weight, bias = _align_weights(x, weight, bias)
+
+    if out is None:
+        out = torch.empty_like(x)
+    elif out.shape != x.shape or out.dtype != x.dtype or out.device != x.device:
+        raise ValueError("out must match x in shape, dtype and device")
+
+    a = _cabi.PrefillArgs()
+    a.struct_size = C.sizeof(_cabi.PrefillArgs)
+    a.dtype = _IO_DTYPES[x.dtype]
+    a.wdtype = _IO_DTYPES[weight.dtype]
+    a.activation = act
+    a.batch, a.dim, a.seqlen, a.width = batch, dim, seqlen, width
+    a.x = x.data_ptr()
+    a.y = out.data_ptr()
+    a.weight = weight.data_ptr()
+    a.bias = bias.data_ptr() if bias is not None else None
+    a.x_stride_b, a.x_stride_d, a.x_stride_t = x.stride()
+    a.y_stride_b, a.y_stride_d, a.y_stride_t = out.stride()
+    a.w_stride_d, a.w_stride_w = weight.stride()
+
+    if attention_mask is not None:
+        m = attention_mask
+        _require_cuda(m, "Attention mask")
+        if m.dim() != 2:
+            raise ValueError(f"Expected 2D attention mask, got {m.dim()}D")
+        if tuple(m.shape) != (batch, seqlen):
+            raise ValueError(
+                f"Attention mask shape {tuple(m.shape)} does not match input shape ({batch}, {seqlen})"
+            )
+        if m.dtype not in _MASK_DTYPES:
+            raise ValueError(f"unsupported attention mask dtype {m.dtype}")
+        a.mask = m.data_ptr()
+        a.mask_dtype = _MASK_DTYPES[m.dtype]
+        a.mask_stride_b, a.mask_stride_t = m.stride()
+        a.skip_masked_loads = 1 if skip_masked_loads else 0
+
+    if residual is not None and residual is not False:
+        r = x if residual is True else residual
+        if r.shape != x.shape or r.dtype != x.dtype or r.device != x.device:
+            raise ValueError("residual must match x in shape, dtype and device")
+        a.residual = r.data_ptr()
+        a.r_stride_b, a.r_stride_d, a.r_stride_t = r.stride()
+
+    if initial_states is not None:
+        s0 = initial_states
+        if s0.dim() != 3 or s0.shape[0] != batch or s0.shape[1] != dim or s0.shape[2] < width - 1:
+            raise ValueError(
+                f"initial_states shape {tuple(s0.shape)} does not match (batch, dim, >=width-1) = "
+                f"({batch}, {dim}, >={width - 1})"
+            )
+        if s0.dtype != x.dtype or s0.device != x.device:
+            raise ValueError("initial_states must match x in dtype and device")
+        if not s0.is_contiguous():
+            s0 = s0.contiguous()
+        a.initial_state = s0.data_ptr()
+        a.init_len = s0.shape[2]
+
+    final_states = None
+    if return_final_states or final_states_out is not None:
+        L = int(state_len) if state_len is not None else (
+            final_states_out.shape[2] if final_states_out is not None else width - 1
+        )
+        if L < 1:
+            raise ValueError(f"state_len must be >= 1, got {L}")
+        if final_states_out is not None:
+            final_states = final_states_out
+            if tuple(final_states.shape) != (batch, dim, L) or final_states.dtype != x.dtype:
+                raise ValueError(
+                    f"final_states_out shape {tuple(final_states.shape)} does not match ({batch}, {dim}, {L})"
+                )
+            if not final_states.is_contiguous():
+                raise ValueError("final_states_out must be contiguous [batch, dim, state_len]")
+        else:
+            final_states = torch.empty((batch, dim, L), dtype=x.dtype, device=x.device)
+        a.final_state = final_states.data_ptr()
+        a.state_len = L
+
+    if kernel not in _cabi.KERNEL_BY_NAME:
+        raise ValueError(f"unknown kernel {kernel!r}")
+    a.kernel = _cabi.KERNEL_BY_NAME[kernel]
+    a.rows_per_thread = int(rows_per_thread)
+    a.block_threads = int(block_threads)
+    a.unroll = int(unroll)
+
+    if x.device.index != torch.cuda.current_device():
+        with torch.cuda.device(x.device):
+            st = _cabi.lib.vc1d_prefill(C.byref(a), _stream_handle(x.device))
+    else:
+        st = _cabi.lib.vc1d_prefill(C.byref(a), _stream_handle(x.device))
+    _cabi.check(st, "causal_conv1d_fn")
+    if return_final_states or final_states_out is not None:
+        return out, final_states
+    return out
+
+
+def causal_conv1d_update(
+    x: torch.Tensor,
+    conv_state: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    activation: Optional[str] = None,
+    cache_seqlens: Optional[torch.Tensor] = None,
+    *,
+    residual: bool = False,
+    out: Optional[torch.Tensor] = None,
+    kernel: Optional[str] = None,
+    block_threads: int = 0,
+) -> torch.Tensor:
+    """Single-token causal conv step against a rolling ``conv_state`` (decode).
+
+    ``cat = [conv_state | x]``; ``y = act(bias + cat[..., -W:] . weight)``;
+    ``conv_state <- cat[..., -state_len:]`` **in place**; returns ``y`` shaped like ``x``.
+    Matches the reference call at model/model.py:305-311 and the PyTorch step at
+    model/model.py:372-398 for any ``state_len >= width-1`` (the reference's CUDA branch uses
+    ``state_len == width``, its fallback 8).
+
+    x ``[batch, dim]`` (or ``[batch, dim, 1]``), conv_state ``[batch, dim, state_len]``.
+    ``cache_seqlens[batch]`` (int32) switches to the circular-buffer state of
+    causal-conv1d-mps (causal_conv1d.metal:586-664): write position ``cache_seqlens[b] % state_len``.
+    ``residual=True`` adds ``x`` to the result (causal_conv1d.metal:655-658).
+    """
+    squeeze = False
+    if x.dim() == 3 and x.shape[-1] == 1:
+        x = x.squeeze(-1)
+        squeeze = True
+    if x.dim() != 2:
+        raise ValueError(f"Expected 2D input tensor (batch, dim), got {x.dim()}D")
+    if conv_state.dim() != 3:
+        raise ValueError(f"Expected 3D conv_state tensor (batch, dim, state_len), got {conv_state.dim()}D")
+    batch, dim = x.shape
+    conv_batch, conv_dim, L = conv_state.shape
+    if batch != conv_batch or dim != conv_dim:
+        raise ValueError(f"Input shape {tuple(x.shape)} doesn't match conv_state batch/dim {(conv_batch, conv_dim)}")
+    width = _check_weight_shapes(weight, bias, dim)
+    if L < width - 1 or L < 1:
+        raise ValueError(f"conv_state length {L} is shorter than width-1 = {width - 1}")
+    if x.dtype not in _IO_DTYPES:
+        raise ValueError(f"unsupported dtype {x.dtype}: expected float32, bfloat16 or float16")
+    if conv_state.dtype != x.dtype:
+        raise ValueError(f"conv_state dtype {conv_state.dtype} does not match input dtype {x.dtype}")
+    act = _activation_code(activation)
+    _require_cuda(x, "Input")
+    _require_cuda(conv_state, "Convolution state")
+    weight, bias = _align_weights(x, weight, bias)
+
+    if out is None:
+        out = torch.empty_like(x)
+    elif out.shape != x.shape or out.dtype != x.dtype or out.device != x.device:
+        raise ValueError("out must match x in shape, dtype and device")
+
+    a = _cabi.UpdateArgs()
+    a.struct_size = C.sizeof(_cabi.UpdateArgs)
+    a.dtype = _IO_DTYPES[x.dtype]
+    a.wdtype = _IO_DTYPES[weight.dtype]
+    a.activation = act
+    a.batch, a.dim, a.width, a.state_len = batch, dim, width, L
+    a.x = x.data_ptr()
+    a.y = out.data_ptr()
+    a.conv_state = conv_state.data_ptr()
+    a.weight = weight.data_ptr()
+    a.bias = bias.data_ptr() if bias is not None else None
+    a.x_stride_b, a.x_stride_d = x.stride()
+    a.y_stride_b, a.y_stride_d = out.stride()
+    a.s_stride_b, a.s_stride_d, a.s_stride_l = conv_state.stride()
+    a.w_stride_d, a.w_stride_w = weight.stride()
+    if cache_seqlens is not None:
+        _require_cuda(cache_seqlens, "cache_seqlens")
+        if cache_seqlens.dim() != 1:
+            raise ValueError(f"Expected 1D cache_seqlens, got {cache_seqlens.dim()}D")
+        if cache_seqlens.shape[0] != batch:
+            raise ValueError(f"cache_seqlens batch size {cache_seqlens.shape[0]} != input batch {batch}")
+        if cache_seqlens.dtype != torch.int32 or not cache_seqlens.is_contiguous():
+            cache_seqlens = cache_seqlens.to(torch.int32).contiguous()
+        a.cache_seqlens = cache_seqlens.data_ptr()
+    a.residual = 1 if residual else 0
+    if kernel not in (None, "auto", "generic"):
+        raise ValueError(f"unknown update kernel {kernel!r}")
+    a.kernel = _cabi.KERNEL_GENERIC if kernel == "generic" else _cabi.KERNEL_AUTO
+    a.block_threads = int(block_threads)
+
+    if x.device.index != torch.cuda.current_device():
+        with torch.cuda.device(x.device):
+            st = _cabi.lib.vc1d_update(C.byref(a), _stream_handle(x.device))
+    else:
+        st = _cabi.lib.vc1d_update(C.byref(a), _stream_handle(x.device))
+    _cabi.check(st, "causal_conv1d_update")
+    return out.unsqueeze(-1) if squeeze else out
