@@ -175,6 +175,11 @@ VC1D_API uint64_t vc1d_launch_count(void);
  * ("channel_last", "time_major", "generic", "tma", "update_vec", "update_generic"). */
 VC1D_API const char* vc1d_last_kernel(void);
 
+/* Number of bounded mbarrier waits that expired inside the TMA prefill kernel since the process
+ * started (0 in a healthy run; a CTA whose wait expires abandons its remaining tiles).  Reads a
+ * device counter with a synchronising copy: call it after the stream has been synchronised. */
+VC1D_API unsigned int vc1d_tma_timeouts(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,10 +6,10 @@ Public surface:
   launch_count, last_kernel               -- proof that the CUDA kernels ran
 
 The operators call hand-written CUDA kernels through the C ABI of include/vc1d.h
-(libvc1d.so, built by ``python -m viby_model_b200.build``).  Importing the package without
+(libvc1d.so, built by ``python viby_model_b200/build.py``).  Importing the package without
 that library raises ImportError: there is no CPU or PyTorch fallback.
 """
-from ._cabi import last_kernel, launch_count, library_path
+from ._cabi import last_kernel, launch_count, library_path, tma_timeouts
 from .ops import causal_conv1d_fn, causal_conv1d_update
 
 __all__ = [
@@ -18,5 +18,6 @@ __all__ = [
     "launch_count",
     "last_kernel",
     "library_path",
+    "tma_timeouts",
 ]
 __version__ = "0.1.0"

@@ -1,7 +1,7 @@
 """ctypes binding of libvc1d.so (declarations: include/vc1d.h).
 
 The shared library is the product; there is no fallback.  Importing this module raises
-ImportError when the library has not been built (``python -m viby_model_b200.build``).
+ImportError when the library has not been built (``python viby_model_b200/build.py``).
 """
 from __future__ import annotations
 
@@ -120,6 +120,7 @@ EXPORTS = {
     "vc1d_status_string": (C.c_char_p, [C.c_int]),
     "vc1d_launch_count": (C.c_uint64, []),
     "vc1d_last_kernel": (C.c_char_p, []),
+    "vc1d_tma_timeouts": (C.c_uint, []),
 }
 
 
@@ -135,7 +136,7 @@ def _load() -> C.CDLL:
     if not path.exists():
         raise ImportError(
             f"{path} not found: the CUDA library has not been built. "
-            "Run `python -m viby_model_b200.build` (needs nvcc 12.9, targets sm_100a). "
+            "Run `python viby_model_b200/build.py` (needs nvcc 12.9, targets sm_100a). "
             "There is no CPU or PyTorch fallback."
         )
     lib = C.CDLL(str(path))
@@ -168,6 +169,11 @@ def launch_count() -> int:
 
 def last_kernel() -> str:
     return lib.vc1d_last_kernel().decode()
+
+
+def tma_timeouts() -> int:
+    """Expired mbarrier waits in the TMA kernel so far (synchronising read; 0 when healthy)."""
+    return int(lib.vc1d_tma_timeouts())
 
 
 _VALUE_ERRORS = {

@@ -1,6 +1,6 @@
 """Build recipe for libvc1d.so: nvcc, sm_100a only, in-tree output next to this file.
 
-Run as ``python -m viby_model_b200.build`` (add ``--force`` to rebuild everything,
+Run as ``python viby_model_b200/build.py`` (add ``--force`` to rebuild everything,
 ``--verbose`` for ptxas register/spill reports).  Objects go to ``build/vc1d`` at the
 repository root; the shared library is written to ``viby_model_b200/libvc1d.so``.
 """

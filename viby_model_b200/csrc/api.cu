@@ -174,12 +174,19 @@ VC1D_API int vc1d_prefill(const vc1d_prefill_args* a, void* stream) {
             break;
         default:
             // a dim-1 or seqlen-1 tensor can satisfy both layouts; channel-last carries the fused options
-            if (cl && (a->dim > 1 || !tm))
-                err = launch_prefill_channel_last(*a, s);
-            else if (tm)
+            if (cl && (a->dim > 1 || !tm)) {
+                // large problems stream through the TMA pipeline; small ones are launch-bound and
+                // take the direct kernel, as does anything the tensor map cannot describe
+                const long long elems = (long long)a->batch * a->dim * a->seqlen;
+                err = cudaErrorNotSupported;
+                if (a->initial_state == nullptr && a->seqlen >= 16 && elems >= (1LL << 20) && tma_available())
+                    err = launch_prefill_tma(*a, s);
+                if (err == cudaErrorNotSupported) err = launch_prefill_channel_last(*a, s);
+            } else if (tm) {
                 err = launch_prefill_time_major(*a, s);
-            else
+            } else {
                 err = launch_prefill_generic(*a, s);
+            }
             break;
     }
     return (int)err;
@@ -224,5 +231,7 @@ VC1D_API const char* vc1d_status_string(int status) {
 VC1D_API uint64_t vc1d_launch_count(void) { return vc1d::g_launches.load(std::memory_order_relaxed); }
 
 VC1D_API const char* vc1d_last_kernel(void) { return vc1d::t_last_kernel; }
+
+VC1D_API unsigned int vc1d_tma_timeouts(void) { return vc1d::tma_timeouts(); }
 
 }  // extern "C"

@@ -25,6 +25,8 @@ cudaError_t launch_prefill_channel_last(const vc1d_prefill_args& a, cudaStream_t
 // with cp.async.bulk.tensor.
 cudaError_t launch_prefill_tma(const vc1d_prefill_args& a, cudaStream_t s);
 bool tma_available();
+// mbarrier waits that expired inside the TMA kernel since the process started (synchronising read).
+unsigned int tma_timeouts();
 
 // Time-major prefill: x/y have time stride 1, seqlen % vec == 0, aligned rows, none of
 // mask / residual / initial_state / final_state.
