@@ -116,6 +116,15 @@ typedef struct vc1d_prefill_args {
     int32_t rows_per_thread;
     int32_t block_threads;
     int32_t unroll;         /* rows a thread loads before computing: 0 auto, 4 or 8 */
+    /* tuning of the TMA-staged kernel: 0 = automatic */
+    int32_t tma_stages;          /* ring depth, 2..8 */
+    int32_t tma_ctas_per_sm;     /* persistent CTAs per SM */
+    int32_t tma_slab_bytes;      /* channel slab of a tile: 128 or 256 bytes */
+    int32_t tma_rows_per_thread; /* 2, 4 or 8 consecutive rows per thread and tile */
+    int32_t tma_vec_bytes;       /* bytes of channels per thread: 8 or 16 */
+    int32_t tma_direct_store;    /* 1: streaming stores from registers instead of bulk tensor stores */
+    int32_t tma_debug_copy;      /* 1: skip the arithmetic and store tiles as loaded (bandwidth probe) */
+    int32_t reserved;
 } vc1d_prefill_args;
 
 VC1D_API int vc1d_prefill(const vc1d_prefill_args* args, void* stream);

@@ -25,6 +25,9 @@ SOURCES = [
     "prefill_time_major.cu",
     "prefill_generic.cu",
     "prefill_tma.cu",
+    "prefill_tma_f32.cu",
+    "prefill_tma_bf16.cu",
+    "prefill_tma_f16.cu",
     "update.cu",
 ]
 

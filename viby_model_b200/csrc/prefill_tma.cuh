@@ -1,0 +1,765 @@
+// TMA-staged prefill kernel for the channel-last layout (reference call site
+// model/model.py:459-466; fused mask / residual / final state: model/model.py:454-457,
+// 491, 470-489).  Device code and the templated launcher; prefill_tma_<dtype>.cu instantiate it
+// per element type, prefill_tma.cu holds the tensor-map encoder and the dispatch.
+//
+// Geometry.  A tile is kTileRows time rows x one 128- or 256-byte slab of channels of one
+// sequence.  Its input box, (kTileRows + W-1) rows starting W-1 rows ABOVE the tile, arrives in
+// shared memory by one cp.async.bulk.tensor.3d load (no multicast); rows before t = 0 are
+// out of bounds for the tensor map and are zero-filled by the hardware, which is exactly the
+// causal left padding.  The grid is (channel slabs) x (persistent CTAs per slab): a CTA keeps
+// the weights of its slab in registers for its whole life and walks row tiles
+// j, j + G, j + 2G, ... of that slab, so neighbouring CTAs touch neighbouring rows and the
+// (W-1)-row halo of a tile is an L2 hit.
+//
+// Pipeline.  One producer warp and the consumer warps share a ring of kStages buffers guarded
+// by full/done mbarriers.  The producer scans the tile's mask rows (32 lanes, a few loads
+// each), stores them as floats beside the data and classifies the tile: all rows valid, mixed,
+// or nothing to read -- in the last case no bytes are requested from HBM at all.  Bytes in
+// flight are set by the ring depth, not by registers.  Each consumer thread owns VB bytes of
+// channels (8 or 16) and kRowsPerThread consecutive rows: a register sliding window over
+// shared memory, fp32x2 FMAs, fused mask / bias / SiLU / residual epilogue.  Results overwrite
+// the input rows in place and leave by one cp.async.bulk.tensor store per tile, issued by the
+// producer warp, so no consumer warp ever waits on HBM in either direction; the store also
+// clips the ragged last tile in time and in channels.
+//
+// Every mbarrier wait is bounded; on expiry the CTA records the event in a device counter
+// (read by vc1d_tma_timeouts()) and leaves its loops.
+#pragma once
+
+#include <cuda.h>
+
+#include <atomic>
+
+#include "vc1d_common.cuh"
+#include "vc1d_internal.h"
+
+namespace vc1d {
+namespace tma {
+
+constexpr int kMaxStages = 8;
+constexpr unsigned kSpinLimit = 1u << 24;
+
+enum : int { TILE_EMPTY = 0, TILE_MIXED = 1, TILE_FULL = 2 };
+
+struct TmaParams {
+    char* y;        // for direct stores
+    long long syb, syt;
+    const char* x;  // for the final-state pass
+    const char* res;
+    const void* weight;
+    const void* bias;
+    const void* mask;
+    char* fstate;
+    unsigned int* timeouts;  // device counter of expired waits
+    long long sxb, sxt;  // bytes
+    long long srb, srt;
+    long long smb, smt;  // elements
+    long long wsd, wsw;
+    int wdtype;
+    int B, D, T;
+    int n_ttile, n_rowtiles, ctas_per_slab;
+    int mask_dtype;
+    int skip;
+    int res_is_x;
+    int state_len;
+    int stages;      // ring depth (2..kMaxStages)
+    int debug_copy;  // experiment: consumers do nothing, the tile is stored as loaded
+};
+
+// ---- raw PTX wrappers -----------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the limit expired.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (unsigned i = 0; i < kSpinLimit; ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if (i > 64) __nanosleep(64);
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int c0, int c1, int c2, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(src)
+                 : "memory");
+}
+__device__ __forceinline__ float lds_f32(uint32_t a) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ int lds_s32(uint32_t a) {
+    int v;
+    asm volatile("ld.volatile.shared.s32 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ void sts_s32(uint32_t a, int v) {
+    asm volatile("st.volatile.shared.s32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sts_f32(uint32_t a, float v) {
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory");
+}
+
+// Row tile number -> (sequence, first row).  The time position is rotated by the sequence index so
+// that a CTA that walks tiles j, j+G, ... does not keep meeting the same position of every
+// sequence (with right-padded batches the late positions are the cheap, masked ones).
+__device__ __forceinline__ void decode_tile(int rt, int n_ttile, int tile_rows, int& b, int& t0) {
+    b = rt / n_ttile;
+    int tt = rt - b * n_ttile + b;
+    tt %= n_ttile;
+    t0 = tt * tile_rows;
+}
+
+// ---- a thread's slice of one row: VB bytes = NP fp32 pairs ----------------------------------------
+template <int DT, int VB>
+struct Slice {
+    static constexpr int kElems = VB / Elem<DT>::kBytes;
+    static constexpr int kPairs = kElems / 2;
+    static constexpr int kWords = VB / 4;
+
+    __device__ __forceinline__ static void lds(uint32_t a, uint32_t (&r)[kWords]) {
+        if constexpr (VB == 16)
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(r[0]), "=r"(r[1]), "=r"(r[kWords > 2 ? 2 : 0]), "=r"(r[kWords > 3 ? 3 : 0])
+                         : "r"(a));
+        else
+            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+    }
+    __device__ __forceinline__ static void sts(uint32_t a, const uint32_t (&r)[kWords]) {
+        if constexpr (VB == 16)
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(r[0]), "r"(r[1]),
+                         "r"(r[kWords > 2 ? 2 : 0]), "r"(r[kWords > 3 ? 3 : 0])
+                         : "memory");
+        else
+            asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(r[0]), "r"(r[1]) : "memory");
+    }
+    __device__ __forceinline__ static void stg(void* g, const uint32_t (&r)[kWords]) {
+        if constexpr (VB == 16)
+            asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(g), "r"(r[0]), "r"(r[1]),
+                         "r"(r[kWords > 2 ? 2 : 0]), "r"(r[kWords > 3 ? 3 : 0])
+                         : "memory");
+        else
+            asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(g), "r"(r[0]), "r"(r[1]) : "memory");
+    }
+    __device__ __forceinline__ static void unpack(const uint32_t (&r)[kWords], float2 (&f)[kPairs]) {
+        if constexpr (DT == VC1D_F32) {
+#pragma unroll
+            for (int q = 0; q < kPairs; ++q) f[q] = make_float2(__uint_as_float(r[2 * q]), __uint_as_float(r[2 * q + 1]));
+        } else if constexpr (DT == VC1D_BF16) {
+#pragma unroll
+            for (int q = 0; q < kPairs; ++q) f[q] = Pack<VC1D_BF16>::up(r[q]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < kPairs; ++q) f[q] = Pack<VC1D_F16>::up(r[q]);
+        }
+    }
+    __device__ __forceinline__ static void pack(const float2 (&f)[kPairs], uint32_t (&r)[kWords]) {
+        if constexpr (DT == VC1D_F32) {
+#pragma unroll
+            for (int q = 0; q < kPairs; ++q) {
+                r[2 * q] = __float_as_uint(f[q].x);
+                r[2 * q + 1] = __float_as_uint(f[q].y);
+            }
+        } else if constexpr (DT == VC1D_BF16) {
+#pragma unroll
+            for (int q = 0; q < kPairs; ++q) r[q] = Pack<VC1D_BF16>::down(f[q]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < kPairs; ++q) r[q] = Pack<VC1D_F16>::down(f[q]);
+        }
+    }
+    __device__ __forceinline__ static float2 round_trip(float2 f) { return Pack<DT>::round_trip(f); }
+};
+
+template <int DT, int W, int SLAB_BYTES, int VB, int RPT>
+struct Geometry {
+    static constexpr int kH = W - 1;
+    static constexpr int kRows = RPT;  // consecutive rows one thread computes per tile
+    static constexpr int kLanesPerRow = SLAB_BYTES / VB;
+    static constexpr int kConsumerWarps = (VB == 16) ? 4 : 8;
+    static constexpr int kConsumerThreads = kConsumerWarps * 32;
+    static constexpr int kThreads = kConsumerThreads + 32;
+    static constexpr int kGroups = kConsumerThreads / kLanesPerRow;  // row groups per tile
+    static constexpr int kTileRows = kGroups * RPT;
+    static constexpr int kBoxRows = kTileRows + kH;
+    static constexpr int kRowBytes = SLAB_BYTES;
+    static constexpr int kSlabElems = SLAB_BYTES / Elem<DT>::kBytes;
+    static constexpr int kStageBytes = ((kBoxRows * kRowBytes + 127) / 128) * 128;
+    static constexpr int kMaskFloats = ((kBoxRows + 31) / 32) * 32;
+    // layout for S stages: stages | mask floats | full[S], done[S] | {class, b, t0}[S], abort, producer-abort
+    __host__ __device__ static constexpr int off_mask(int S) { return S * kStageBytes; }
+    __host__ __device__ static constexpr int off_bars(int S) { return off_mask(S) + S * kMaskFloats * 4; }
+    __host__ __device__ static constexpr int off_flags(int S) { return off_bars(S) + 2 * S * 8; }
+    __host__ __device__ static constexpr int smem_bytes(int S) {
+        return off_flags(S) + (3 * S + 2) * 4 + 128 /* base alignment slack */;
+    }
+};
+
+// Weights and bias of this thread's channels as fp32 pairs; zeros for channels past dim.
+template <int DT, int W, int VB>
+__device__ __forceinline__ void load_weights(const TmaParams& p, int d0, bool in_range,
+                                             float2 (&wp)[W][Slice<DT, VB>::kPairs],
+                                             float2 (&bp)[Slice<DT, VB>::kPairs]) {
+    using E = Elem<DT>;
+    using T = typename E::type;
+    constexpr int NE = Slice<DT, VB>::kElems;
+    constexpr int NP = Slice<DT, VB>::kPairs;
+    float wf[NE][W];
+    float bf[NE];
+#pragma unroll
+    for (int c = 0; c < NE; ++c) {
+        bf[c] = 0.f;
+#pragma unroll
+        for (int w = 0; w < W; ++w) wf[c][w] = 0.f;
+    }
+    if (in_range) {
+#pragma unroll
+        for (int c = 0; c < NE; ++c) {
+#pragma unroll
+            for (int w = 0; w < W; ++w) {
+                const long long idx = (long long)(d0 + c) * p.wsd + (long long)w * p.wsw;
+                wf[c][w] = (p.wdtype == VC1D_F32) ? __ldg(reinterpret_cast<const float*>(p.weight) + idx)
+                                                  : E::to_float(__ldg(reinterpret_cast<const T*>(p.weight) + idx));
+            }
+            if (p.bias != nullptr) {
+                bf[c] = (p.wdtype == VC1D_F32) ? __ldg(reinterpret_cast<const float*>(p.bias) + d0 + c)
+                                               : E::to_float(__ldg(reinterpret_cast<const T*>(p.bias) + d0 + c));
+            }
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < NP; ++q) {
+#pragma unroll
+        for (int w = 0; w < W; ++w) wp[w][q] = make_float2(wf[2 * q][w], wf[2 * q + 1][w]);
+        bp[q] = make_float2(bf[2 * q], bf[2 * q + 1]);
+    }
+}
+
+// One staged row -> fp32 pairs with the reference's multiplicative mask (x * mask rounded to the
+// I/O dtype); with skip_masked_loads a zero mask makes the row +0 whatever it holds.
+template <int DT, int VB>
+__device__ __forceinline__ void apply_mask(float2 (&f)[Slice<DT, VB>::kPairs], float mk, int skip) {
+    constexpr int NP = Slice<DT, VB>::kPairs;
+    if (mk != 1.0f) {
+        if (mk == 0.0f && skip) {
+#pragma unroll
+            for (int q = 0; q < NP; ++q) f[q] = make_float2(0.f, 0.f);
+        } else {
+            const float2 m2 = make_float2(mk, mk);
+#pragma unroll
+            for (int q = 0; q < NP; ++q) f[q] = Slice<DT, VB>::round_trip(mul2(f[q], m2));
+        }
+    }
+}
+
+// The R rows of one thread in one tile.  GENERAL adds the per-row mask and the residual.  Results
+// go back into the stage (DIRECT = false, a bulk tensor store follows) or straight to global memory
+// with streaming stores (DIRECT = true; yrow is the address of the thread's first output row).
+template <int DT, int W, int VB, int RPT, bool ACT, bool GENERAL, bool DIRECT, int ROW_BYTES>
+__device__ __forceinline__ void process_rows(uint32_t trow, uint32_t mk_addr, const TmaParams& p, bool mixed,
+                                             const char* rb, char* yrow, int tfirst, bool store_ok,
+                                             float2 (&hist)[W - 1 > 0 ? W - 1 : 1][Slice<DT, VB>::kPairs],
+                                             const float2 (&wp)[W][Slice<DT, VB>::kPairs],
+                                             const float2 (&bp)[Slice<DT, VB>::kPairs]) {
+    using S = Slice<DT, VB>;
+    using E = Elem<DT>;
+    constexpr int NP = S::kPairs;
+    constexpr int NW = S::kWords;
+    constexpr int H = W - 1;
+    constexpr int R = RPT;
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+        const uint32_t slot = trow + (H + k) * ROW_BYTES;
+        uint32_t raw[NW];
+        S::lds(slot, raw);
+        float2 cur[NP];
+        S::unpack(raw, cur);
+        if (GENERAL) {
+            if (mixed) apply_mask<DT, VB>(cur, lds_f32(mk_addr + (H + k) * 4), p.skip);
+        }
+        float2 acc[NP];
+#pragma unroll
+        for (int q = 0; q < NP; ++q) {
+            acc[q] = bp[q];
+#pragma unroll
+            for (int w = 0; w < H; ++w) acc[q] = fma2(wp[w][q], hist[w][q], acc[q]);
+            acc[q] = fma2(wp[H][q], cur[q], acc[q]);
+            if (ACT) acc[q] = silu2<E::kPreciseSilu>(acc[q]);
+        }
+        if (GENERAL) {
+            if (p.res != nullptr) {
+                float2 rr[NP];
+                if (p.res_is_x) {
+                    S::unpack(raw, rr);  // the unmasked input, already on chip
+                } else {
+                    uint32_t rv[NW];
+#pragma unroll
+                    for (int i = 0; i < NW; ++i) rv[i] = 0u;
+                    const int t = tfirst + k;
+                    if (rb != nullptr && t < p.T) {
+                        const uint32_t* src = reinterpret_cast<const uint32_t*>(rb + (long long)t * p.srt);
+#pragma unroll
+                        for (int i = 0; i < NW; ++i) rv[i] = __ldg(src + i);
+                    }
+                    S::unpack(rv, rr);
+                }
+#pragma unroll
+                for (int q = 0; q < NP; ++q) acc[q] = add2(S::round_trip(acc[q]), rr[q]);
+            }
+        }
+        uint32_t outw[NW];
+        S::pack(acc, outw);
+        if (DIRECT) {
+            if (store_ok && tfirst + k < p.T) S::stg(yrow + (long long)k * p.syt, outw);
+        } else {
+            S::sts(slot, outw);
+        }
+#pragma unroll
+        for (int w = 0; w + 1 < H; ++w) {
+#pragma unroll
+            for (int q = 0; q < NP; ++q) hist[w][q] = hist[w + 1][q];
+        }
+        if (H > 0) {
+#pragma unroll
+            for (int q = 0; q < NP; ++q) hist[H - 1][q] = cur[q];
+        }
+    }
+}
+
+// Mask values of one tile's box rows, kBoxRows spread over the 32 lanes of the producer warp.
+template <int NMK, int BOX_ROWS, int H, int TILE_ROWS>
+__device__ __forceinline__ void fetch_mask(const TmaParams& p, int rt, int lane, float (&mk)[NMK]) {
+    int b, t0;
+    decode_tile(rt, p.n_ttile, TILE_ROWS, b, t0);
+#pragma unroll
+    for (int q = 0; q < NMK; ++q) {
+        const int jrow = lane + 32 * q;
+        const int t = t0 - H + jrow;
+        float v = 1.0f;                        // rows before t = 0 are zero-filled data: any multiplier works
+        if (jrow < BOX_ROWS) {
+            if (t >= p.T) v = 0.0f;            // rows past the end are never stored
+            else if (t >= 0) v = load_mask(p.mask, (long long)b * p.smb + (long long)t * p.smt, p.mask_dtype);
+        }
+        mk[q] = v;
+    }
+}
+
+template <int DT, int W, int SLAB_BYTES, int VB, int RPT, bool ACT, bool DIRECT>
+__global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads)
+    k_prefill_tma(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
+                  const TmaParams p) {
+    using E = Elem<DT>;
+    using S = Slice<DT, VB>;
+    using G = Geometry<DT, W, SLAB_BYTES, VB, RPT>;
+    constexpr int NE = S::kElems;
+    constexpr int NP = S::kPairs;
+    constexpr int NW = S::kWords;
+    constexpr int H = G::kH;
+    constexpr int R = RPT;
+    constexpr int LPR = G::kLanesPerRow;
+    constexpr int NMK = (G::kBoxRows + 31) / 32;
+
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
+    const int kStages = p.stages;  // ring depth of this launch
+    const uint32_t mask_base = base + G::off_mask(kStages);
+    const uint32_t bars = base + G::off_bars(kStages);    // full[s] at bars + 8 s, done[s] at bars + 8 (kStages + s)
+    const uint32_t flags = base + G::off_flags(kStages);  // per stage {class, sequence, first row}; then abort, producer-abort
+    const uint32_t abort_c = flags + 12 * kStages;
+    const uint32_t abort_p = abort_c + 4;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int slab = blockIdx.x;
+    const int j0 = blockIdx.y;
+    const int stride = p.ctas_per_slab;
+    const int slab_ch0 = slab * G::kSlabElems;
+    const int n_my = (j0 < p.n_rowtiles) ? (p.n_rowtiles - j0 + stride - 1) / stride : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(bars + 8 * s, 1);                              // full: the producer's arrive (+ tx bytes)
+            mbar_init(bars + 8 * (kStages + s), G::kConsumerWarps);  // done: one arrive per consumer warp
+        }
+        sts_s32(abort_c, 0);  // a consumer wait expired
+        sts_s32(abort_p, 0);  // a producer wait expired
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == G::kConsumerWarps) {
+        // ================================ producer warp ==================================
+        // Iteration i issues the load of tile i.  With bulk stores it then waits for the consumers
+        // of tile i-(S-1) and issues that tile's store; the stage of tile i held tile i-S, whose
+        // store was issued in the previous iteration and is the newest bulk group, so
+        // wait_group.read 0 frees the stage.  With direct stores the stage is free as soon as the
+        // consumers of tile i-S have arrived on done[s].  The mask of tile i+1 is fetched while
+        // tile i is being handled, so its latency never sits between two loads.
+        float mk_cur[NMK];
+#pragma unroll
+        for (int q = 0; q < NMK; ++q) mk_cur[q] = 1.0f;
+        if (p.mask != nullptr && n_my > 0) fetch_mask<NMK, G::kBoxRows, H, G::kTileRows>(p, j0, lane, mk_cur);
+        bool live = true;
+        const int n_iter = DIRECT ? n_my : n_my + kStages - 1;
+        for (int i = 0; live && i < n_iter; ++i) {
+            if (i < n_my) {
+                const int s = i % kStages;
+                float mk_next[NMK];
+#pragma unroll
+                for (int q = 0; q < NMK; ++q) mk_next[q] = 1.0f;
+                if (p.mask != nullptr && i + 1 < n_my)
+                    fetch_mask<NMK, G::kBoxRows, H, G::kTileRows>(p, j0 + (i + 1) * stride, lane, mk_next);
+                if (i >= kStages) {
+                    if (DIRECT) {
+                        if (!mbar_wait(bars + 8 * (kStages + s), ((i / kStages) & 1) ^ 1)) {
+                            if (lane == 0) {
+                                atomicAdd(p.timeouts, 1u);
+                                sts_s32(abort_p, 1);
+                            }
+                            live = false;
+                        }
+                    } else if (lane == 0) {
+                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    }
+                    __syncwarp();
+                }
+                if (live) {
+                    int b, t0;
+                    decode_tile(j0 + i * stride, p.n_ttile, G::kTileRows, b, t0);
+                    int cls = TILE_FULL;
+                    if (p.mask != nullptr) {
+                        bool any = false, all_one = true;
+#pragma unroll
+                        for (int q = 0; q < NMK; ++q) {
+                            const int jrow = lane + 32 * q;
+                            const int t = t0 - H + jrow;
+                            if (jrow < G::kBoxRows) {
+                                sts_f32(mask_base + (s * G::kMaskFloats + jrow) * 4, mk_cur[q]);
+                                if (t >= 0 && t < p.T) {
+                                    any |= (mk_cur[q] != 0.0f);
+                                    all_one &= (mk_cur[q] == 1.0f);
+                                }
+                            }
+                        }
+                        any = __any_sync(0xffffffffu, any);
+                        all_one = __all_sync(0xffffffffu, all_one);
+                        cls = all_one ? TILE_FULL : ((any || !p.skip || p.res != nullptr) ? TILE_MIXED : TILE_EMPTY);
+                        __syncwarp();
+                    }
+                    if (lane == 0) {
+                        sts_s32(flags + 12 * s, cls);
+                        sts_s32(flags + 12 * s + 4, b);
+                        sts_s32(flags + 12 * s + 8, t0);
+                        const uint32_t full = bars + 8 * s;
+                        if (cls != TILE_EMPTY) {
+                            mbar_arrive_expect_tx(full, G::kBoxRows * G::kRowBytes);
+                            tma_load_3d(base + s * G::kStageBytes, &tmap_x, slab_ch0, t0 - H, b, full);
+                        } else {
+                            mbar_arrive(full);
+                        }
+                    }
+                    __syncwarp();
+                }
+#pragma unroll
+                for (int q = 0; q < NMK; ++q) mk_cur[q] = mk_next[q];
+            }
+            if (!DIRECT) {
+                const int j = i - (kStages - 1);
+                if (live && j >= 0 && j < n_my) {
+                    const int s = j % kStages;
+                    if (!mbar_wait(bars + 8 * (kStages + s), (j / kStages) & 1)) {
+                        // recorded only: the consumers decide among themselves when to stop (they share a barrier)
+                        if (lane == 0) {
+                            atomicAdd(p.timeouts, 1u);
+                            sts_s32(abort_p, 1);
+                        }
+                        live = false;
+                    } else if (lds_s32(abort_c)) {
+                        live = false;
+                    } else if (lane == 0) {
+                        int b, t0;
+                        decode_tile(j0 + j * stride, p.n_ttile, G::kTileRows, b, t0);
+                        // output row t sits in box row t - t0 + H: the store starts H rows into the stage
+                        tma_store_3d(&tmap_y, slab_ch0, t0, b, base + s * G::kStageBytes + H * G::kRowBytes);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+        if (!DIRECT && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    } else {
+        // ================================ consumer warps =================================
+        const int grp = threadIdx.x / LPR;  // row group inside the tile
+        const int cl = threadIdx.x % LPR;   // channel slice inside the slab
+        const int d0 = slab_ch0 + cl * NE;
+        const bool ch_ok = d0 < p.D;  // dim is a multiple of the 128-bit vector: a slice is in or out as a whole
+        const int rbase = grp * R;
+
+        float2 wp[W][NP];
+        float2 bp[NP];
+        load_weights<DT, W, VB>(p, d0, ch_ok, wp, bp);
+        // value of a row whose W taps are all masked: act(bias)
+        uint32_t const_row[NW];
+        {
+            float2 c[NP];
+#pragma unroll
+            for (int q = 0; q < NP; ++q) c[q] = ACT ? silu2<E::kPreciseSilu>(bp[q]) : bp[q];
+            S::pack(c, const_row);
+        }
+        const bool general_kernel = (p.mask != nullptr) || (p.res != nullptr);
+
+        for (int i = 0; i < n_my; ++i) {
+            const int s = i % kStages;
+            const bool ok = mbar_wait(bars + 8 * s, (i / kStages) & 1);
+            if (!ok) {
+                if (lane == 0) {
+                    atomicAdd(p.timeouts, 1u);
+                    sts_s32(abort_c, 1);
+                }
+                if (DIRECT) break;  // no barrier is shared with the other warps: each leaves on its own
+            }
+            // box row of time t is (t - t0 + H); this thread reads box rows rbase .. rbase+R+H-1 and,
+            // with bulk stores, writes its R results over box rows rbase+H .. rbase+R+H-1
+            const uint32_t trow = base + s * G::kStageBytes + rbase * G::kRowBytes + cl * VB;
+            const uint32_t mk_addr = mask_base + (s * G::kMaskFloats + rbase) * 4;
+            int cls = TILE_FULL;
+            if (general_kernel) cls = lds_s32(flags + 12 * s);
+            const bool mixed = (cls == TILE_MIXED);
+            const bool need_pos = DIRECT || (p.res != nullptr && !p.res_is_x);
+            int b = 0, tfirst = 0;
+            if (need_pos) {
+                b = lds_s32(flags + 12 * s + 4);
+                tfirst = lds_s32(flags + 12 * s + 8) + rbase;
+            }
+
+            if (p.debug_copy) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bars + 8 * (kStages + s));
+                continue;
+            }
+            float2 hist[H > 0 ? H : 1][NP];
+            if (cls != TILE_EMPTY) {
+#pragma unroll
+                for (int w = 0; w < H; ++w) {
+                    uint32_t raw[NW];
+                    S::lds(trow + w * G::kRowBytes, raw);
+                    S::unpack(raw, hist[w]);
+                    if (mixed) apply_mask<DT, VB>(hist[w], lds_f32(mk_addr + w * 4), p.skip);
+                }
+            }
+            if (!DIRECT) {
+                // The first H rows a group reads are the last rows the group above it overwrites:
+                // nobody writes until everybody holds its history.  The same barrier makes an expired
+                // wait a collective decision, so no warp is left alone at it.
+                asm volatile("bar.sync 1, %0;" ::"n"(G::kConsumerThreads) : "memory");
+                if (lds_s32(abort_c)) break;
+            }
+            char* yrow = nullptr;
+            if (DIRECT) yrow = p.y + (long long)b * p.syb + (long long)tfirst * p.syt + (long long)d0 * E::kBytes;
+            const char* rb = nullptr;
+            if (p.res != nullptr && !p.res_is_x && ch_ok)
+                rb = p.res + (long long)b * p.srb + (long long)d0 * E::kBytes;
+
+            if (cls == TILE_EMPTY) {
+#pragma unroll
+                for (int k = 0; k < R; ++k) {
+                    if (DIRECT) {
+                        if (ch_ok && tfirst + k < p.T) S::stg(yrow + (long long)k * p.syt, const_row);
+                    } else {
+                        S::sts(trow + (H + k) * G::kRowBytes, const_row);
+                    }
+                }
+            } else if (cls == TILE_FULL && p.res == nullptr) {
+                process_rows<DT, W, VB, RPT, ACT, false, DIRECT, G::kRowBytes>(trow, mk_addr, p, false, nullptr, yrow, tfirst,
+                                                                          ch_ok, hist, wp, bp);
+            } else {
+                process_rows<DT, W, VB, RPT, ACT, true, DIRECT, G::kRowBytes>(trow, mk_addr, p, mixed, rb, yrow, tfirst,
+                                                                         ch_ok, hist, wp, bp);
+            }
+            // bulk stores read the results through the async proxy; they were written through the generic one
+            if (!DIRECT) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bars + 8 * (kStages + s));
+        }
+
+        // ---- final state: right-aligned last state_len masked inputs (model/model.py:470-489) ----
+        if (p.fstate != nullptr && threadIdx.x < LPR && ch_ok) {
+            using T = typename E::type;
+            const int L = p.state_len;
+            for (int b = j0; b < p.B; b += stride) {
+                const T* xb = reinterpret_cast<const T*>(p.x + (long long)b * p.sxb) + d0;
+                T* out = reinterpret_cast<T*>(p.fstate) + ((long long)b * p.D + d0) * L;
+                for (int jc = 0; jc < L; ++jc) {
+                    const int t = p.T - L + jc;
+                    float mkv = 1.0f;
+                    if (t >= 0 && p.mask != nullptr)
+                        mkv = load_mask(p.mask, (long long)b * p.smb + (long long)t * p.smt, p.mask_dtype);
+#pragma unroll
+                    for (int c = 0; c < NE; ++c) {
+                        T v = E::from_float(0.f);
+                        if (t >= 0) {
+                            v = xb[(long long)t * (p.sxt / E::kBytes) + c];
+                            if (mkv != 1.0f) v = E::from_float(E::to_float(v) * mkv);
+                        }
+                        out[(long long)c * L + jc] = v;
+                    }
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encode_fn();
+
+template <int DT, int W, int SLAB_BYTES, int VB, int RPT, bool ACT, bool DIRECT>
+cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cudaStream_t s) {
+    using G = Geometry<DT, W, SLAB_BYTES, VB, RPT>;
+    const int eb = Elem<DT>::kBytes;
+    TmaParams p = base;
+    const int slab_ch = G::kSlabElems;
+    const int n_slab = (a.dim + slab_ch - 1) / slab_ch;
+    p.n_ttile = (a.seqlen + G::kTileRows - 1) / G::kTileRows;
+    const long long n_rowtiles = (long long)a.batch * p.n_ttile;
+    if (n_rowtiles > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    p.n_rowtiles = (int)n_rowtiles;
+
+    EncodeFn enc = encode_fn();
+    if (enc == nullptr) return cudaErrorNotSupported;
+    const CUtensorMapDataType dt = (DT == VC1D_F32)    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                   : (DT == VC1D_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                       : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const cuuint64_t dims[3] = {(cuuint64_t)a.dim, (cuuint64_t)a.seqlen, (cuuint64_t)a.batch};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    // input box: tile rows plus the W-1 rows above; output box: the tile rows
+    CUtensorMap tmap_x, tmap_y;
+    {
+        cuuint64_t st[2] = {(cuuint64_t)a.x_stride_t * eb, (cuuint64_t)a.x_stride_b * eb};
+        // an extent of 1 makes its stride irrelevant, but the encoder still wants a legal value
+        if (a.seqlen == 1) st[0] = (cuuint64_t)a.dim * eb;
+        if (a.batch == 1) st[1] = st[0] * (cuuint64_t)a.seqlen;
+        if (st[0] % 16 != 0 || st[1] % 16 != 0) return cudaErrorNotSupported;
+        const cuuint32_t box[3] = {(cuuint32_t)slab_ch, (cuuint32_t)G::kBoxRows, 1u};
+        const CUresult r = enc(&tmap_x, dt, 3, const_cast<void*>(a.x), dims, st, box, estr,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorNotSupported;  // the caller falls back to the direct kernel
+    }
+    {
+        cuuint64_t st[2] = {(cuuint64_t)a.y_stride_t * eb, (cuuint64_t)a.y_stride_b * eb};
+        if (a.seqlen == 1) st[0] = (cuuint64_t)a.dim * eb;
+        if (a.batch == 1) st[1] = st[0] * (cuuint64_t)a.seqlen;
+        if (st[0] % 16 != 0 || st[1] % 16 != 0) return cudaErrorNotSupported;
+        const cuuint32_t box[3] = {(cuuint32_t)slab_ch, (cuuint32_t)G::kTileRows, 1u};
+        const CUresult r = enc(&tmap_y, dt, 3, a.y, dims, st, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return cudaErrorNotSupported;
+    }
+    int stages = a.tma_stages > 0 ? a.tma_stages : 3;
+    if (stages < 2) stages = 2;
+    if (stages > kMaxStages) stages = kMaxStages;
+    int per_sm = (a.tma_ctas_per_sm > 0 && a.tma_ctas_per_sm <= 32) ? a.tma_ctas_per_sm : 3;
+    while (stages > 2 && G::smem_bytes(stages) > 200 * 1024) --stages;
+    p.stages = stages;
+    const int smem = G::smem_bytes(stages);
+    {
+        // opt in to > 48 KB of dynamic shared memory; the attribute is per device and sticky, so
+        // remember the largest value set so far
+        static std::atomic<int> granted[64];
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev < 0 || dev >= 64 || granted[dev].load(std::memory_order_acquire) < smem) {
+            const cudaError_t e = cudaFuncSetAttribute(k_prefill_tma<DT, W, SLAB_BYTES, VB, RPT, ACT, DIRECT>,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (e != cudaSuccess) return e;
+            if (dev >= 0 && dev < 64) granted[dev].store(smem, std::memory_order_release);
+        }
+    }
+    // persistent CTAs, split evenly over the channel slabs
+    long long g = ((long long)sm_count() * per_sm) / n_slab;
+    if (g < 1) g = 1;
+    if (g > n_rowtiles) g = n_rowtiles;
+    if (g > 65535) g = 65535;
+    p.ctas_per_slab = (int)g;
+    const dim3 grid((unsigned)n_slab, (unsigned)g);
+    note_launch("tma");
+    k_prefill_tma<DT, W, SLAB_BYTES, VB, RPT, ACT, DIRECT><<<grid, G::kThreads, smem, s>>>(tmap_x, tmap_y, p);
+    return cudaGetLastError();
+}
+
+template <int DT, int W, int SLAB_BYTES, int VB, int RPT>
+cudaError_t launch_store(const vc1d_prefill_args& a, const TmaParams& p, cudaStream_t s) {
+    const bool act = a.activation == VC1D_ACT_SILU;
+    if (a.tma_direct_store)
+        return act ? launch_kernel<DT, W, SLAB_BYTES, VB, RPT, true, true>(a, p, s)
+                   : launch_kernel<DT, W, SLAB_BYTES, VB, RPT, false, true>(a, p, s);
+    return act ? launch_kernel<DT, W, SLAB_BYTES, VB, RPT, true, false>(a, p, s)
+               : launch_kernel<DT, W, SLAB_BYTES, VB, RPT, false, false>(a, p, s);
+}
+
+template <int DT, int W, int SLAB_BYTES>
+cudaError_t launch_slab(const vc1d_prefill_args& a, const TmaParams& p, cudaStream_t s) {
+    // 8 bytes of channels and 8 rows per thread by default; the other shapes exist for tuning
+    if (a.tma_vec_bytes == 16) return launch_store<DT, W, SLAB_BYTES, 16, 8>(a, p, s);
+    if (a.tma_rows_per_thread == 4) return launch_store<DT, W, SLAB_BYTES, 8, 4>(a, p, s);
+    if (a.tma_rows_per_thread == 2) return launch_store<DT, W, SLAB_BYTES, 8, 2>(a, p, s);
+    return launch_store<DT, W, SLAB_BYTES, 8, 8>(a, p, s);
+}
+
+template <int DT, int W>
+cudaError_t launch_w(const vc1d_prefill_args& a, const TmaParams& p, cudaStream_t s) {
+    // 256-byte slabs when dim fills them; 128-byte slabs when that avoids idle lanes
+    const int eb = Elem<DT>::kBytes;
+    const int wide = 256 / eb, narrow = 128 / eb;
+    bool use_wide = (a.dim % wide == 0) || (a.dim % narrow != 0);
+    if (a.tma_slab_bytes == 128) use_wide = false;
+    if (a.tma_slab_bytes == 256) use_wide = true;
+    return use_wide ? launch_slab<DT, W, 256>(a, p, s) : launch_slab<DT, W, 128>(a, p, s);
+}
+
+template <int DT>
+cudaError_t launch_dt(const vc1d_prefill_args& a, const TmaParams& p, cudaStream_t s) {
+    switch (a.width) {
+        case 2: return launch_w<DT, 2>(a, p, s);
+        case 3: return launch_w<DT, 3>(a, p, s);
+        default: return launch_w<DT, 4>(a, p, s);
+    }
+}
+
+}  // namespace tma
+}  // namespace vc1d

@@ -71,23 +71,39 @@ __device__ __forceinline__ void st_vec(void* p, const uint4& v) {
 // ---------------------------------------------------------------------------------------
 // Packed fp32x2 arithmetic (sm_100 issues one instruction for two fp32 lanes).
 // ---------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned long long f2_bits(float2 v) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(v.x), "f"(v.y));
+    return r;
+}
+__device__ __forceinline__ float2 bits_f2(unsigned long long r) {
+    float2 v;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(v.x), "=f"(v.y) : "l"(r));
+    return v;
+}
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
 #if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ >= 1000)
-    return __ffma2_rn(a, b, c);
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(f2_bits(a)), "l"(f2_bits(b)), "l"(f2_bits(c)));
+    return bits_f2(d);
 #else
     return make_float2(fmaf(a.x, b.x, c.x), fmaf(a.y, b.y, c.y));
 #endif
 }
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) {
 #if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ >= 1000)
-    return __fmul2_rn(a, b);
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(f2_bits(a)), "l"(f2_bits(b)));
+    return bits_f2(d);
 #else
     return make_float2(a.x * b.x, a.y * b.y);
 #endif
 }
 __device__ __forceinline__ float2 add2(float2 a, float2 b) {
 #if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ >= 1000)
-    return __fadd2_rn(a, b);
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(f2_bits(a)), "l"(f2_bits(b)));
+    return bits_f2(d);
 #else
     return make_float2(a.x + b.x, a.y + b.y);
 #endif

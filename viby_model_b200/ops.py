@@ -30,6 +30,9 @@ _MASK_DTYPES = {
 }
 
 
+_TMA_TUNING = {"stages", "ctas_per_sm", "slab_bytes", "rows_per_thread", "vec_bytes", "direct_store", "debug_copy"}
+
+
 def _activation_code(activation) -> int:
     # reference: autograd.py:527-530 accepts None, "silu", "swish"; the BTD API passes a bool
     if activation is None or activation is False:
@@ -98,6 +101,7 @@ def causal_conv1d_fn(
     rows_per_thread: int = 0,
     block_threads: int = 0,
     unroll: int = 0,
+    tma: Optional[dict] = None,
 ) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
     """Depthwise causal conv1d over ``x[batch, dim, seqlen]`` (prefill).
 
@@ -123,7 +127,9 @@ def causal_conv1d_fn(
       residual: a tensor shaped like ``x`` (or True for ``x`` itself) added after the activation,
         with the same two roundings as ``x + y`` (model/model.py:491).
       state_len: width of the returned final state (CanonLayer keeps ``kernel_size`` columns).
-      out: preallocated output; kernel / rows_per_thread / block_threads / unroll: tuning overrides.
+      out: preallocated output; kernel / rows_per_thread / block_threads / unroll: tuning overrides;
+      tma: dict of tuning overrides of the TMA-staged kernel (stages, ctas_per_sm, slab_bytes,
+        rows_per_thread, vec_bytes, direct_store).
     """
     if x.dim() != 3:
         raise ValueError(f"Expected 3D input tensor (batch, dim, seqlen), got {x.dim()}D")
@@ -219,6 +225,11 @@ def causal_conv1d_fn(
     a.rows_per_thread = int(rows_per_thread)
     a.block_threads = int(block_threads)
     a.unroll = int(unroll)
+    if tma:
+        for key, value in tma.items():
+            if key not in _TMA_TUNING:
+                raise ValueError(f"unknown TMA tuning key {key!r}; expected one of {sorted(_TMA_TUNING)}")
+            setattr(a, "tma_" + key, int(value))
 
     if x.device.index != torch.cuda.current_device():
         with torch.cuda.device(x.device):
