@@ -3,6 +3,9 @@
 Public surface:
   causal_conv1d_fn, causal_conv1d_update  -- the CUDA slot of the reference's CanonLayer
                                              (model/model.py:20-30, 305-311, 460-466)
+  causal_conv1d_fwd, short_conv_fused,
+  short_conv_update                       -- the [B,T,D] operators of causal-conv1d-mps
+                                             (causal_conv1d_mps/__init__.py:81-419)
   launch_count, last_kernel               -- proof that the CUDA kernels ran
 
 The operators call hand-written CUDA kernels through the C ABI of include/vc1d.h
@@ -11,10 +14,14 @@ that library raises ImportError: there is no CPU or PyTorch fallback.
 """
 from ._cabi import last_kernel, launch_count, library_path, tma_timeouts
 from .ops import causal_conv1d_fn, causal_conv1d_update
+from .short_conv import causal_conv1d_fwd, short_conv_fused, short_conv_update
 
 __all__ = [
     "causal_conv1d_fn",
     "causal_conv1d_update",
+    "causal_conv1d_fwd",
+    "short_conv_fused",
+    "short_conv_update",
     "launch_count",
     "last_kernel",
     "library_path",

@@ -30,6 +30,7 @@
 #include <cuda.h>
 
 #include <atomic>
+#include <type_traits>
 
 #include "vc1d_common.cuh"
 #include "vc1d_internal.h"
@@ -128,15 +129,47 @@ __device__ __forceinline__ void sts_f32(uint32_t a, float v) {
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory");
 }
 
-// Row tile number -> (sequence, first row).  The time position is rotated by the sequence index so
-// that a CTA that walks tiles j, j+G, ... does not keep meeting the same position of every
-// sequence (with right-padded batches the late positions are the cheap, masked ones).
-__device__ __forceinline__ void decode_tile(int rt, int n_ttile, int tile_rows, int& b, int& t0) {
-    b = rt / n_ttile;
-    int tt = rt - b * n_ttile + b;
-    tt %= n_ttile;
-    t0 = tt * tile_rows;
+template <int K, int N, class F>
+__device__ __forceinline__ void static_for(F&& f) {
+    if constexpr (K < N) {
+        f(std::integral_constant<int, K>{});
+        static_for<K + 1, N>(f);
+    }
 }
+
+// Walks the row tiles j0, j0 + G, j0 + 2G, ... of one CTA without a division per tile.  Tile
+// number rt means sequence b = rt / n_ttile and time position (rt % n_ttile + b) % n_ttile: the
+// position is rotated by the sequence index so that a CTA does not keep meeting the same position
+// of every sequence (with right-padded batches the late positions are the cheap, masked ones).
+struct TileIter {
+    int b, r, brot;        // sequence, rt % n_ttile, b % n_ttile
+    int n, sb, sr, sbrot;  // n_ttile, G / n_ttile, G % n_ttile, sb % n_ttile
+    __device__ __forceinline__ void init(int rt, int n_ttile, int stride) {
+        n = n_ttile;
+        b = rt / n;
+        r = rt - b * n;
+        brot = b % n;
+        sb = stride / n;
+        sr = stride - sb * n;
+        sbrot = sb % n;
+    }
+    __device__ __forceinline__ void next() {
+        b += sb;
+        brot += sbrot;
+        if (brot >= n) brot -= n;
+        r += sr;
+        if (r >= n) {
+            r -= n;
+            ++b;
+            if (++brot == n) brot = 0;
+        }
+    }
+    __device__ __forceinline__ int t0(int tile_rows) const {
+        int tt = r + brot;
+        if (tt >= n) tt -= n;
+        return tt * tile_rows;
+    }
+};
 
 // ---- a thread's slice of one row: VB bytes = NP fp32 pairs ----------------------------------------
 template <int DT, int VB>
@@ -285,7 +318,7 @@ __device__ __forceinline__ void apply_mask(float2 (&f)[Slice<DT, VB>::kPairs], f
 // with streaming stores (DIRECT = true; yrow is the address of the thread's first output row).
 template <int DT, int W, int VB, int RPT, bool ACT, bool GENERAL, bool DIRECT, int ROW_BYTES>
 __device__ __forceinline__ void process_rows(uint32_t trow, uint32_t mk_addr, const TmaParams& p, bool mixed,
-                                             const char* rb, char* yrow, int tfirst, bool store_ok,
+                                             const char* rb, char* yrow, int tfirst, int rows_ok,
                                              float2 (&hist)[W - 1 > 0 ? W - 1 : 1][Slice<DT, VB>::kPairs],
                                              const float2 (&wp)[W][Slice<DT, VB>::kPairs],
                                              const float2 (&bp)[Slice<DT, VB>::kPairs]) {
@@ -294,15 +327,16 @@ __device__ __forceinline__ void process_rows(uint32_t trow, uint32_t mk_addr, co
     constexpr int NP = S::kPairs;
     constexpr int NW = S::kWords;
     constexpr int H = W - 1;
-    constexpr int R = RPT;
-#pragma unroll
-    for (int k = 0; k < R; ++k) {
+    // Unrolled at the language level: every index below is a compile-time constant, and the history
+    // window rotates by index (row k overwrites slot k % H, the oldest) instead of by moving registers.
+    static_for<0, RPT>([&](auto kc) {
+        constexpr int k = decltype(kc)::value;
         const uint32_t slot = trow + (H + k) * ROW_BYTES;
         uint32_t raw[NW];
         S::lds(slot, raw);
         float2 cur[NP];
         S::unpack(raw, cur);
-        if (GENERAL) {
+        if constexpr (GENERAL) {
             if (mixed) apply_mask<DT, VB>(cur, lds_f32(mk_addr + (H + k) * 4), p.skip);
         }
         float2 acc[NP];
@@ -310,11 +344,11 @@ __device__ __forceinline__ void process_rows(uint32_t trow, uint32_t mk_addr, co
         for (int q = 0; q < NP; ++q) {
             acc[q] = bp[q];
 #pragma unroll
-            for (int w = 0; w < H; ++w) acc[q] = fma2(wp[w][q], hist[w][q], acc[q]);
+            for (int w = 0; w < H; ++w) acc[q] = fma2(wp[w][q], hist[(k + w) % (H > 0 ? H : 1)][q], acc[q]);
             acc[q] = fma2(wp[H][q], cur[q], acc[q]);
-            if (ACT) acc[q] = silu2<E::kPreciseSilu>(acc[q]);
+            if constexpr (ACT) acc[q] = silu2<E::kPreciseSilu>(acc[q]);
         }
-        if (GENERAL) {
+        if constexpr (GENERAL) {
             if (p.res != nullptr) {
                 float2 rr[NP];
                 if (p.res_is_x) {
@@ -337,28 +371,21 @@ __device__ __forceinline__ void process_rows(uint32_t trow, uint32_t mk_addr, co
         }
         uint32_t outw[NW];
         S::pack(acc, outw);
-        if (DIRECT) {
-            if (store_ok && tfirst + k < p.T) S::stg(yrow + (long long)k * p.syt, outw);
+        if constexpr (DIRECT) {
+            if (rows_ok > k) S::stg(yrow + (long long)k * p.syt, outw);
         } else {
             S::sts(slot, outw);
         }
+        if constexpr (H > 0) {
 #pragma unroll
-        for (int w = 0; w + 1 < H; ++w) {
-#pragma unroll
-            for (int q = 0; q < NP; ++q) hist[w][q] = hist[w + 1][q];
+            for (int q = 0; q < NP; ++q) hist[k % H][q] = cur[q];
         }
-        if (H > 0) {
-#pragma unroll
-            for (int q = 0; q < NP; ++q) hist[H - 1][q] = cur[q];
-        }
-    }
+    });
 }
 
 // Mask values of one tile's box rows, kBoxRows spread over the 32 lanes of the producer warp.
 template <int NMK, int BOX_ROWS, int H, int TILE_ROWS>
-__device__ __forceinline__ void fetch_mask(const TmaParams& p, int rt, int lane, float (&mk)[NMK]) {
-    int b, t0;
-    decode_tile(rt, p.n_ttile, TILE_ROWS, b, t0);
+__device__ __forceinline__ void fetch_mask(const TmaParams& p, int b, int t0, int lane, float (&mk)[NMK]) {
 #pragma unroll
     for (int q = 0; q < NMK; ++q) {
         const int jrow = lane + 32 * q;
@@ -421,99 +448,122 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         // of tile i-(S-1) and issues that tile's store; the stage of tile i held tile i-S, whose
         // store was issued in the previous iteration and is the newest bulk group, so
         // wait_group.read 0 frees the stage.  With direct stores the stage is free as soon as the
-        // consumers of tile i-S have arrived on done[s].  The mask of tile i+1 is fetched while
+        // consumers of tile i-S have arrived on done[s].  The mask of tile i+2 is fetched while
         // tile i is being handled, so its latency never sits between two loads.
-        float mk_cur[NMK];
-#pragma unroll
-        for (int q = 0; q < NMK; ++q) mk_cur[q] = 1.0f;
-        if (p.mask != nullptr && n_my > 0) fetch_mask<NMK, G::kBoxRows, H, G::kTileRows>(p, j0, lane, mk_cur);
-        bool live = true;
+        // Three mask buffers rotate roles (the loop is unrolled by three): the values fetched for
+        // tile i+2 are not touched -- not even moved -- until iteration i+2.
         const int n_iter = DIRECT ? n_my : n_my + kStages - 1;
-        for (int i = 0; live && i < n_iter; ++i) {
+        TileIter it_fetch, it_load, it_store;  // tiles i+2 (mask fetch), i (load), i-(S-1) (store)
+        it_load.init(j0, p.n_ttile, stride);
+        it_store = it_load;
+        it_fetch = it_load;
+        int s_load = 0, s_store = 0;            // ring slots of the load and of the store
+        uint32_t ph_load = 0, ph_store = 0;     // how often each has wrapped, mod 2
+        auto step = [&](int i, float (&mk_use)[NMK], float (&mk_fill)[NMK]) -> bool {
             if (i < n_my) {
-                const int s = i % kStages;
-                float mk_next[NMK];
-#pragma unroll
-                for (int q = 0; q < NMK; ++q) mk_next[q] = 1.0f;
-                if (p.mask != nullptr && i + 1 < n_my)
-                    fetch_mask<NMK, G::kBoxRows, H, G::kTileRows>(p, j0 + (i + 1) * stride, lane, mk_next);
+                const int s = s_load;
+                if (p.mask != nullptr && i + 2 < n_my) {
+                    it_fetch.next();
+                    fetch_mask<NMK, G::kBoxRows, H, G::kTileRows>(p, it_fetch.b, it_fetch.t0(G::kTileRows), lane, mk_fill);
+                }
                 if (i >= kStages) {
+                    bool ok = true;
                     if (DIRECT) {
-                        if (!mbar_wait(bars + 8 * (kStages + s), ((i / kStages) & 1) ^ 1)) {
-                            if (lane == 0) {
-                                atomicAdd(p.timeouts, 1u);
-                                sts_s32(abort_p, 1);
-                            }
-                            live = false;
+                        ok = mbar_wait(bars + 8 * (kStages + s), ph_load ^ 1);
+                        if (!ok && lane == 0) {
+                            atomicAdd(p.timeouts, 1u);
+                            sts_s32(abort_p, 1);
                         }
                     } else if (lane == 0) {
                         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                     }
                     __syncwarp();
+                    if (!ok) return false;
                 }
-                if (live) {
-                    int b, t0;
-                    decode_tile(j0 + i * stride, p.n_ttile, G::kTileRows, b, t0);
-                    int cls = TILE_FULL;
-                    if (p.mask != nullptr) {
-                        bool any = false, all_one = true;
+                const int b = it_load.b;
+                const int t0 = it_load.t0(G::kTileRows);
+                int cls = TILE_FULL;
+                if (p.mask != nullptr) {
+                    bool any = false, all_one = true;
 #pragma unroll
-                        for (int q = 0; q < NMK; ++q) {
-                            const int jrow = lane + 32 * q;
-                            const int t = t0 - H + jrow;
-                            if (jrow < G::kBoxRows) {
-                                sts_f32(mask_base + (s * G::kMaskFloats + jrow) * 4, mk_cur[q]);
-                                if (t >= 0 && t < p.T) {
-                                    any |= (mk_cur[q] != 0.0f);
-                                    all_one &= (mk_cur[q] == 1.0f);
-                                }
+                    for (int q = 0; q < NMK; ++q) {
+                        const int jrow = lane + 32 * q;
+                        const int t = t0 - H + jrow;
+                        if (jrow < G::kBoxRows) {
+                            sts_f32(mask_base + (s * G::kMaskFloats + jrow) * 4, mk_use[q]);
+                            if (t >= 0 && t < p.T) {
+                                any |= (mk_use[q] != 0.0f);
+                                all_one &= (mk_use[q] == 1.0f);
                             }
                         }
-                        any = __any_sync(0xffffffffu, any);
-                        all_one = __all_sync(0xffffffffu, all_one);
-                        cls = all_one ? TILE_FULL : ((any || !p.skip || p.res != nullptr) ? TILE_MIXED : TILE_EMPTY);
-                        __syncwarp();
                     }
-                    if (lane == 0) {
-                        sts_s32(flags + 12 * s, cls);
-                        sts_s32(flags + 12 * s + 4, b);
-                        sts_s32(flags + 12 * s + 8, t0);
-                        const uint32_t full = bars + 8 * s;
-                        if (cls != TILE_EMPTY) {
-                            mbar_arrive_expect_tx(full, G::kBoxRows * G::kRowBytes);
-                            tma_load_3d(base + s * G::kStageBytes, &tmap_x, slab_ch0, t0 - H, b, full);
-                        } else {
-                            mbar_arrive(full);
-                        }
-                    }
+                    any = __any_sync(0xffffffffu, any);
+                    all_one = __all_sync(0xffffffffu, all_one);
+                    cls = all_one ? TILE_FULL : ((any || !p.skip || p.res != nullptr) ? TILE_MIXED : TILE_EMPTY);
                     __syncwarp();
                 }
-#pragma unroll
-                for (int q = 0; q < NMK; ++q) mk_cur[q] = mk_next[q];
+                if (lane == 0) {
+                    sts_s32(flags + 12 * s, cls);
+                    sts_s32(flags + 12 * s + 4, b);
+                    sts_s32(flags + 12 * s + 8, t0);
+                    const uint32_t full = bars + 8 * s;
+                    if (cls != TILE_EMPTY) {
+                        mbar_arrive_expect_tx(full, G::kBoxRows * G::kRowBytes);
+                        tma_load_3d(base + s * G::kStageBytes, &tmap_x, slab_ch0, t0 - H, b, full);
+                    } else {
+                        mbar_arrive(full);
+                    }
+                }
+                __syncwarp();
+                it_load.next();
+                if (++s_load == kStages) {
+                    s_load = 0;
+                    ph_load ^= 1;
+                }
             }
             if (!DIRECT) {
                 const int j = i - (kStages - 1);
-                if (live && j >= 0 && j < n_my) {
-                    const int s = j % kStages;
-                    if (!mbar_wait(bars + 8 * (kStages + s), (j / kStages) & 1)) {
+                if (j >= 0 && j < n_my) {
+                    const int s = s_store;
+                    bool ok = mbar_wait(bars + 8 * (kStages + s), ph_store);
+                    if (!ok) {
                         // recorded only: the consumers decide among themselves when to stop (they share a barrier)
                         if (lane == 0) {
                             atomicAdd(p.timeouts, 1u);
                             sts_s32(abort_p, 1);
                         }
-                        live = false;
                     } else if (lds_s32(abort_c)) {
-                        live = false;
+                        ok = false;
                     } else if (lane == 0) {
-                        int b, t0;
-                        decode_tile(j0 + j * stride, p.n_ttile, G::kTileRows, b, t0);
                         // output row t sits in box row t - t0 + H: the store starts H rows into the stage
-                        tma_store_3d(&tmap_y, slab_ch0, t0, b, base + s * G::kStageBytes + H * G::kRowBytes);
+                        tma_store_3d(&tmap_y, slab_ch0, it_store.t0(G::kTileRows), it_store.b,
+                                     base + s * G::kStageBytes + H * G::kRowBytes);
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                     __syncwarp();
+                    if (!ok) return false;
+                    it_store.next();
+                    if (++s_store == kStages) {
+                        s_store = 0;
+                        ph_store ^= 1;
+                    }
                 }
             }
+            return true;
+        };
+        float mk_a[NMK], mk_b[NMK], mk_c[NMK];
+#pragma unroll
+        for (int q = 0; q < NMK; ++q) mk_a[q] = mk_b[q] = mk_c[q] = 1.0f;
+        if (p.mask != nullptr && n_my > 0)
+            fetch_mask<NMK, G::kBoxRows, H, G::kTileRows>(p, it_fetch.b, it_fetch.t0(G::kTileRows), lane, mk_a);
+        if (p.mask != nullptr && n_my > 1) {
+            it_fetch.next();
+            fetch_mask<NMK, G::kBoxRows, H, G::kTileRows>(p, it_fetch.b, it_fetch.t0(G::kTileRows), lane, mk_b);
+        }
+        for (int i = 0; i < n_iter; i += 3) {
+            if (!step(i, mk_a, mk_c)) break;
+            if (i + 1 < n_iter && !step(i + 1, mk_b, mk_a)) break;
+            if (i + 2 < n_iter && !step(i + 2, mk_c, mk_b)) break;
         }
         if (!DIRECT && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     } else {
@@ -537,9 +587,12 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         }
         const bool general_kernel = (p.mask != nullptr) || (p.res != nullptr);
 
+        int s = -1;
+        uint32_t ph = 1;
         for (int i = 0; i < n_my; ++i) {
-            const int s = i % kStages;
-            const bool ok = mbar_wait(bars + 8 * s, (i / kStages) & 1);
+            if (++s == kStages) s = 0;
+            if (s == 0) ph ^= 1;
+            const bool ok = mbar_wait(bars + 8 * s, ph);
             if (!ok) {
                 if (lane == 0) {
                     atomicAdd(p.timeouts, 1u);
@@ -583,6 +636,9 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
                 asm volatile("bar.sync 1, %0;" ::"n"(G::kConsumerThreads) : "memory");
                 if (lds_s32(abort_c)) break;
             }
+            // rows of this thread that exist in the output (streaming stores only; bulk stores clip)
+            int rows_ok = 0;
+            if (DIRECT && ch_ok) rows_ok = min(R, max(0, p.T - tfirst));
             char* yrow = nullptr;
             if (DIRECT) yrow = p.y + (long long)b * p.syb + (long long)tfirst * p.syt + (long long)d0 * E::kBytes;
             const char* rb = nullptr;
@@ -593,17 +649,17 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
 #pragma unroll
                 for (int k = 0; k < R; ++k) {
                     if (DIRECT) {
-                        if (ch_ok && tfirst + k < p.T) S::stg(yrow + (long long)k * p.syt, const_row);
+                        if (rows_ok > k) S::stg(yrow + (long long)k * p.syt, const_row);
                     } else {
                         S::sts(trow + (H + k) * G::kRowBytes, const_row);
                     }
                 }
             } else if (cls == TILE_FULL && p.res == nullptr) {
                 process_rows<DT, W, VB, RPT, ACT, false, DIRECT, G::kRowBytes>(trow, mk_addr, p, false, nullptr, yrow, tfirst,
-                                                                          ch_ok, hist, wp, bp);
+                                                                               rows_ok, hist, wp, bp);
             } else {
                 process_rows<DT, W, VB, RPT, ACT, true, DIRECT, G::kRowBytes>(trow, mk_addr, p, mixed, rb, yrow, tfirst,
-                                                                         ch_ok, hist, wp, bp);
+                                                                              rows_ok, hist, wp, bp);
             }
             // bulk stores read the results through the async proxy; they were written through the generic one
             if (!DIRECT) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
