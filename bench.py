@@ -149,7 +149,7 @@ def time_cpu_reference(cfg, rows, steps, warmup):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     x = WL.prefill_inputs(cfg, rows)
-    m = WL.attention_mask(cfg, rows)
+    m = WL.attention_mask(cfg, rows, dtype=torch.bool)
     w, b = WL.weights(cfg.cfg, cfg.dim, cfg.width, cfg.dtype)
     with torch.no_grad():
         for _ in range(warmup):
@@ -214,7 +214,7 @@ def workload_config(cfg, n_gpus):
         "width": cfg.width,
         "activation": cfg.activation,
         "bias": True,
-        "mask": "right-padded, valid length uniform in [128,1024], applied in-kernel",
+        "mask": "bool [B,T], right-padded, valid length uniform in [128,1024], applied in-kernel",
         "layout": "channel-last [B,T,D] viewed as [B,D,T]",
         "parallelism": f"sequence-sharded x{n_gpus}, no collective",
         "l2": "inputs larger than L2 (226 MB read + 226 MB written per step vs 126 MB)",
@@ -281,7 +281,8 @@ def main():
     cfg = WL.CANON_D_PREFILL
     rows = [rank * cfg.batch + i for i in range(cfg.batch)]
     x_host = WL.prefill_inputs(cfg, rows).pin_memory()
-    m_host = WL.attention_mask(cfg, rows).pin_memory()
+    # bool, as the reference's trainer builds it: attn_mask = (X != pad)  (trainer/base_trainer.py:204)
+    m_host = WL.attention_mask(cfg, rows, dtype=torch.bool).pin_memory()
     lens = WL.sequence_lengths(cfg, rows)
     w, b = WL.weights(cfg.cfg, cfg.dim, cfg.width, cfg.dtype, device=dev)
     x = x_host.to(dev, non_blocking=True)
@@ -314,7 +315,7 @@ def main():
         kernel_name = V.last_kernel()
 
         # ---- end to end: pinned host in, pinned host out, every step -------------------------
-        pipe = HostPrefill(cfg.batch, cfg.seqlen, cfg.dim, cfg.dtype, device=dev, chunk_batch=4)
+        pipe = HostPrefill(cfg.batch, cfg.seqlen, cfg.dim, cfg.dtype, device=dev, chunk_batch=4, mask_dtype=torch.bool)
         y_host = torch.empty_like(x_host).pin_memory()
         e2e_steps = max(3, min(steps, 20))
         for _ in range(3):

@@ -1,13 +1,21 @@
-// Prefill kernel for the channel-last layout the Canon layers pass
-// (x.transpose(1,2) of a contiguous [B,T,D] tensor, reference model/model.py:459-466).
+// Register-window prefill kernel for the channel-last layout the Canon layers pass
+// (x.transpose(1,2) of a contiguous [B,T,D] tensor, reference model/model.py:459-466), with the
+// fused options of the layer around it (mask model/model.py:454-457, residual :491, state
+// :470-489, history :607-617).
 //
-// Work unit: one thread owns one 128-bit channel vector (8 bf16 / 4 fp32 channels) and a
-// chunk of consecutive time rows.  Units are numbered with the channel vector fastest, so
-// a warp reads 512 contiguous bytes per row and no lane idles whatever dim is.  Weights
-// and bias of the owned channels live in registers as fp32 pairs; the (W-1)-row history
-// is a register sliding window, seeded by re-reading the W-1 rows before the chunk (they
-// come from L1/L2: another thread of the grid streams them from HBM).  Loads are issued
-// U rows at a time before any arithmetic so that every thread keeps U*16 bytes in flight.
+// Work unit: one thread owns VB bytes of channels (8 = four bf16, or 16) and a chunk of R
+// consecutive time rows.  Units are numbered with the channel slice fastest, so a warp reads
+// 32*VB contiguous bytes per row, a 256-thread CTA 2-4 KB, and no lane idles whatever dim is.
+// Weights and bias of the owned channels live in registers as fp32 pairs; the (W-1)-row
+// history is a register window rotated by index, seeded by re-reading the W-1 rows before the
+// chunk (L1/L2 hits: the thread of the chunk above streams them from HBM).  Loads are issued U
+// rows at a time before any arithmetic, so a thread keeps U*VB bytes in flight and an SM, at
+// ~900 resident threads, some 50 KB -- the depth at which this GPU's HBM streams best.  There
+// is no shared memory and no barrier: the grid is many small CTAs and the hardware scheduler
+// balances ragged (masked) batches and uneven SMs by itself.
+//
+// Masked rows are not read at all when skip_masked_loads is set; a chunk tail in which every
+// tap of every row is masked stores act(bias) without any arithmetic.
 #include "vc1d_common.cuh"
 #include "vc1d_internal.h"
 
@@ -31,133 +39,95 @@ struct CLParams {
     long long total;
     int wdtype;
     int B, D, T;
-    int nvec, nchunk, R;
-    int act;
+    int nslice, nchunk, R;
     int mask_dtype;
     int skip;
     int init_len, state_len;
-    int w_fast;  // weights contiguous [D,W], same dtype as x, 16-byte aligned
 };
 
-template <int DT, int W>
-__device__ __forceinline__ void load_weights(const CLParams& p, int d0,
-                                             float2 (&wp)[W][Pack<DT>::kPairs],
-                                             float2 (&bp)[Pack<DT>::kPairs]) {
+template <int DT, int W, int VB>
+__device__ __forceinline__ void load_weights(const CLParams& p, int d0, float2 (&wp)[W][Slice<DT, VB>::kPairs],
+                                             float2 (&bp)[Slice<DT, VB>::kPairs]) {
     using E = Elem<DT>;
     using T = typename E::type;
-    constexpr int VEC = E::kVec;
-    constexpr int PAIRS = Pack<DT>::kPairs;
-    float wf[VEC * W];
-    if (p.w_fast) {
-        // VEC channels x W taps are VEC*W consecutive elements = W 128-bit vectors
-        const char* base = reinterpret_cast<const char*>(p.weight) + (long long)d0 * W * E::kBytes;
+    constexpr int NE = Slice<DT, VB>::kElems;
+    constexpr int NP = Slice<DT, VB>::kPairs;
+    float wf[NE][W];
+    float bf[NE];
 #pragma unroll
-        for (int j = 0; j < W; ++j) {
-            const uint4 v = ld_vec(base + j * 16);
-            float2 f[PAIRS];
-            Pack<DT>::unpack(v, f);
+    for (int c = 0; c < NE; ++c) {
 #pragma unroll
-            for (int q = 0; q < PAIRS; ++q) {
-                wf[j * VEC + 2 * q] = f[q].x;
-                wf[j * VEC + 2 * q + 1] = f[q].y;
-            }
+        for (int w = 0; w < W; ++w) {
+            const long long idx = (long long)(d0 + c) * p.wsd + (long long)w * p.wsw;
+            wf[c][w] = (p.wdtype == VC1D_F32) ? __ldg(reinterpret_cast<const float*>(p.weight) + idx)
+                                              : E::to_float(__ldg(reinterpret_cast<const T*>(p.weight) + idx));
         }
-    } else {
-#pragma unroll
-        for (int c = 0; c < VEC; ++c) {
-#pragma unroll
-            for (int w = 0; w < W; ++w) {
-                const long long idx = (long long)(d0 + c) * p.wsd + (long long)w * p.wsw;
-                wf[c * W + w] = (p.wdtype == VC1D_F32)
-                                    ? __ldg(reinterpret_cast<const float*>(p.weight) + idx)
-                                    : E::to_float(__ldg(reinterpret_cast<const T*>(p.weight) + idx));
-            }
+        bf[c] = 0.f;
+        if (p.bias != nullptr) {
+            bf[c] = (p.wdtype == VC1D_F32) ? __ldg(reinterpret_cast<const float*>(p.bias) + d0 + c)
+                                           : E::to_float(__ldg(reinterpret_cast<const T*>(p.bias) + d0 + c));
         }
     }
 #pragma unroll
-    for (int w = 0; w < W; ++w) {
+    for (int q = 0; q < NP; ++q) {
 #pragma unroll
-        for (int q = 0; q < PAIRS; ++q) {
-            wp[w][q] = make_float2(wf[(2 * q) * W + w], wf[(2 * q + 1) * W + w]);
-        }
-    }
-    if (p.bias != nullptr) {
-        float bf[VEC];
-#pragma unroll
-        for (int c = 0; c < VEC; ++c) {
-            bf[c] = (p.wdtype == VC1D_F32)
-                        ? __ldg(reinterpret_cast<const float*>(p.bias) + d0 + c)
-                        : E::to_float(__ldg(reinterpret_cast<const T*>(p.bias) + d0 + c));
-        }
-#pragma unroll
-        for (int q = 0; q < PAIRS; ++q) bp[q] = make_float2(bf[2 * q], bf[2 * q + 1]);
-    } else {
-#pragma unroll
-        for (int q = 0; q < PAIRS; ++q) bp[q] = make_float2(0.f, 0.f);
+        for (int w = 0; w < W; ++w) wp[w][q] = make_float2(wf[2 * q][w], wf[2 * q + 1][w]);
+        bp[q] = make_float2(bf[2 * q], bf[2 * q + 1]);
     }
 }
 
-// raw 128-bit row -> fp32 pairs, with the multiplicative mask of the reference
-// (x * mask, rounded to the I/O dtype) when the mask value is not exactly 1
-template <int DT, bool MASK>
-__device__ __forceinline__ void decode_row(const uint4& raw, float mk,
-                                           float2 (&f)[Pack<DT>::kPairs]) {
-    Pack<DT>::unpack(raw, f);
-    if (MASK) {
-        if (mk != 1.0f) {
-            const float2 m2 = make_float2(mk, mk);
+// raw row -> fp32 pairs, with the multiplicative mask of the reference (x * mask, rounded to the
+// I/O dtype) when the mask value is not exactly 1
+template <int DT, int VB>
+__device__ __forceinline__ void decode_row(const uint32_t (&raw)[Slice<DT, VB>::kWords], bool masked, float mk,
+                                           float2 (&f)[Slice<DT, VB>::kPairs]) {
+    using S = Slice<DT, VB>;
+    S::unpack(raw, f);
+    if (masked && mk != 1.0f) {
+        const float2 m2 = make_float2(mk, mk);
 #pragma unroll
-            for (int q = 0; q < Pack<DT>::kPairs; ++q) f[q] = Pack<DT>::round_trip(mul2(f[q], m2));
-        }
+        for (int q = 0; q < S::kPairs; ++q) f[q] = S::round_trip(mul2(f[q], m2));
     }
 }
 
-template <int DT>
-__device__ __forceinline__ void store_channel_column(char* fstate, long long row0, int L, int j,
-                                                     const uint4& raw) {
-    // fstate is [B, D, L] contiguous; this thread owns channels row0 .. row0+VEC-1
+// one column of an initial state [B, D, init_len] for this thread's channels, as a raw row
+template <int DT, int VB>
+__device__ __forceinline__ void load_init_column(const char* init, long long row0, int init_len, int col,
+                                                 uint32_t (&raw)[Slice<DT, VB>::kWords]) {
     using T = typename Elem<DT>::type;
-    constexpr int VEC = Elem<DT>::kVec;
-    T vals[VEC];
-    *reinterpret_cast<uint4*>(vals) = raw;
-    T* out = reinterpret_cast<T*>(fstate);
-#pragma unroll
-    for (int c = 0; c < VEC; ++c) out[(row0 + c) * L + j] = vals[c];
-}
-
-template <int DT>
-__device__ __forceinline__ uint4 load_init_column(const char* init, long long row0, int init_len,
-                                                  int col) {
-    using T = typename Elem<DT>::type;
-    constexpr int VEC = Elem<DT>::kVec;
-    T vals[VEC];
+    constexpr int NE = Slice<DT, VB>::kElems;
+    T vals[NE];
     const T* in = reinterpret_cast<const T*>(init);
 #pragma unroll
-    for (int c = 0; c < VEC; ++c) vals[c] = in[(row0 + c) * init_len + col];
-    return *reinterpret_cast<uint4*>(vals);
+    for (int c = 0; c < NE; ++c) vals[c] = in[(row0 + c) * init_len + col];
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(vals);
+#pragma unroll
+    for (int i = 0; i < Slice<DT, VB>::kWords; ++i) raw[i] = w[i];
 }
 
-template <int DT, int W, int U, bool MASK, bool RES>
-__global__ void __launch_bounds__(256) k_prefill_channel_last(const CLParams p) {
+template <int DT, int W, int VB, int U, bool ACT, bool MASK, bool RES>
+__global__ void __launch_bounds__(256, (VB == 8 && !MASK) ? 3 : 2) k_prefill_window(const CLParams p) {
     using E = Elem<DT>;
-    using PK = Pack<DT>;
-    constexpr int VEC = E::kVec;
-    constexpr int PAIRS = PK::kPairs;
+    using S = Slice<DT, VB>;
+    constexpr int NE = S::kElems;
+    constexpr int NP = S::kPairs;
+    constexpr int NW = S::kWords;
     constexpr int H = W - 1;
+    constexpr int HS = H > 0 ? H : 1;
 
     const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (g >= p.total) return;
-    const int lane = (int)(g % p.nvec);
-    const long long q = g / p.nvec;
-    const int chunk = (int)(q % p.nchunk);
-    const int b = (int)(q / p.nchunk);
-    const int d0 = lane * VEC;
+    const int slice = (int)(g % p.nslice);
+    const long long q0 = g / p.nslice;
+    const int chunk = (int)(q0 % p.nchunk);
+    const int b = (int)(q0 / p.nchunk);
+    const int d0 = slice * NE;
     const int t0 = chunk * p.R;
     const int t1 = min(t0 + p.R, p.T);
 
-    float2 wp[W][PAIRS];
-    float2 bp[PAIRS];
-    load_weights<DT, W>(p, d0, wp, bp);
+    float2 wp[W][NP];
+    float2 bp[NP];
+    load_weights<DT, W, VB>(p, d0, wp, bp);
 
     const char* xb = p.x + (long long)b * p.sxb + (long long)d0 * E::kBytes;
     char* yb = p.y + (long long)b * p.syb + (long long)d0 * E::kBytes;
@@ -165,133 +135,209 @@ __global__ void __launch_bounds__(256) k_prefill_channel_last(const CLParams p) 
     const long long mrow = (long long)b * p.smb;
     const long long row0 = (long long)b * p.D + d0;  // first owned row of a [B*D, L] state
 
-    // ---- history: the W-1 rows before the chunk --------------------------------------
-    float2 hist[H][PAIRS];
+    // ---- history: the W-1 rows before the chunk; hist[j] is the row W-1-j steps back ... oldest first
+    float2 hist[HS][NP];
+    int zero_run = 0;  // trailing rows known to be +0 because their mask is 0 and loads are skipped
 #pragma unroll
     for (int j = 0; j < H; ++j) {
         const int t = t0 - H + j;
-        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+        uint32_t raw[NW];
+#pragma unroll
+        for (int i = 0; i < NW; ++i) raw[i] = 0u;
         float mk = 1.0f;
+        bool zero = false;
         if (t >= 0) {
             if (MASK) mk = load_mask(p.mask, mrow + (long long)t * p.smt, p.mask_dtype);
-            if (!MASK || !p.skip || mk != 0.0f) raw = ld_vec(xb + (long long)t * p.sxt);
+            if (MASK && p.skip && mk == 0.0f)
+                zero = true;
+            else
+                S::ldg(xb + (long long)t * p.sxt, raw);
         } else if (p.init != nullptr) {
-            raw = load_init_column<DT>(p.init, row0, p.init_len, p.init_len + t);
+            load_init_column<DT, VB>(p.init, row0, p.init_len, p.init_len + t, raw);
+        } else {
+            zero = true;  // causal left padding
         }
-        decode_row<DT, MASK>(raw, mk, hist[j]);
+        decode_row<DT, VB>(raw, MASK && t >= 0 && !zero, mk, hist[j]);
+        zero_run = zero ? zero_run + 1 : 0;
     }
 
-    // ---- main sweep ------------------------------------------------------------------
+    // value of a row whose W taps are all +0: act(bias)
+    uint32_t const_row[NW];
+    {
+        float2 c[NP];
+#pragma unroll
+        for (int qq = 0; qq < NP; ++qq) c[qq] = ACT ? silu2<E::kPreciseSilu>(bp[qq]) : bp[qq];
+        S::pack(c, const_row);
+    }
+
+    // ---- main sweep, U rows at a time ------------------------------------------------------
+    float mk_next[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+        mk_next[k] = 1.0f;
+        if (MASK && t0 + k < t1) mk_next[k] = load_mask(p.mask, mrow + (long long)(t0 + k) * p.smt, p.mask_dtype);
+    }
     for (int tb = t0; tb < t1; tb += U) {
-        uint4 raw[U];
-        uint4 rres[RES ? U : 1];
         float mk[U];
+        bool skip_row[U];
+        bool any_live = false;
+        uint32_t raw[U][NW];
+        uint32_t rres[RES ? U : 1][NW];
 #pragma unroll
         for (int k = 0; k < U; ++k) {
-            const int t = tb + k;
-            const bool in = t < t1;
-            mk[k] = 1.0f;
-            if (MASK) mk[k] = in ? load_mask(p.mask, mrow + (long long)t * p.smt, p.mask_dtype) : 0.0f;
-            const bool need = in && (!MASK || !p.skip || mk[k] != 0.0f);
-            raw[k] = make_uint4(0u, 0u, 0u, 0u);
-            if (need) raw[k] = ld_vec(xb + (long long)t * p.sxt);
+            mk[k] = mk_next[k];
+            const bool in = tb + k < t1;
+            skip_row[k] = !in || (MASK && p.skip && mk[k] == 0.0f);
+            any_live |= in && !skip_row[k];
+#pragma unroll
+            for (int i = 0; i < NW; ++i) raw[k][i] = 0u;
+            if (!skip_row[k]) S::ldg(xb + (long long)(tb + k) * p.sxt, raw[k]);
             if (RES) {
-                rres[k] = make_uint4(0u, 0u, 0u, 0u);
-                if (in) rres[k] = ld_vec(rb + (long long)t * p.srt);
+#pragma unroll
+                for (int i = 0; i < NW; ++i) rres[k][i] = 0u;
+                if (in) S::ldg(rb + (long long)(tb + k) * p.srt, rres[k]);
             }
         }
+        if (MASK) {
+            // the mask values of the next batch travel while this batch is computed
 #pragma unroll
-        for (int k = 0; k < U; ++k) {
-            const int t = tb + k;
-            if (t < t1) {
-                float2 cur[PAIRS];
-                decode_row<DT, MASK>(raw[k], mk[k], cur);
-                float2 acc[PAIRS];
+            for (int k = 0; k < U; ++k) {
+                mk_next[k] = 1.0f;
+                if (tb + U + k < t1)
+                    mk_next[k] = load_mask(p.mask, mrow + (long long)(tb + U + k) * p.smt, p.mask_dtype);
+            }
+        }
+        if (MASK && !RES && !any_live && zero_run >= H) {
+            // every tap of every row of this batch is +0
 #pragma unroll
-                for (int qq = 0; qq < PAIRS; ++qq) {
+            for (int k = 0; k < U; ++k)
+                if (tb + k < t1) S::stg(yb + (long long)(tb + k) * p.syt, const_row);
+            zero_run += U;
+            continue;  // hist stays all-zero
+        }
+        static_for<0, U>([&](auto kc) {
+            constexpr int k = decltype(kc)::value;
+            if (tb + k < t1) {
+                float2 cur[NP];
+                decode_row<DT, VB>(raw[k], MASK && !skip_row[k], mk[k], cur);
+                float2 acc[NP];
+#pragma unroll
+                for (int qq = 0; qq < NP; ++qq) {
                     acc[qq] = bp[qq];
 #pragma unroll
-                    for (int w = 0; w < H; ++w) acc[qq] = fma2(wp[w][qq], hist[w][qq], acc[qq]);
+                    for (int w = 0; w < H; ++w) acc[qq] = fma2(wp[w][qq], hist[(k + w) % HS][qq], acc[qq]);
                     acc[qq] = fma2(wp[H][qq], cur[qq], acc[qq]);
-                    if (p.act) acc[qq] = silu2<E::kPreciseSilu>(acc[qq]);
+                    if (ACT) acc[qq] = silu2<E::kPreciseSilu>(acc[qq]);
                 }
                 if (RES) {
                     // same roundings as the unfused `x + y`: y rounded to the I/O dtype, then the sum
-                    float2 rr[PAIRS];
-                    PK::unpack(rres[k], rr);
+                    float2 rr[NP];
+                    S::unpack(rres[k], rr);
 #pragma unroll
-                    for (int qq = 0; qq < PAIRS; ++qq) acc[qq] = add2(PK::round_trip(acc[qq]), rr[qq]);
+                    for (int qq = 0; qq < NP; ++qq) acc[qq] = add2(S::round_trip(acc[qq]), rr[qq]);
                 }
-                st_vec_stream(yb + (long long)t * p.syt, PK::pack(acc));
-#pragma unroll
-                for (int w = 0; w + 1 < H; ++w) {
-#pragma unroll
-                    for (int qq = 0; qq < PAIRS; ++qq) hist[w][qq] = hist[w + 1][qq];
-                }
+                uint32_t outw[NW];
+                S::pack(acc, outw);
+                S::stg(yb + (long long)(tb + k) * p.syt, outw);
                 if (H > 0) {
 #pragma unroll
-                    for (int qq = 0; qq < PAIRS; ++qq) hist[H - 1][qq] = cur[qq];
+                    for (int qq = 0; qq < NP; ++qq) hist[k % HS][qq] = cur[qq];
                 }
+                zero_run = skip_row[k] ? zero_run + 1 : 0;
             }
+        });
+        // the batch advanced the window by U rows: bring the oldest row back to slot 0
+        // (rows past t1 only occur in the last batch, after which the window is dead)
+        if (H > 1 && (U % HS) != 0) {
+            float2 tmp[HS][NP];
+#pragma unroll
+            for (int w = 0; w < H; ++w)
+#pragma unroll
+                for (int qq = 0; qq < NP; ++qq) tmp[w][qq] = hist[(U + w) % HS][qq];
+#pragma unroll
+            for (int w = 0; w < H; ++w)
+#pragma unroll
+                for (int qq = 0; qq < NP; ++qq) hist[w][qq] = tmp[w][qq];
         }
     }
 
     // ---- final state: right-aligned last state_len masked inputs ------------------------
     if (p.fstate != nullptr && t1 == p.T) {
+        using T = typename E::type;
         const int L = p.state_len;
+        T* out = reinterpret_cast<T*>(p.fstate) + row0 * L;
         for (int j = 0; j < L; ++j) {
             const int t = p.T - L + j;
-            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-            if (t >= 0) {
-                raw = ld_vec(xb + (long long)t * p.sxt);
-                if (MASK) {
-                    const float mk = load_mask(p.mask, mrow + (long long)t * p.smt, p.mask_dtype);
-                    if (mk != 1.0f) {
-                        float2 f[PAIRS];
-                        PK::unpack(raw, f);
-                        const float2 m2 = make_float2(mk, mk);
+            uint32_t raw[NW];
 #pragma unroll
-                        for (int qq = 0; qq < PAIRS; ++qq) f[qq] = mul2(f[qq], m2);
-                        raw = PK::pack(f);
+            for (int i = 0; i < NW; ++i) raw[i] = 0u;
+            if (t >= 0) {
+                S::ldg(xb + (long long)t * p.sxt, raw);
+                if (MASK) {
+                    const float mkv = load_mask(p.mask, mrow + (long long)t * p.smt, p.mask_dtype);
+                    if (mkv != 1.0f) {
+                        float2 f[NP];
+                        S::unpack(raw, f);
+                        const float2 m2 = make_float2(mkv, mkv);
+#pragma unroll
+                        for (int qq = 0; qq < NP; ++qq) f[qq] = mul2(f[qq], m2);
+                        S::pack(f, raw);
                     }
                 }
             } else if (p.init != nullptr && p.init_len + t >= 0) {
-                raw = load_init_column<DT>(p.init, row0, p.init_len, p.init_len + t);
+                load_init_column<DT, VB>(p.init, row0, p.init_len, p.init_len + t, raw);
             }
-            store_channel_column<DT>(p.fstate, row0, L, j, raw);
+            const T* vals = reinterpret_cast<const T*>(raw);
+#pragma unroll
+            for (int c = 0; c < NE; ++c) out[(long long)c * L + j] = vals[c];
         }
     }
 }
 
-template <int DT, int W, int U>
-cudaError_t launch_u(const CLParams& p, bool mask, bool res, int block, cudaStream_t s) {
+template <int DT, int W, int VB, bool ACT>
+cudaError_t launch_flags(const CLParams& p, bool mask, bool res, int block, cudaStream_t s) {
+    constexpr int U = 8;
     const long long blocks = (p.total + block - 1) / block;
     if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     const dim3 grid((unsigned)blocks);
     if (mask && res)
-        k_prefill_channel_last<DT, W, U, true, true><<<grid, block, 0, s>>>(p);
+        k_prefill_window<DT, W, VB, U, ACT, true, true><<<grid, block, 0, s>>>(p);
     else if (mask)
-        k_prefill_channel_last<DT, W, U, true, false><<<grid, block, 0, s>>>(p);
+        k_prefill_window<DT, W, VB, U, ACT, true, false><<<grid, block, 0, s>>>(p);
     else if (res)
-        k_prefill_channel_last<DT, W, U, false, true><<<grid, block, 0, s>>>(p);
+        k_prefill_window<DT, W, VB, U, ACT, false, true><<<grid, block, 0, s>>>(p);
     else
-        k_prefill_channel_last<DT, W, U, false, false><<<grid, block, 0, s>>>(p);
+        k_prefill_window<DT, W, VB, U, ACT, false, false><<<grid, block, 0, s>>>(p);
     return cudaGetLastError();
 }
 
 template <int DT, int W>
-cudaError_t launch_w(const CLParams& p, bool mask, bool res, int block, int unroll, cudaStream_t s) {
-    if (unroll == 4) return launch_u<DT, W, 4>(p, mask, res, block, s);
-    return launch_u<DT, W, 8>(p, mask, res, block, s);
+cudaError_t launch_w(const CLParams& base, const vc1d_prefill_args& a, int block, cudaStream_t s) {
+    const bool mask = a.mask != nullptr, res = a.residual != nullptr;
+    const bool act = a.activation == VC1D_ACT_SILU;
+    CLParams p = base;
+    // bytes of channels per thread: 8 by default (more resident threads), 16 on request
+    const int vb = (a.unroll == 16) ? 16 : 8;
+    const int eb = Elem<DT>::kBytes;
+    p.nslice = a.dim * eb / vb;
+    p.total = (long long)a.batch * p.nchunk * p.nslice;
+    if constexpr (DT == VC1D_BF16 && W == 4) {
+        if (vb == 16)
+            return act ? launch_flags<DT, W, 16, true>(p, mask, res, block, s)
+                       : launch_flags<DT, W, 16, false>(p, mask, res, block, s);
+    }
+    p.nslice = a.dim * eb / 8;
+    p.total = (long long)a.batch * p.nchunk * p.nslice;
+    return act ? launch_flags<DT, W, 8, true>(p, mask, res, block, s)
+               : launch_flags<DT, W, 8, false>(p, mask, res, block, s);
 }
 
 template <int DT>
-cudaError_t launch_dt(const CLParams& p, int width, bool mask, bool res, int block, int unroll,
-                      cudaStream_t s) {
-    switch (width) {
-        case 2: return launch_w<DT, 2>(p, mask, res, block, unroll, s);
-        case 3: return launch_w<DT, 3>(p, mask, res, block, unroll, s);
-        default: return launch_w<DT, 4>(p, mask, res, block, unroll, s);
+cudaError_t launch_dt(const CLParams& p, const vc1d_prefill_args& a, int block, cudaStream_t s) {
+    switch (a.width) {
+        case 2: return launch_w<DT, 2>(p, a, block, s);
+        case 3: return launch_w<DT, 3>(p, a, block, s);
+        default: return launch_w<DT, 4>(p, a, block, s);
     }
 }
 
@@ -299,7 +345,6 @@ cudaError_t launch_dt(const CLParams& p, int width, bool mask, bool res, int blo
 
 cudaError_t launch_prefill_channel_last(const vc1d_prefill_args& a, cudaStream_t s) {
     const int eb = elem_bytes(a.dtype);
-    const int vec = 16 / eb;
     CLParams p;
     p.x = reinterpret_cast<const char*>(a.x);
     p.y = reinterpret_cast<char*>(a.y);
@@ -323,42 +368,34 @@ cudaError_t launch_prefill_channel_last(const vc1d_prefill_args& a, cudaStream_t
     p.B = a.batch;
     p.D = a.dim;
     p.T = a.seqlen;
-    p.nvec = a.dim / vec;
-    p.act = a.activation;
     p.mask_dtype = a.mask_dtype;
     p.skip = (a.mask != nullptr && a.skip_masked_loads) ? 1 : 0;
     p.init_len = a.init_len;
     p.state_len = a.state_len;
-    p.w_fast = (a.wdtype == a.dtype && a.w_stride_w == 1 && a.w_stride_d == a.width &&
-                (reinterpret_cast<uintptr_t>(a.weight) & 15u) == 0)
-                   ? 1
-                   : 0;
 
     int block = a.block_threads > 0 ? a.block_threads : 256;
     if (block > 256) block = 256;
     block = (block + 31) / 32 * 32;
 
-    // Rows per thread: long enough to amortise the weight load and the halo re-read,
-    // short enough that the grid has several waves of CTAs on every SM.
+    // Rows per thread: long enough to amortise the weight load and the halo re-read, short
+    // enough that the grid has several waves of CTAs on every SM.
     int R = a.rows_per_thread;
     if (R <= 0) {
-        R = 32;
-        const long long want_threads = (long long)sm_count() * 2048 * 4;
-        while (R > 8 && (long long)a.batch * p.nvec * ((a.seqlen + R - 1) / R) < want_threads) R /= 2;
+        R = 64;
+        const long long nslice = (long long)a.dim * eb / 8;
+        const long long want_threads = (long long)sm_count() * 1024 * 6;
+        while (R > 8 && (long long)a.batch * nslice * ((a.seqlen + R - 1) / R) < want_threads) R /= 2;
     }
     if (R > a.seqlen) R = a.seqlen;
     p.R = R;
     p.nchunk = (a.seqlen + R - 1) / R;
-    p.total = (long long)a.batch * p.nchunk * p.nvec;
-
-    const bool mask = a.mask != nullptr;
-    const bool res = a.residual != nullptr;
-    const int unroll = (a.unroll == 4) ? 4 : 8;
+    p.nslice = 0;
+    p.total = 0;
     note_launch("channel_last");
     switch (a.dtype) {
-        case VC1D_F32: return launch_dt<VC1D_F32>(p, a.width, mask, res, block, unroll, s);
-        case VC1D_BF16: return launch_dt<VC1D_BF16>(p, a.width, mask, res, block, unroll, s);
-        default: return launch_dt<VC1D_F16>(p, a.width, mask, res, block, unroll, s);
+        case VC1D_F32: return launch_dt<VC1D_F32>(p, a, block, s);
+        case VC1D_BF16: return launch_dt<VC1D_BF16>(p, a, block, s);
+        default: return launch_dt<VC1D_F16>(p, a, block, s);
     }
 }
 

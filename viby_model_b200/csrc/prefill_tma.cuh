@@ -129,14 +129,6 @@ __device__ __forceinline__ void sts_f32(uint32_t a, float v) {
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory");
 }
 
-template <int K, int N, class F>
-__device__ __forceinline__ void static_for(F&& f) {
-    if constexpr (K < N) {
-        f(std::integral_constant<int, K>{});
-        static_for<K + 1, N>(f);
-    }
-}
-
 // Walks the row tiles j0, j0 + G, j0 + 2G, ... of one CTA without a division per tile.  Tile
 // number rt means sequence b = rt / n_ttile and time position (rt % n_ttile + b) % n_ttile: the
 // position is rotated by the sequence index so that a CTA does not keep meeting the same position
@@ -169,67 +161,6 @@ struct TileIter {
         if (tt >= n) tt -= n;
         return tt * tile_rows;
     }
-};
-
-// ---- a thread's slice of one row: VB bytes = NP fp32 pairs ----------------------------------------
-template <int DT, int VB>
-struct Slice {
-    static constexpr int kElems = VB / Elem<DT>::kBytes;
-    static constexpr int kPairs = kElems / 2;
-    static constexpr int kWords = VB / 4;
-
-    __device__ __forceinline__ static void lds(uint32_t a, uint32_t (&r)[kWords]) {
-        if constexpr (VB == 16)
-            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
-                         : "=r"(r[0]), "=r"(r[1]), "=r"(r[kWords > 2 ? 2 : 0]), "=r"(r[kWords > 3 ? 3 : 0])
-                         : "r"(a));
-        else
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
-    }
-    __device__ __forceinline__ static void sts(uint32_t a, const uint32_t (&r)[kWords]) {
-        if constexpr (VB == 16)
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(r[0]), "r"(r[1]),
-                         "r"(r[kWords > 2 ? 2 : 0]), "r"(r[kWords > 3 ? 3 : 0])
-                         : "memory");
-        else
-            asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(r[0]), "r"(r[1]) : "memory");
-    }
-    __device__ __forceinline__ static void stg(void* g, const uint32_t (&r)[kWords]) {
-        if constexpr (VB == 16)
-            asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(g), "r"(r[0]), "r"(r[1]),
-                         "r"(r[kWords > 2 ? 2 : 0]), "r"(r[kWords > 3 ? 3 : 0])
-                         : "memory");
-        else
-            asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(g), "r"(r[0]), "r"(r[1]) : "memory");
-    }
-    __device__ __forceinline__ static void unpack(const uint32_t (&r)[kWords], float2 (&f)[kPairs]) {
-        if constexpr (DT == VC1D_F32) {
-#pragma unroll
-            for (int q = 0; q < kPairs; ++q) f[q] = make_float2(__uint_as_float(r[2 * q]), __uint_as_float(r[2 * q + 1]));
-        } else if constexpr (DT == VC1D_BF16) {
-#pragma unroll
-            for (int q = 0; q < kPairs; ++q) f[q] = Pack<VC1D_BF16>::up(r[q]);
-        } else {
-#pragma unroll
-            for (int q = 0; q < kPairs; ++q) f[q] = Pack<VC1D_F16>::up(r[q]);
-        }
-    }
-    __device__ __forceinline__ static void pack(const float2 (&f)[kPairs], uint32_t (&r)[kWords]) {
-        if constexpr (DT == VC1D_F32) {
-#pragma unroll
-            for (int q = 0; q < kPairs; ++q) {
-                r[2 * q] = __float_as_uint(f[q].x);
-                r[2 * q + 1] = __float_as_uint(f[q].y);
-            }
-        } else if constexpr (DT == VC1D_BF16) {
-#pragma unroll
-            for (int q = 0; q < kPairs; ++q) r[q] = Pack<VC1D_BF16>::down(f[q]);
-        } else {
-#pragma unroll
-            for (int q = 0; q < kPairs; ++q) r[q] = Pack<VC1D_F16>::down(f[q]);
-        }
-    }
-    __device__ __forceinline__ static float2 round_trip(float2 f) { return Pack<DT>::round_trip(f); }
 };
 
 template <int DT, int W, int SLAB_BYTES, int VB, int RPT>
@@ -781,7 +712,9 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
 template <int DT, int W, int SLAB_BYTES, int VB, int RPT>
 cudaError_t launch_store(const vc1d_prefill_args& a, const TmaParams& p, cudaStream_t s) {
     const bool act = a.activation == VC1D_ACT_SILU;
-    if (a.tma_direct_store)
+    // streaming stores from registers by default: one pass fewer through shared memory, and the
+    // stage is free as soon as it has been read; 2 selects bulk tensor stores
+    if (a.tma_direct_store != 2)
         return act ? launch_kernel<DT, W, SLAB_BYTES, VB, RPT, true, true>(a, p, s)
                    : launch_kernel<DT, W, SLAB_BYTES, VB, RPT, false, true>(a, p, s);
     return act ? launch_kernel<DT, W, SLAB_BYTES, VB, RPT, true, false>(a, p, s)

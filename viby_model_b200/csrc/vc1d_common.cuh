@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "../../include/vc1d.h"
 
 namespace vc1d {
@@ -235,5 +237,83 @@ __device__ __forceinline__ float load_mask(const void* base, int64_t idx, int ma
             return 1.0f;
     }
 }
+
+// Compile-time loop: f is called with std::integral_constant<int, K> for K = first .. last-1.
+template <int K, int N, class F>
+__device__ __forceinline__ void static_for(F&& f) {
+    if constexpr (K < N) {
+        f(std::integral_constant<int, K>{});
+        static_for<K + 1, N>(f);
+    }
+}
+
+// ---- a thread's slice of one row: VB bytes = NP fp32 pairs ----------------------------------------
+template <int DT, int VB>
+struct Slice {
+    static constexpr int kElems = VB / Elem<DT>::kBytes;
+    static constexpr int kPairs = kElems / 2;
+    static constexpr int kWords = VB / 4;
+
+    __device__ __forceinline__ static void lds(uint32_t a, uint32_t (&r)[kWords]) {
+        if constexpr (VB == 16)
+            asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(r[0]), "=r"(r[1]), "=r"(r[kWords > 2 ? 2 : 0]), "=r"(r[kWords > 3 ? 3 : 0])
+                         : "r"(a));
+        else
+            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+    }
+    __device__ __forceinline__ static void sts(uint32_t a, const uint32_t (&r)[kWords]) {
+        if constexpr (VB == 16)
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(r[0]), "r"(r[1]),
+                         "r"(r[kWords > 2 ? 2 : 0]), "r"(r[kWords > 3 ? 3 : 0])
+                         : "memory");
+        else
+            asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(r[0]), "r"(r[1]) : "memory");
+    }
+    __device__ __forceinline__ static void ldg(const void* g, uint32_t (&r)[kWords]) {
+        if constexpr (VB == 16)
+            asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(r[0]), "=r"(r[1]), "=r"(r[kWords > 2 ? 2 : 0]), "=r"(r[kWords > 3 ? 3 : 0])
+                         : "l"(g));
+        else
+            asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "l"(g));
+    }
+    __device__ __forceinline__ static void stg(void* g, const uint32_t (&r)[kWords]) {
+        if constexpr (VB == 16)
+            asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(g), "r"(r[0]), "r"(r[1]),
+                         "r"(r[kWords > 2 ? 2 : 0]), "r"(r[kWords > 3 ? 3 : 0])
+                         : "memory");
+        else
+            asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(g), "r"(r[0]), "r"(r[1]) : "memory");
+    }
+    __device__ __forceinline__ static void unpack(const uint32_t (&r)[kWords], float2 (&f)[kPairs]) {
+        if constexpr (DT == VC1D_F32) {
+#pragma unroll
+            for (int q = 0; q < kPairs; ++q) f[q] = make_float2(__uint_as_float(r[2 * q]), __uint_as_float(r[2 * q + 1]));
+        } else if constexpr (DT == VC1D_BF16) {
+#pragma unroll
+            for (int q = 0; q < kPairs; ++q) f[q] = Pack<VC1D_BF16>::up(r[q]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < kPairs; ++q) f[q] = Pack<VC1D_F16>::up(r[q]);
+        }
+    }
+    __device__ __forceinline__ static void pack(const float2 (&f)[kPairs], uint32_t (&r)[kWords]) {
+        if constexpr (DT == VC1D_F32) {
+#pragma unroll
+            for (int q = 0; q < kPairs; ++q) {
+                r[2 * q] = __float_as_uint(f[q].x);
+                r[2 * q + 1] = __float_as_uint(f[q].y);
+            }
+        } else if constexpr (DT == VC1D_BF16) {
+#pragma unroll
+            for (int q = 0; q < kPairs; ++q) r[q] = Pack<VC1D_BF16>::down(f[q]);
+        } else {
+#pragma unroll
+            for (int q = 0; q < kPairs; ++q) r[q] = Pack<VC1D_F16>::down(f[q]);
+        }
+    }
+    __device__ __forceinline__ static float2 round_trip(float2 f) { return Pack<DT>::round_trip(f); }
+};
 
 }  // namespace vc1d
