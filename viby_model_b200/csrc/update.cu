@@ -31,67 +31,120 @@ struct UParams {
     int nvec;
     int act;
     int residual;
+    int nb;      // sequences one thread of the vectorised kernel walks
+    int w_fast;  // weights contiguous [D,W] (and bias) in the I/O dtype, 16-byte aligned
 };
 
 template <int DT, int W, int L>
 __global__ void __launch_bounds__(256) k_update_vec(const UParams p) {
     using E = Elem<DT>;
     using T = typename E::type;
+    using PK = Pack<DT>;
     constexpr int VEC = E::kVec;
+    constexpr int UB = 2;  // sequences in flight per thread
     const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (g >= p.total) return;
     const int lane = (int)(g % p.nvec);
-    const long long b = g / p.nvec;
+    const long long grp = g / p.nvec;
     const int d0 = lane * VEC;
 
-    // issue every load first
-    T st[VEC * L];
-    const char* sp = p.state + (b * p.ssb + (long long)d0 * L) * E::kBytes;
-#pragma unroll
-    for (int j = 0; j < L; ++j) reinterpret_cast<uint4*>(st)[j] = *reinterpret_cast<const uint4*>(sp + j * 16);
-    T xv[VEC];
-    *reinterpret_cast<uint4*>(xv) = ld_vec(p.x + (b * p.sxb + d0) * E::kBytes);
-
+    // weights and bias of the owned channels, once per thread: the thread then walks nb sequences
     float wf[VEC][W];
     float bf[VEC];
+    if (p.w_fast) {
+        // VEC channels x W taps are VEC*W consecutive elements = W 128-bit vectors
+        float flat[VEC * W];
+        const char* base = reinterpret_cast<const char*>(p.weight) + (long long)d0 * W * E::kBytes;
 #pragma unroll
-    for (int c = 0; c < VEC; ++c) {
+        for (int j = 0; j < W; ++j) {
+            float2 f[PK::kPairs];
+            PK::unpack(ld_vec(base + j * 16), f);
 #pragma unroll
-        for (int w = 0; w < W; ++w) {
-            const long long idx = (long long)(d0 + c) * p.wsd + (long long)w * p.wsw;
-            wf[c][w] = (p.wdtype == VC1D_F32) ? __ldg(reinterpret_cast<const float*>(p.weight) + idx)
-                                              : E::to_float(__ldg(reinterpret_cast<const T*>(p.weight) + idx));
+            for (int q = 0; q < PK::kPairs; ++q) {
+                flat[j * VEC + 2 * q] = f[q].x;
+                flat[j * VEC + 2 * q + 1] = f[q].y;
+            }
         }
-        bf[c] = 0.f;
-        if (p.bias != nullptr) {
-            bf[c] = (p.wdtype == VC1D_F32) ? __ldg(reinterpret_cast<const float*>(p.bias) + d0 + c)
-                                           : E::to_float(__ldg(reinterpret_cast<const T*>(p.bias) + d0 + c));
+#pragma unroll
+        for (int c = 0; c < VEC; ++c)
+#pragma unroll
+            for (int w = 0; w < W; ++w) wf[c][w] = flat[c * W + w];
+    } else {
+#pragma unroll
+        for (int c = 0; c < VEC; ++c) {
+#pragma unroll
+            for (int w = 0; w < W; ++w) {
+                const long long idx = (long long)(d0 + c) * p.wsd + (long long)w * p.wsw;
+                wf[c][w] = (p.wdtype == VC1D_F32) ? __ldg(reinterpret_cast<const float*>(p.weight) + idx)
+                                                  : E::to_float(__ldg(reinterpret_cast<const T*>(p.weight) + idx));
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) bf[c] = 0.f;
+    if (p.bias != nullptr) {
+        if (p.w_fast) {
+            float2 f[PK::kPairs];
+            PK::unpack(ld_vec(reinterpret_cast<const char*>(p.bias) + (long long)d0 * E::kBytes), f);
+#pragma unroll
+            for (int q = 0; q < PK::kPairs; ++q) {
+                bf[2 * q] = f[q].x;
+                bf[2 * q + 1] = f[q].y;
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < VEC; ++c)
+                bf[c] = (p.wdtype == VC1D_F32) ? __ldg(reinterpret_cast<const float*>(p.bias) + d0 + c)
+                                               : E::to_float(__ldg(reinterpret_cast<const T*>(p.bias) + d0 + c));
         }
     }
 
-    T ns[VEC * L];
-    T yv[VEC];
+    const long long b0 = grp * p.nb;
+    const long long b1 = (b0 + p.nb < p.B) ? b0 + p.nb : p.B;
+    for (long long bb = b0; bb < b1; bb += UB) {
+        // issue every load first
+        T st[UB][VEC * L];
+        T xv[UB][VEC];
 #pragma unroll
-    for (int c = 0; c < VEC; ++c) {
-        // cat = [state | x]; taps are cat[L+1-W .. L]
-        float acc = bf[c];
+        for (int u = 0; u < UB; ++u) {
+            if (bb + u < b1) {
+                const char* sp = p.state + ((bb + u) * p.ssb + (long long)d0 * L) * E::kBytes;
 #pragma unroll
-        for (int w = 0; w < W; ++w) {
-            const int i = L + 1 - W + w;
-            const float v = (i < L) ? E::to_float(st[c * L + i]) : E::to_float(xv[c]);
-            acc = fmaf(wf[c][w], v, acc);
+                for (int j = 0; j < L; ++j)
+                    reinterpret_cast<uint4*>(st[u])[j] = *reinterpret_cast<const uint4*>(sp + j * 16);
+                *reinterpret_cast<uint4*>(xv[u]) = ld_vec(p.x + ((bb + u) * p.sxb + d0) * E::kBytes);
+            }
         }
-        if (p.act) acc = silu1<E::kPreciseSilu>(acc);
-        if (p.residual) acc = E::to_float(E::from_float(acc)) + E::to_float(xv[c]);
-        yv[c] = E::from_float(acc);
 #pragma unroll
-        for (int j = 0; j + 1 < L; ++j) ns[c * L + j] = st[c * L + j + 1];
-        ns[c * L + L - 1] = xv[c];
+        for (int u = 0; u < UB; ++u) {
+            if (bb + u < b1) {
+                T ns[VEC * L];
+                T yv[VEC];
+#pragma unroll
+                for (int c = 0; c < VEC; ++c) {
+                    // cat = [state | x]; taps are cat[L+1-W .. L]
+                    float acc = bf[c];
+#pragma unroll
+                    for (int w = 0; w < W; ++w) {
+                        const int i = L + 1 - W + w;
+                        const float v = (i < L) ? E::to_float(st[u][c * L + i]) : E::to_float(xv[u][c]);
+                        acc = fmaf(wf[c][w], v, acc);
+                    }
+                    if (p.act) acc = silu1<E::kPreciseSilu>(acc);
+                    if (p.residual) acc = E::to_float(E::from_float(acc)) + E::to_float(xv[u][c]);
+                    yv[c] = E::from_float(acc);
+#pragma unroll
+                    for (int j = 0; j + 1 < L; ++j) ns[c * L + j] = st[u][c * L + j + 1];
+                    ns[c * L + L - 1] = xv[u][c];
+                }
+                char* spw = p.state + ((bb + u) * p.ssb + (long long)d0 * L) * E::kBytes;
+#pragma unroll
+                for (int j = 0; j < L; ++j)
+                    *reinterpret_cast<uint4*>(spw + j * 16) = reinterpret_cast<const uint4*>(ns)[j];
+                st_vec(p.y + ((bb + u) * p.syb + d0) * E::kBytes, *reinterpret_cast<const uint4*>(yv));
+            }
+        }
     }
-    char* spw = p.state + (b * p.ssb + (long long)d0 * L) * E::kBytes;
-#pragma unroll
-    for (int j = 0; j < L; ++j) *reinterpret_cast<uint4*>(spw + j * 16) = reinterpret_cast<const uint4*>(ns)[j];
-    st_vec(p.y + (b * p.syb + d0) * E::kBytes, *reinterpret_cast<const uint4*>(yv));
 }
 
 // Scalar kernel: any strides, any state_len >= width-1, shifting or circular state.
@@ -175,6 +228,12 @@ UParams make_params(const vc1d_update_args& a) {
     p.residual = a.residual;
     p.nvec = 0;
     p.total = 0;
+    p.nb = 1;
+    p.w_fast = (a.wdtype == a.dtype && a.w_stride_w == 1 && a.w_stride_d == a.width &&
+                (reinterpret_cast<uintptr_t>(a.weight) & 15u) == 0 &&
+                (a.bias == nullptr || (reinterpret_cast<uintptr_t>(a.bias) & 15u) == 0))
+                   ? 1
+                   : 0;
     return p;
 }
 
@@ -215,7 +274,16 @@ cudaError_t launch_update_vec(const vc1d_update_args& a, cudaStream_t s) {
     UParams p = make_params(a);
     const int vec = 16 / elem_bytes(a.dtype);
     p.nvec = a.dim / vec;
-    p.total = (long long)a.batch * p.nvec;
+    // a thread keeps its channels' weights in registers and walks nb sequences; small batches keep
+    // one sequence per thread so that the grid still fills the GPU
+    const long long threads1 = (long long)a.batch * p.nvec;
+    long long nb = threads1 / ((long long)sm_count() * 2048);
+    if (nb < 1) nb = 1;
+    if (nb > 16) nb = 16;
+    if (a.reserved > 0) nb = a.reserved;  // tuning override
+    p.nb = (int)nb;
+    const long long ngroups = (a.batch + nb - 1) / nb;
+    p.total = ngroups * p.nvec;
     int block = a.block_threads > 0 ? a.block_threads : 128;
     if (block > 256) block = 256;
     block = (block + 31) / 32 * 32;
