@@ -120,11 +120,8 @@ typedef struct vc1d_prefill_args {
     int32_t tma_stages;          /* ring depth, 2..8 */
     int32_t tma_ctas_per_sm;     /* persistent CTAs per SM */
     int32_t tma_slab_bytes;      /* channel slab of a tile: 128 or 256 bytes */
-    int32_t tma_rows_per_thread; /* 2, 4 or 8 consecutive rows per thread and tile */
-    int32_t tma_vec_bytes;       /* bytes of channels per thread: 8 or 16 */
-    int32_t tma_direct_store;    /* 1: streaming stores from registers (default), 2: bulk tensor stores */
-    int32_t tma_debug_copy;      /* 1: skip the arithmetic and store tiles as loaded (bandwidth probe) */
-    int32_t reserved;
+    int32_t tma_rows_per_thread; /* 4 or 8 consecutive rows per thread and tile */
+    int32_t reserved[4];
 } vc1d_prefill_args;
 
 VC1D_API int vc1d_prefill(const vc1d_prefill_args* args, void* stream);

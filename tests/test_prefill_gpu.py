@@ -305,17 +305,12 @@ def test_tma_kernel_multi_tile(B, T, D, W, dtype):
     # without residual the all-masked tiles take the no-load path; forced narrow / wide slabs agree
     y0 = V.causal_conv1d_fn(xd, dev(w), dev(b), activation="silu", attention_mask=dev(m), kernel="tma")
     assert_close_to_oracle(y0, O.causal_conv1d_ref(x, w, b, "silu", attention_mask=m), "tma no residual")
-    # every shape of the kernel: slab width, bytes and rows per thread, bulk / streaming stores, ring depth
+    # every shape of the kernel: slab width, rows per thread, ring depth, grid size
     for slab in (128, 256):
-        for vb, direct, rpt, stages in ((8, 2, 8, 3), (8, 1, 8, 2), (16, 2, 8, 4), (16, 1, 8, 3), (8, 2, 4, 3),
-                                        (8, 1, 2, 5), (8, 2, 2, 2)):
+        for rpt, stages, per_sm in ((8, 3, 3), (8, 2, 1), (4, 3, 3), (4, 5, 6), (8, 8, 2)):
             ys = V.causal_conv1d_fn(xd, dev(w), dev(b), activation="silu", attention_mask=dev(m), kernel="tma",
-                                    tma=dict(slab_bytes=slab, vec_bytes=vb, direct_store=direct, rows_per_thread=rpt,
-                                             stages=stages))
-            assert torch.equal(ys, y0), (slab, vb, direct, rpt, stages)
-    y_res = V.causal_conv1d_fn(xd, dev(w), dev(b), activation="silu", attention_mask=dev(m), kernel="tma",
-                               residual=True, tma=dict(direct_store=2))
-    assert torch.equal(y_res, y)
+                                    tma=dict(slab_bytes=slab, rows_per_thread=rpt, stages=stages, ctas_per_sm=per_sm))
+            assert torch.equal(ys, y0), (slab, rpt, stages, per_sm)
     y_cl = V.causal_conv1d_fn(xd, dev(w), dev(b), activation="silu", attention_mask=dev(m), kernel="channel_last")
     assert torch.equal(y_cl, y0)
     torch.cuda.synchronize()

@@ -77,10 +77,7 @@ class PrefillArgs(C.Structure):
         ("tma_ctas_per_sm", C.c_int32),
         ("tma_slab_bytes", C.c_int32),
         ("tma_rows_per_thread", C.c_int32),
-        ("tma_vec_bytes", C.c_int32),
-        ("tma_direct_store", C.c_int32),
-        ("tma_debug_copy", C.c_int32),
-        ("reserved", C.c_int32),
+        ("reserved", C.c_int32 * 4),
     ]
 
 

@@ -87,7 +87,6 @@ cudaError_t launch_prefill_tma(const vc1d_prefill_args& a, cudaStream_t s) {
                      : 0;
     p.state_len = a.state_len;
     p.stages = 0;
-    p.debug_copy = a.tma_debug_copy ? 1 : 0;
     switch (a.dtype) {
         case VC1D_F32: return tma::launch_dt<VC1D_F32>(a, p, s);
         case VC1D_BF16: return tma::launch_dt<VC1D_BF16>(a, p, s);

@@ -12,19 +12,19 @@
 // j, j + G, j + 2G, ... of that slab, so neighbouring CTAs touch neighbouring rows and the
 // (W-1)-row halo of a tile is an L2 hit.
 //
-// Pipeline.  One producer warp and the consumer warps share a ring of kStages buffers guarded
-// by full/done mbarriers.  The producer scans the tile's mask rows (32 lanes, a few loads
-// each), stores them as floats beside the data and classifies the tile: all rows valid, mixed,
-// or nothing to read -- in the last case no bytes are requested from HBM at all.  Bytes in
-// flight are set by the ring depth, not by registers.  Each consumer thread owns VB bytes of
-// channels (8 or 16) and kRowsPerThread consecutive rows: a register sliding window over
-// shared memory, fp32x2 FMAs, fused mask / bias / SiLU / residual epilogue.  Results overwrite
-// the input rows in place and leave by one cp.async.bulk.tensor store per tile, issued by the
-// producer warp, so no consumer warp ever waits on HBM in either direction; the store also
-// clips the ragged last tile in time and in channels.
+// Pipeline.  One producer warp and eight consumer warps share a ring of stages guarded by
+// full/done mbarriers.  The producer fetches the tile's mask rows two tiles ahead (32 lanes, a
+// few loads each) and classifies the tile: all rows valid, mixed, or nothing to read.  A tile
+// with nothing to read never enters the ring: no byte of it is requested from HBM and the
+// producer warp stores its outputs, act(bias), itself.  Bytes in flight are set by the ring
+// depth, not by registers.  Each consumer thread owns 8 bytes of channels and 8 consecutive
+// rows of the tile: a register window over shared memory rotated by index, fp32x2 FMAs, fused
+// mask / bias / SiLU / residual epilogue, streaming 8-byte stores (a warp writes 256 contiguous
+// bytes per row).  No consumer warp waits on HBM for its input, and none waits for another
+// warp: the only synchronisation is the pair of mbarriers per stage.
 //
-// Every mbarrier wait is bounded; on expiry the CTA records the event in a device counter
-// (read by vc1d_tma_timeouts()) and leaves its loops.
+// Every mbarrier wait is bounded; on expiry the warp records the event in a device counter
+// (read by vc1d_tma_timeouts()) and leaves its loop.
 #pragma once
 
 #include <cuda.h>
@@ -41,10 +41,10 @@ namespace tma {
 constexpr int kMaxStages = 8;
 constexpr unsigned kSpinLimit = 1u << 24;
 
-enum : int { TILE_EMPTY = 0, TILE_MIXED = 1, TILE_FULL = 2 };
+enum : int { TILE_EMPTY = 0, TILE_MIXED = 1, TILE_FULL = 2, TILE_END = 3 };
 
 struct TmaParams {
-    char* y;        // for direct stores
+    char* y;
     long long syb, syt;
     const char* x;  // for the final-state pass
     const char* res;
@@ -65,7 +65,6 @@ struct TmaParams {
     int res_is_x;
     int state_len;
     int stages;      // ring depth (2..kMaxStages)
-    int debug_copy;  // experiment: consumers do nothing, the tile is stored as loaded
 };
 
 // ---- raw PTX wrappers -----------------------------------------------------------------------
@@ -106,11 +105,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
         : "memory");
-}
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int c0, int c1, int c2, uint32_t src) {
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
-                 ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(src)
-                 : "memory");
 }
 __device__ __forceinline__ float lds_f32(uint32_t a) {
     float v;
@@ -178,12 +172,12 @@ struct Geometry {
     static constexpr int kSlabElems = SLAB_BYTES / Elem<DT>::kBytes;
     static constexpr int kStageBytes = ((kBoxRows * kRowBytes + 127) / 128) * 128;
     static constexpr int kMaskFloats = ((kBoxRows + 31) / 32) * 32;
-    // layout for S stages: stages | mask floats | full[S], done[S] | {class, b, t0}[S], abort, producer-abort
+    // layout for S stages: stages | mask floats | full[S], done[S] | {class, b, t0}[S], abort
     __host__ __device__ static constexpr int off_mask(int S) { return S * kStageBytes; }
     __host__ __device__ static constexpr int off_bars(int S) { return off_mask(S) + S * kMaskFloats * 4; }
     __host__ __device__ static constexpr int off_flags(int S) { return off_bars(S) + 2 * S * 8; }
     __host__ __device__ static constexpr int smem_bytes(int S) {
-        return off_flags(S) + (3 * S + 2) * 4 + 128 /* base alignment slack */;
+        return off_flags(S) + (3 * S + 1) * 4 + 128 /* base alignment slack */;
     }
 };
 
@@ -244,10 +238,9 @@ __device__ __forceinline__ void apply_mask(float2 (&f)[Slice<DT, VB>::kPairs], f
     }
 }
 
-// The R rows of one thread in one tile.  GENERAL adds the per-row mask and the residual.  Results
-// go back into the stage (DIRECT = false, a bulk tensor store follows) or straight to global memory
-// with streaming stores (DIRECT = true; yrow is the address of the thread's first output row).
-template <int DT, int W, int VB, int RPT, bool ACT, bool GENERAL, bool DIRECT, int ROW_BYTES>
+// The R rows of one thread in one tile.  GENERAL adds the per-row mask and the residual.  Results go
+// straight to global memory with streaming stores (yrow is the address of the thread's first row).
+template <int DT, int W, int VB, int RPT, bool ACT, bool GENERAL, int ROW_BYTES>
 __device__ __forceinline__ void process_rows(uint32_t trow, uint32_t mk_addr, const TmaParams& p, bool mixed,
                                              const char* rb, char* yrow, int tfirst, int rows_ok,
                                              float2 (&hist)[W - 1 > 0 ? W - 1 : 1][Slice<DT, VB>::kPairs],
@@ -302,11 +295,7 @@ __device__ __forceinline__ void process_rows(uint32_t trow, uint32_t mk_addr, co
         }
         uint32_t outw[NW];
         S::pack(acc, outw);
-        if constexpr (DIRECT) {
-            if (rows_ok > k) S::stg(yrow + (long long)k * p.syt, outw);
-        } else {
-            S::sts(slot, outw);
-        }
+        if (rows_ok > k) S::stg(yrow + (long long)k * p.syt, outw);
         if constexpr (H > 0) {
 #pragma unroll
             for (int q = 0; q < NP; ++q) hist[k % H][q] = cur[q];
@@ -330,10 +319,9 @@ __device__ __forceinline__ void fetch_mask(const TmaParams& p, int b, int t0, in
     }
 }
 
-template <int DT, int W, int SLAB_BYTES, int VB, int RPT, bool ACT, bool DIRECT>
+template <int DT, int W, int SLAB_BYTES, int VB, int RPT, bool ACT>
 __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads)
-    k_prefill_tma(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
-                  const TmaParams p) {
+    k_prefill_tma(const __grid_constant__ CUtensorMap tmap_x, const TmaParams p) {
     using E = Elem<DT>;
     using S = Slice<DT, VB>;
     using G = Geometry<DT, W, SLAB_BYTES, VB, RPT>;
@@ -350,9 +338,8 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
     const int kStages = p.stages;  // ring depth of this launch
     const uint32_t mask_base = base + G::off_mask(kStages);
     const uint32_t bars = base + G::off_bars(kStages);    // full[s] at bars + 8 s, done[s] at bars + 8 (kStages + s)
-    const uint32_t flags = base + G::off_flags(kStages);  // per stage {class, sequence, first row}; then abort, producer-abort
+    const uint32_t flags = base + G::off_flags(kStages);  // per stage {class, sequence, first row}; then the abort flag
     const uint32_t abort_c = flags + 12 * kStages;
-    const uint32_t abort_p = abort_c + 4;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -368,118 +355,114 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
             mbar_init(bars + 8 * (kStages + s), G::kConsumerWarps);  // done: one arrive per consumer warp
         }
         sts_s32(abort_c, 0);  // a consumer wait expired
-        sts_s32(abort_p, 0);  // a producer wait expired
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
     if (warp == G::kConsumerWarps) {
         // ================================ producer warp ==================================
-        // Iteration i issues the load of tile i.  With bulk stores it then waits for the consumers
-        // of tile i-(S-1) and issues that tile's store; the stage of tile i held tile i-S, whose
-        // store was issued in the previous iteration and is the newest bulk group, so
-        // wait_group.read 0 frees the stage.  With direct stores the stage is free as soon as the
-        // consumers of tile i-S have arrived on done[s].  The mask of tile i+2 is fetched while
-        // tile i is being handled, so its latency never sits between two loads.
-        // Three mask buffers rotate roles (the loop is unrolled by three): the values fetched for
-        // tile i+2 are not touched -- not even moved -- until iteration i+2.
-        const int n_iter = DIRECT ? n_my : n_my + kStages - 1;
-        TileIter it_fetch, it_load, it_store;  // tiles i+2 (mask fetch), i (load), i-(S-1) (store)
+        // Walks the CTA's tiles in order.  A tile with something to read takes the next ring slot
+        // (after the consumers of the slot's previous tile have arrived on done[s]) and is loaded
+        // by one bulk tensor copy.  A tile in which every tap of every row is masked never enters
+        // the ring: its outputs are act(bias), and this warp -- one lane per 8 bytes of the slab
+        // row -- stores them itself.  After the last tile an END marker takes a slot.  The mask of
+        // tile i+2 is fetched while tile i is handled, in three register buffers that rotate roles
+        // (the loop is unrolled by three), so the fetched values are not touched until needed.
+        using S8 = Slice<DT, 8>;
+        constexpr int NE8 = S8::kElems;
+        const int pd0 = slab_ch0 + lane * NE8;  // this lane's channels when it stores a masked-out tile
+        const bool p_ok = lane * 8 < SLAB_BYTES && pd0 < p.D;
+        uint32_t pconst[2] = {0u, 0u};
+        if (p.mask != nullptr && p_ok) {
+            float2 c[S8::kPairs];
+#pragma unroll
+            for (int q = 0; q < S8::kPairs; ++q) {
+                float v[2] = {0.f, 0.f};
+                if (p.bias != nullptr) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e)
+                        v[e] = (p.wdtype == VC1D_F32)
+                                   ? __ldg(reinterpret_cast<const float*>(p.bias) + pd0 + 2 * q + e)
+                                   : E::to_float(__ldg(reinterpret_cast<const typename E::type*>(p.bias) + pd0 + 2 * q + e));
+                }
+                c[q] = make_float2(v[0], v[1]);
+                if (ACT) c[q] = silu2<E::kPreciseSilu>(c[q]);
+            }
+            S8::pack(c, pconst);
+        }
+        TileIter it_fetch, it_load;  // tiles i+2 (mask fetch) and i (load)
         it_load.init(j0, p.n_ttile, stride);
-        it_store = it_load;
         it_fetch = it_load;
-        int s_load = 0, s_store = 0;            // ring slots of the load and of the store
-        uint32_t ph_load = 0, ph_store = 0;     // how often each has wrapped, mod 2
+        int s_ring = 0, n_ring = 0;  // next ring slot, tiles put into the ring so far
+        uint32_t ph_ring = 0;        // how often the ring has wrapped, mod 2
+        // claim the next slot: wait until its previous tile has been consumed
+        auto claim = [&]() -> bool {
+            if (n_ring >= kStages) {
+                const bool ok = mbar_wait(bars + 8 * (kStages + s_ring), ph_ring ^ 1);
+                if (!ok && lane == 0) atomicAdd(p.timeouts, 1u);
+                if (!ok) return false;
+            }
+            return true;
+        };
+        auto advance = [&]() {
+            ++n_ring;
+            if (++s_ring == kStages) {
+                s_ring = 0;
+                ph_ring ^= 1;
+            }
+        };
         auto step = [&](int i, float (&mk_use)[NMK], float (&mk_fill)[NMK]) -> bool {
-            if (i < n_my) {
-                const int s = s_load;
-                if (p.mask != nullptr && i + 2 < n_my) {
-                    it_fetch.next();
-                    fetch_mask<NMK, G::kBoxRows, H, G::kTileRows>(p, it_fetch.b, it_fetch.t0(G::kTileRows), lane, mk_fill);
-                }
-                if (i >= kStages) {
-                    bool ok = true;
-                    if (DIRECT) {
-                        ok = mbar_wait(bars + 8 * (kStages + s), ph_load ^ 1);
-                        if (!ok && lane == 0) {
-                            atomicAdd(p.timeouts, 1u);
-                            sts_s32(abort_p, 1);
-                        }
-                    } else if (lane == 0) {
-                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            if (p.mask != nullptr && i + 2 < n_my) {
+                it_fetch.next();
+                fetch_mask<NMK, G::kBoxRows, H, G::kTileRows>(p, it_fetch.b, it_fetch.t0(G::kTileRows), lane, mk_fill);
+            }
+            const int b = it_load.b;
+            const int t0 = it_load.t0(G::kTileRows);
+            int cls = TILE_FULL;
+            if (p.mask != nullptr) {
+                bool any = false, all_one = true;
+#pragma unroll
+                for (int q = 0; q < NMK; ++q) {
+                    const int jrow = lane + 32 * q;
+                    const int t = t0 - H + jrow;
+                    if (jrow < G::kBoxRows && t >= 0 && t < p.T) {
+                        any |= (mk_use[q] != 0.0f);
+                        all_one &= (mk_use[q] == 1.0f);
                     }
-                    __syncwarp();
-                    if (!ok) return false;
                 }
-                const int b = it_load.b;
-                const int t0 = it_load.t0(G::kTileRows);
-                int cls = TILE_FULL;
-                if (p.mask != nullptr) {
-                    bool any = false, all_one = true;
+                any = __any_sync(0xffffffffu, any);
+                all_one = __all_sync(0xffffffffu, all_one);
+                cls = all_one ? TILE_FULL : ((any || !p.skip || p.res != nullptr) ? TILE_MIXED : TILE_EMPTY);
+            }
+            if (cls == TILE_EMPTY) {
+                if (p_ok) {
+                    char* yrow = p.y + (long long)b * p.syb + (long long)t0 * p.syt + (long long)pd0 * E::kBytes;
+                    const int nrows = min(G::kTileRows, p.T - t0);
+                    for (int r = 0; r < nrows; ++r) S8::stg(yrow + (long long)r * p.syt, pconst);
+                }
+            } else {
+                if (!claim()) return false;
+                const int s = s_ring;
+                if (cls == TILE_MIXED) {
 #pragma unroll
                     for (int q = 0; q < NMK; ++q) {
                         const int jrow = lane + 32 * q;
-                        const int t = t0 - H + jrow;
-                        if (jrow < G::kBoxRows) {
-                            sts_f32(mask_base + (s * G::kMaskFloats + jrow) * 4, mk_use[q]);
-                            if (t >= 0 && t < p.T) {
-                                any |= (mk_use[q] != 0.0f);
-                                all_one &= (mk_use[q] == 1.0f);
-                            }
-                        }
+                        if (jrow < G::kBoxRows) sts_f32(mask_base + (s * G::kMaskFloats + jrow) * 4, mk_use[q]);
                     }
-                    any = __any_sync(0xffffffffu, any);
-                    all_one = __all_sync(0xffffffffu, all_one);
-                    cls = all_one ? TILE_FULL : ((any || !p.skip || p.res != nullptr) ? TILE_MIXED : TILE_EMPTY);
-                    __syncwarp();
                 }
+                __syncwarp();
                 if (lane == 0) {
                     sts_s32(flags + 12 * s, cls);
                     sts_s32(flags + 12 * s + 4, b);
                     sts_s32(flags + 12 * s + 8, t0);
                     const uint32_t full = bars + 8 * s;
-                    if (cls != TILE_EMPTY) {
-                        mbar_arrive_expect_tx(full, G::kBoxRows * G::kRowBytes);
-                        tma_load_3d(base + s * G::kStageBytes, &tmap_x, slab_ch0, t0 - H, b, full);
-                    } else {
-                        mbar_arrive(full);
-                    }
+                    mbar_arrive_expect_tx(full, G::kBoxRows * G::kRowBytes);
+                    tma_load_3d(base + s * G::kStageBytes, &tmap_x, slab_ch0, t0 - H, b, full);
                 }
                 __syncwarp();
-                it_load.next();
-                if (++s_load == kStages) {
-                    s_load = 0;
-                    ph_load ^= 1;
-                }
+                advance();
             }
-            if (!DIRECT) {
-                const int j = i - (kStages - 1);
-                if (j >= 0 && j < n_my) {
-                    const int s = s_store;
-                    bool ok = mbar_wait(bars + 8 * (kStages + s), ph_store);
-                    if (!ok) {
-                        // recorded only: the consumers decide among themselves when to stop (they share a barrier)
-                        if (lane == 0) {
-                            atomicAdd(p.timeouts, 1u);
-                            sts_s32(abort_p, 1);
-                        }
-                    } else if (lds_s32(abort_c)) {
-                        ok = false;
-                    } else if (lane == 0) {
-                        // output row t sits in box row t - t0 + H: the store starts H rows into the stage
-                        tma_store_3d(&tmap_y, slab_ch0, it_store.t0(G::kTileRows), it_store.b,
-                                     base + s * G::kStageBytes + H * G::kRowBytes);
-                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                    }
-                    __syncwarp();
-                    if (!ok) return false;
-                    it_store.next();
-                    if (++s_store == kStages) {
-                        s_store = 0;
-                        ph_store ^= 1;
-                    }
-                }
-            }
+            it_load.next();
             return true;
         };
         float mk_a[NMK], mk_b[NMK], mk_c[NMK];
@@ -491,12 +474,20 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
             it_fetch.next();
             fetch_mask<NMK, G::kBoxRows, H, G::kTileRows>(p, it_fetch.b, it_fetch.t0(G::kTileRows), lane, mk_b);
         }
-        for (int i = 0; i < n_iter; i += 3) {
-            if (!step(i, mk_a, mk_c)) break;
-            if (i + 1 < n_iter && !step(i + 1, mk_b, mk_a)) break;
-            if (i + 2 < n_iter && !step(i + 2, mk_c, mk_b)) break;
+        bool live = true;
+        for (int i = 0; live && i < n_my; i += 3) {
+            live = step(i, mk_a, mk_c);
+            if (live && i + 1 < n_my) live = step(i + 1, mk_b, mk_a);
+            if (live && i + 2 < n_my) live = step(i + 2, mk_c, mk_b);
         }
-        if (!DIRECT && lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        // END marker: the consumers leave when they meet it
+        if (live && claim()) {
+            if (lane == 0) {
+                sts_s32(flags + 12 * s_ring, TILE_END);
+                mbar_arrive(bars + 8 * s_ring);
+            }
+            __syncwarp();
+        }
     } else {
         // ================================ consumer warps =================================
         const int grp = threadIdx.x / LPR;  // row group inside the tile
@@ -508,94 +499,50 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         float2 wp[W][NP];
         float2 bp[NP];
         load_weights<DT, W, VB>(p, d0, ch_ok, wp, bp);
-        // value of a row whose W taps are all masked: act(bias)
-        uint32_t const_row[NW];
-        {
-            float2 c[NP];
-#pragma unroll
-            for (int q = 0; q < NP; ++q) c[q] = ACT ? silu2<E::kPreciseSilu>(bp[q]) : bp[q];
-            S::pack(c, const_row);
-        }
         const bool general_kernel = (p.mask != nullptr) || (p.res != nullptr);
 
         int s = -1;
         uint32_t ph = 1;
-        for (int i = 0; i < n_my; ++i) {
+        for (;;) {
             if (++s == kStages) s = 0;
             if (s == 0) ph ^= 1;
-            const bool ok = mbar_wait(bars + 8 * s, ph);
-            if (!ok) {
-                if (lane == 0) {
-                    atomicAdd(p.timeouts, 1u);
-                    sts_s32(abort_c, 1);
-                }
-                if (DIRECT) break;  // no barrier is shared with the other warps: each leaves on its own
+            if (!mbar_wait(bars + 8 * s, ph)) {
+                if (lane == 0) atomicAdd(p.timeouts, 1u);
+                break;  // no barrier is shared with the other warps: each leaves on its own
             }
-            // box row of time t is (t - t0 + H); this thread reads box rows rbase .. rbase+R+H-1 and,
-            // with bulk stores, writes its R results over box rows rbase+H .. rbase+R+H-1
+            const int cls = lds_s32(flags + 12 * s);
+            if (cls == TILE_END) break;
+            // box row of time t is (t - t0 + H); this thread reads box rows rbase .. rbase+R+H-1
             const uint32_t trow = base + s * G::kStageBytes + rbase * G::kRowBytes + cl * VB;
             const uint32_t mk_addr = mask_base + (s * G::kMaskFloats + rbase) * 4;
-            int cls = TILE_FULL;
-            if (general_kernel) cls = lds_s32(flags + 12 * s);
             const bool mixed = (cls == TILE_MIXED);
-            const bool need_pos = DIRECT || (p.res != nullptr && !p.res_is_x);
-            int b = 0, tfirst = 0;
-            if (need_pos) {
-                b = lds_s32(flags + 12 * s + 4);
-                tfirst = lds_s32(flags + 12 * s + 8) + rbase;
-            }
+            const int b = lds_s32(flags + 12 * s + 4);
+            const int tfirst = lds_s32(flags + 12 * s + 8) + rbase;
 
-            if (p.debug_copy) {
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bars + 8 * (kStages + s));
-                continue;
-            }
             float2 hist[H > 0 ? H : 1][NP];
-            if (cls != TILE_EMPTY) {
 #pragma unroll
-                for (int w = 0; w < H; ++w) {
-                    uint32_t raw[NW];
-                    S::lds(trow + w * G::kRowBytes, raw);
-                    S::unpack(raw, hist[w]);
-                    if (mixed) apply_mask<DT, VB>(hist[w], lds_f32(mk_addr + w * 4), p.skip);
-                }
+            for (int w = 0; w < H; ++w) {
+                uint32_t raw[NW];
+                S::lds(trow + w * G::kRowBytes, raw);
+                S::unpack(raw, hist[w]);
+                if (mixed) apply_mask<DT, VB>(hist[w], lds_f32(mk_addr + w * 4), p.skip);
             }
-            if (!DIRECT) {
-                // The first H rows a group reads are the last rows the group above it overwrites:
-                // nobody writes until everybody holds its history.  The same barrier makes an expired
-                // wait a collective decision, so no warp is left alone at it.
-                asm volatile("bar.sync 1, %0;" ::"n"(G::kConsumerThreads) : "memory");
-                if (lds_s32(abort_c)) break;
-            }
-            // rows of this thread that exist in the output (streaming stores only; bulk stores clip)
-            int rows_ok = 0;
-            if (DIRECT && ch_ok) rows_ok = min(R, max(0, p.T - tfirst));
-            char* yrow = nullptr;
-            if (DIRECT) yrow = p.y + (long long)b * p.syb + (long long)tfirst * p.syt + (long long)d0 * E::kBytes;
+            // rows of this thread that exist in the output
+            const int rows_ok = ch_ok ? min(R, max(0, p.T - tfirst)) : 0;
+            char* yrow = p.y + (long long)b * p.syb + (long long)tfirst * p.syt + (long long)d0 * E::kBytes;
             const char* rb = nullptr;
             if (p.res != nullptr && !p.res_is_x && ch_ok)
                 rb = p.res + (long long)b * p.srb + (long long)d0 * E::kBytes;
 
-            if (cls == TILE_EMPTY) {
-#pragma unroll
-                for (int k = 0; k < R; ++k) {
-                    if (DIRECT) {
-                        if (rows_ok > k) S::stg(yrow + (long long)k * p.syt, const_row);
-                    } else {
-                        S::sts(trow + (H + k) * G::kRowBytes, const_row);
-                    }
-                }
-            } else if (cls == TILE_FULL && p.res == nullptr) {
-                process_rows<DT, W, VB, RPT, ACT, false, DIRECT, G::kRowBytes>(trow, mk_addr, p, false, nullptr, yrow, tfirst,
-                                                                               rows_ok, hist, wp, bp);
+            if (!general_kernel || (cls == TILE_FULL && p.res == nullptr)) {
+                process_rows<DT, W, VB, RPT, ACT, false, G::kRowBytes>(trow, mk_addr, p, false, nullptr, yrow, tfirst,
+                                                                       rows_ok, hist, wp, bp);
             } else {
-                process_rows<DT, W, VB, RPT, ACT, true, DIRECT, G::kRowBytes>(trow, mk_addr, p, mixed, rb, yrow, tfirst,
-                                                                              rows_ok, hist, wp, bp);
+                process_rows<DT, W, VB, RPT, ACT, true, G::kRowBytes>(trow, mk_addr, p, mixed, rb, yrow, tfirst,
+                                                                      rows_ok, hist, wp, bp);
             }
-            // bulk stores read the results through the async proxy; they were written through the generic one
-            if (!DIRECT) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
-            if (lane == 0) mbar_arrive(bars + 8 * (kStages + s));
+            if (lane == 0) mbar_arrive(bars + 8 * (kStages + s));  // the stage has been read
         }
 
         // ---- final state: right-aligned last state_len masked inputs (model/model.py:470-489) ----
@@ -633,7 +580,7 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeFn encode_fn();
 
-template <int DT, int W, int SLAB_BYTES, int VB, int RPT, bool ACT, bool DIRECT>
+template <int DT, int W, int SLAB_BYTES, int VB, int RPT, bool ACT>
 cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cudaStream_t s) {
     using G = Geometry<DT, W, SLAB_BYTES, VB, RPT>;
     const int eb = Elem<DT>::kBytes;
@@ -650,11 +597,11 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     const CUtensorMapDataType dt = (DT == VC1D_F32)    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                    : (DT == VC1D_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    const cuuint64_t dims[3] = {(cuuint64_t)a.dim, (cuuint64_t)a.seqlen, (cuuint64_t)a.batch};
-    const cuuint32_t estr[3] = {1u, 1u, 1u};
-    // input box: tile rows plus the W-1 rows above; output box: the tile rows
-    CUtensorMap tmap_x, tmap_y;
+    // input box: the tile's rows plus the W-1 rows above them
+    CUtensorMap tmap_x;
     {
+        const cuuint64_t dims[3] = {(cuuint64_t)a.dim, (cuuint64_t)a.seqlen, (cuuint64_t)a.batch};
+        const cuuint32_t estr[3] = {1u, 1u, 1u};
         cuuint64_t st[2] = {(cuuint64_t)a.x_stride_t * eb, (cuuint64_t)a.x_stride_b * eb};
         // an extent of 1 makes its stride irrelevant, but the encoder still wants a legal value
         if (a.seqlen == 1) st[0] = (cuuint64_t)a.dim * eb;
@@ -665,17 +612,6 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cudaErrorNotSupported;  // the caller falls back to the direct kernel
-    }
-    {
-        cuuint64_t st[2] = {(cuuint64_t)a.y_stride_t * eb, (cuuint64_t)a.y_stride_b * eb};
-        if (a.seqlen == 1) st[0] = (cuuint64_t)a.dim * eb;
-        if (a.batch == 1) st[1] = st[0] * (cuuint64_t)a.seqlen;
-        if (st[0] % 16 != 0 || st[1] % 16 != 0) return cudaErrorNotSupported;
-        const cuuint32_t box[3] = {(cuuint32_t)slab_ch, (cuuint32_t)G::kTileRows, 1u};
-        const CUresult r = enc(&tmap_y, dt, 3, a.y, dims, st, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return cudaErrorNotSupported;
     }
     int stages = a.tma_stages > 0 ? a.tma_stages : 3;
     if (stages < 2) stages = 2;
@@ -691,7 +627,7 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
         int dev = 0;
         cudaGetDevice(&dev);
         if (dev < 0 || dev >= 64 || granted[dev].load(std::memory_order_acquire) < smem) {
-            const cudaError_t e = cudaFuncSetAttribute(k_prefill_tma<DT, W, SLAB_BYTES, VB, RPT, ACT, DIRECT>,
+            const cudaError_t e = cudaFuncSetAttribute(k_prefill_tma<DT, W, SLAB_BYTES, VB, RPT, ACT>,
                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
             if (e != cudaSuccess) return e;
             if (dev >= 0 && dev < 64) granted[dev].store(smem, std::memory_order_release);
@@ -705,29 +641,19 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     p.ctas_per_slab = (int)g;
     const dim3 grid((unsigned)n_slab, (unsigned)g);
     note_launch("tma");
-    k_prefill_tma<DT, W, SLAB_BYTES, VB, RPT, ACT, DIRECT><<<grid, G::kThreads, smem, s>>>(tmap_x, tmap_y, p);
+    k_prefill_tma<DT, W, SLAB_BYTES, VB, RPT, ACT><<<grid, G::kThreads, smem, s>>>(tmap_x, p);
     return cudaGetLastError();
-}
-
-template <int DT, int W, int SLAB_BYTES, int VB, int RPT>
-cudaError_t launch_store(const vc1d_prefill_args& a, const TmaParams& p, cudaStream_t s) {
-    const bool act = a.activation == VC1D_ACT_SILU;
-    // streaming stores from registers by default: one pass fewer through shared memory, and the
-    // stage is free as soon as it has been read; 2 selects bulk tensor stores
-    if (a.tma_direct_store != 2)
-        return act ? launch_kernel<DT, W, SLAB_BYTES, VB, RPT, true, true>(a, p, s)
-                   : launch_kernel<DT, W, SLAB_BYTES, VB, RPT, false, true>(a, p, s);
-    return act ? launch_kernel<DT, W, SLAB_BYTES, VB, RPT, true, false>(a, p, s)
-               : launch_kernel<DT, W, SLAB_BYTES, VB, RPT, false, false>(a, p, s);
 }
 
 template <int DT, int W, int SLAB_BYTES>
 cudaError_t launch_slab(const vc1d_prefill_args& a, const TmaParams& p, cudaStream_t s) {
-    // 8 bytes of channels and 8 rows per thread by default; the other shapes exist for tuning
-    if (a.tma_vec_bytes == 16) return launch_store<DT, W, SLAB_BYTES, 16, 8>(a, p, s);
-    if (a.tma_rows_per_thread == 4) return launch_store<DT, W, SLAB_BYTES, 8, 4>(a, p, s);
-    if (a.tma_rows_per_thread == 2) return launch_store<DT, W, SLAB_BYTES, 8, 2>(a, p, s);
-    return launch_store<DT, W, SLAB_BYTES, 8, 8>(a, p, s);
+    // 8 bytes of channels and 8 rows per thread; 4 rows (half-height tiles) on request
+    const bool act = a.activation == VC1D_ACT_SILU;
+    if (a.tma_rows_per_thread == 4)
+        return act ? launch_kernel<DT, W, SLAB_BYTES, 8, 4, true>(a, p, s)
+                   : launch_kernel<DT, W, SLAB_BYTES, 8, 4, false>(a, p, s);
+    return act ? launch_kernel<DT, W, SLAB_BYTES, 8, 8, true>(a, p, s)
+               : launch_kernel<DT, W, SLAB_BYTES, 8, 8, false>(a, p, s);
 }
 
 template <int DT, int W>

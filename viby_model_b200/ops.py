@@ -30,7 +30,7 @@ _MASK_DTYPES = {
 }
 
 
-_TMA_TUNING = {"stages", "ctas_per_sm", "slab_bytes", "rows_per_thread", "vec_bytes", "direct_store", "debug_copy"}
+_TMA_TUNING = {"stages", "ctas_per_sm", "slab_bytes", "rows_per_thread"}
 
 
 def _activation_code(activation) -> int:
@@ -129,7 +129,7 @@ def causal_conv1d_fn(
       state_len: width of the returned final state (CanonLayer keeps ``kernel_size`` columns).
       out: preallocated output; kernel / rows_per_thread / block_threads / unroll: tuning overrides;
       tma: dict of tuning overrides of the TMA-staged kernel (stages, ctas_per_sm, slab_bytes,
-        rows_per_thread, vec_bytes, direct_store).
+        rows_per_thread).
     """
     if x.dim() != 3:
         raise ValueError(f"Expected 3D input tensor (batch, dim, seqlen), got {x.dim()}D")
