@@ -121,7 +121,14 @@ typedef struct vc1d_prefill_args {
     int32_t tma_ctas_per_sm;     /* persistent CTAs per SM */
     int32_t tma_slab_bytes;      /* channel slab of a tile: 128 or 256 bytes */
     int32_t tma_rows_per_thread; /* 4 or 8 consecutive rows per thread and tile */
-    int32_t reserved[4];
+    /* Optional scratch for the TMA-staged kernel's dynamic tile scheduler: device memory, 16-byte
+     * aligned, at least 4096 + batch * ceil(seqlen / 32) bytes.  Its first 4096 bytes (one claim
+     * counter per channel slab) must be ZERO before its first use; every launch leaves them zeroed.
+     * With a mask a small pre-pass kernel fills the rest with one class byte per tile.  Launches
+     * that may overlap on the GPU must not share it.  NULL, too small, or more than 1023 channel
+     * slabs = static tile assignment. */
+    void* scratch;
+    int64_t scratch_bytes;
 } vc1d_prefill_args;
 
 VC1D_API int vc1d_prefill(const vc1d_prefill_args* args, void* stream);

@@ -77,7 +77,8 @@ class PrefillArgs(C.Structure):
         ("tma_ctas_per_sm", C.c_int32),
         ("tma_slab_bytes", C.c_int32),
         ("tma_rows_per_thread", C.c_int32),
-        ("reserved", C.c_int32 * 4),
+        ("scratch", C.c_void_p),
+        ("scratch_bytes", C.c_int64),
     ]
 
 

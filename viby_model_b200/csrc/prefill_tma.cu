@@ -64,6 +64,7 @@ cudaError_t launch_prefill_tma(const vc1d_prefill_args& a, cudaStream_t s) {
     p.bias = a.bias;
     p.mask = a.mask;
     p.fstate = reinterpret_cast<char*>(a.final_state);
+    p.sched = nullptr;
     p.timeouts = tma::timeouts_ptr();
     if (p.timeouts == nullptr) return cudaErrorNotSupported;
     p.sxb = a.x_stride_b * eb;

@@ -15,8 +15,8 @@
 // Pipeline.  One producer warp and eight consumer warps share a ring of stages guarded by
 // full/done mbarriers.  The producer fetches the tile's mask rows two tiles ahead (32 lanes, a
 // few loads each) and classifies the tile: all rows valid, mixed, or nothing to read.  A tile
-// with nothing to read never enters the ring: no byte of it is requested from HBM and the
-// producer warp stores its outputs, act(bias), itself.  Bytes in flight are set by the ring
+// with nothing to read takes a ring slot but no bulk copy: no byte of it is requested from HBM
+// and the consumers store act(bias).  Bytes in flight are set by the ring
 // depth, not by registers.  Each consumer thread owns 8 bytes of channels and 8 consecutive
 // rows of the tile: a register window over shared memory rotated by index, fp32x2 FMAs, fused
 // mask / bias / SiLU / residual epilogue, streaming 8-byte stores (a warp writes 256 contiguous
@@ -53,6 +53,8 @@ struct TmaParams {
     const void* mask;
     char* fstate;
     unsigned int* timeouts;  // device counter of expired waits
+    unsigned int* sched;     // dynamic tile scheduler: one counter per channel slab + one CTA counter, or NULL
+    const unsigned char* gtable;  // class of every (sequence, time tile), written by k_classify_tiles, or NULL
     long long sxb, sxt;  // bytes
     long long srb, srt;
     long long smb, smt;  // elements
@@ -119,43 +121,14 @@ __device__ __forceinline__ int lds_s32(uint32_t a) {
 __device__ __forceinline__ void sts_s32(uint32_t a, int v) {
     asm volatile("st.volatile.shared.s32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
 }
-__device__ __forceinline__ void sts_f32(uint32_t a, float v) {
-    asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory");
+__device__ __forceinline__ int lds_u8(uint32_t a) {
+    int v;
+    asm volatile("ld.volatile.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+    return v;
 }
-
-// Walks the row tiles j0, j0 + G, j0 + 2G, ... of one CTA without a division per tile.  Tile
-// number rt means sequence b = rt / n_ttile and time position (rt % n_ttile + b) % n_ttile: the
-// position is rotated by the sequence index so that a CTA does not keep meeting the same position
-// of every sequence (with right-padded batches the late positions are the cheap, masked ones).
-struct TileIter {
-    int b, r, brot;        // sequence, rt % n_ttile, b % n_ttile
-    int n, sb, sr, sbrot;  // n_ttile, G / n_ttile, G % n_ttile, sb % n_ttile
-    __device__ __forceinline__ void init(int rt, int n_ttile, int stride) {
-        n = n_ttile;
-        b = rt / n;
-        r = rt - b * n;
-        brot = b % n;
-        sb = stride / n;
-        sr = stride - sb * n;
-        sbrot = sb % n;
-    }
-    __device__ __forceinline__ void next() {
-        b += sb;
-        brot += sbrot;
-        if (brot >= n) brot -= n;
-        r += sr;
-        if (r >= n) {
-            r -= n;
-            ++b;
-            if (++brot == n) brot = 0;
-        }
-    }
-    __device__ __forceinline__ int t0(int tile_rows) const {
-        int tt = r + brot;
-        if (tt >= n) tt -= n;
-        return tt * tile_rows;
-    }
-};
+__device__ __forceinline__ void sts_u8(uint32_t a, int v) {
+    asm volatile("st.volatile.shared.u8 [%0], %1;" ::"r"(a), "r"(v) : "memory");
+}
 
 template <int DT, int W, int SLAB_BYTES, int VB, int RPT>
 struct Geometry {
@@ -171,13 +144,12 @@ struct Geometry {
     static constexpr int kRowBytes = SLAB_BYTES;
     static constexpr int kSlabElems = SLAB_BYTES / Elem<DT>::kBytes;
     static constexpr int kStageBytes = ((kBoxRows * kRowBytes + 127) / 128) * 128;
-    static constexpr int kMaskFloats = ((kBoxRows + 31) / 32) * 32;
-    // layout for S stages: stages | mask floats | full[S], done[S] | {class, b, t0}[S], abort
-    __host__ __device__ static constexpr int off_mask(int S) { return S * kStageBytes; }
-    __host__ __device__ static constexpr int off_bars(int S) { return off_mask(S) + S * kMaskFloats * 4; }
+    // layout for S stages: stages | full[S], done[S] | {class, b, t0}[S] | class table (one byte per tile)
+    __host__ __device__ static constexpr int off_bars(int S) { return S * kStageBytes; }
     __host__ __device__ static constexpr int off_flags(int S) { return off_bars(S) + 2 * S * 8; }
-    __host__ __device__ static constexpr int smem_bytes(int S) {
-        return off_flags(S) + (3 * S + 1) * 4 + 128 /* base alignment slack */;
+    __host__ __device__ static constexpr int off_table(int S) { return off_flags(S) + 3 * S * 4; }
+    __host__ __device__ static constexpr int smem_bytes(int S, int table_bytes) {
+        return off_table(S) + table_bytes + 128 /* base alignment slack */;
     }
 };
 
@@ -238,10 +210,17 @@ __device__ __forceinline__ void apply_mask(float2 (&f)[Slice<DT, VB>::kPairs], f
     }
 }
 
+// Mask multiplier of time row t of the sequence whose mask row starts at element mrow.  Rows before
+// t = 0 hold zero-filled data (any multiplier works); rows past the end are never stored.
+__device__ __forceinline__ float tile_mask(const TmaParams& p, long long mrow, int t) {
+    if (t < 0 || t >= p.T) return 1.0f;
+    return load_mask(p.mask, mrow + (long long)t * p.smt, p.mask_dtype);
+}
+
 // The R rows of one thread in one tile.  GENERAL adds the per-row mask and the residual.  Results go
 // straight to global memory with streaming stores (yrow is the address of the thread's first row).
 template <int DT, int W, int VB, int RPT, bool ACT, bool GENERAL, int ROW_BYTES>
-__device__ __forceinline__ void process_rows(uint32_t trow, uint32_t mk_addr, const TmaParams& p, bool mixed,
+__device__ __forceinline__ void process_rows(uint32_t trow, long long mrow, const TmaParams& p, bool mixed,
                                              const char* rb, char* yrow, int tfirst, int rows_ok,
                                              float2 (&hist)[W - 1 > 0 ? W - 1 : 1][Slice<DT, VB>::kPairs],
                                              const float2 (&wp)[W][Slice<DT, VB>::kPairs],
@@ -261,7 +240,7 @@ __device__ __forceinline__ void process_rows(uint32_t trow, uint32_t mk_addr, co
         float2 cur[NP];
         S::unpack(raw, cur);
         if constexpr (GENERAL) {
-            if (mixed) apply_mask<DT, VB>(cur, lds_f32(mk_addr + (H + k) * 4), p.skip);
+            if (mixed) apply_mask<DT, VB>(cur, tile_mask(p, mrow, tfirst + k), p.skip);
         }
         float2 acc[NP];
 #pragma unroll
@@ -303,20 +282,34 @@ __device__ __forceinline__ void process_rows(uint32_t trow, uint32_t mk_addr, co
     });
 }
 
-// Mask values of one tile's box rows, kBoxRows spread over the 32 lanes of the producer warp.
-template <int NMK, int BOX_ROWS, int H, int TILE_ROWS>
-__device__ __forceinline__ void fetch_mask(const TmaParams& p, int b, int t0, int lane, float (&mk)[NMK]) {
-#pragma unroll
-    for (int q = 0; q < NMK; ++q) {
-        const int jrow = lane + 32 * q;
+// Class of one tile from its mask rows: all valid, mixed, or nothing to read.  One warp per tile.
+__device__ __forceinline__ int classify_tile(const TmaParams& p, int b, int t0, int H, int box_rows, int lane) {
+    bool any = false, all_one = true;
+    for (int jrow = lane; jrow < box_rows; jrow += 32) {
         const int t = t0 - H + jrow;
-        float v = 1.0f;                        // rows before t = 0 are zero-filled data: any multiplier works
-        if (jrow < BOX_ROWS) {
-            if (t >= p.T) v = 0.0f;            // rows past the end are never stored
-            else if (t >= 0) v = load_mask(p.mask, (long long)b * p.smb + (long long)t * p.smt, p.mask_dtype);
+        if (t >= 0 && t < p.T) {
+            const float mk = load_mask(p.mask, (long long)b * p.smb + (long long)t * p.smt, p.mask_dtype);
+            any |= (mk != 0.0f);
+            all_one &= (mk == 1.0f);
         }
-        mk[q] = v;
     }
+    any = __any_sync(0xffffffffu, any);
+    all_one = __all_sync(0xffffffffu, all_one);
+    return all_one ? TILE_FULL : ((any || !p.skip || p.res != nullptr) ? TILE_MIXED : TILE_EMPTY);
+}
+
+// Pre-pass of masked launches that schedule dynamically: the class of every (sequence, time tile),
+// one byte each, into scratch memory.  The mask is the same for every channel slab.
+constexpr int kSchedCounterBytes = 4096;
+
+static __global__ void __launch_bounds__(256) k_classify_tiles(const TmaParams p, unsigned char* table, int tile_rows, int H) {
+    const int lane = threadIdx.x & 31;
+    const long long tile = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (tile >= (long long)p.B * p.n_ttile) return;
+    const int b = (int)(tile / p.n_ttile);
+    const int tt = (int)(tile - (long long)b * p.n_ttile);
+    const int cls = classify_tile(p, b, tt * tile_rows, H, tile_rows + H, lane);
+    if (lane == 0) table[tile] = (unsigned char)cls;
 }
 
 template <int DT, int W, int SLAB_BYTES, int VB, int RPT, bool ACT>
@@ -336,10 +329,9 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
     const int kStages = p.stages;  // ring depth of this launch
-    const uint32_t mask_base = base + G::off_mask(kStages);
     const uint32_t bars = base + G::off_bars(kStages);    // full[s] at bars + 8 s, done[s] at bars + 8 (kStages + s)
-    const uint32_t flags = base + G::off_flags(kStages);  // per stage {class, sequence, first row}; then the abort flag
-    const uint32_t abort_c = flags + 12 * kStages;
+    const uint32_t flags = base + G::off_flags(kStages);  // per stage {class, sequence, first row}
+    const uint32_t table = base + G::off_table(kStages);  // class of each of this CTA's tiles (masked launches)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -354,45 +346,38 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
             mbar_init(bars + 8 * s, 1);                              // full: the producer's arrive (+ tx bytes)
             mbar_init(bars + 8 * (kStages + s), G::kConsumerWarps);  // done: one arrive per consumer warp
         }
-        sts_s32(abort_c, 0);  // a consumer wait expired
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+
+    // tile number -> (sequence, first row); the time position is rotated by the sequence index so
+    // that tiles handled together do not all sit at the same position of their sequences (with
+    // right-padded batches the late positions are the cheap, masked ones)
+    auto locate = [&](int rt, int& b, int& t0) {
+        b = rt / p.n_ttile;
+        int tt = rt - b * p.n_ttile + b % p.n_ttile;
+        if (tt >= p.n_ttile) tt -= p.n_ttile;
+        t0 = tt * G::kTileRows;
+    };
+
+    // ---- prologue with a mask: classify all of this CTA's tiles, one warp per tile, all warps ----
+    // at once.  The producer then only reads a byte per tile, so no mask latency ever sits between
+    // two bulk copies.  (Tiles are assigned statically when there is a mask.)
+    if (p.mask != nullptr && p.gtable == nullptr) {
+        for (int i = warp; i < n_my; i += G::kThreads / 32) {
+            int b, t0;
+            locate(j0 + i * stride, b, t0);
+            const int cls = classify_tile(p, b, t0, H, G::kBoxRows, lane);
+            if (lane == 0) sts_u8(table + i, cls);
+        }
     }
     __syncthreads();
 
     if (warp == G::kConsumerWarps) {
         // ================================ producer warp ==================================
-        // Walks the CTA's tiles in order.  A tile with something to read takes the next ring slot
-        // (after the consumers of the slot's previous tile have arrived on done[s]) and is loaded
-        // by one bulk tensor copy.  A tile in which every tap of every row is masked never enters
-        // the ring: its outputs are act(bias), and this warp -- one lane per 8 bytes of the slab
-        // row -- stores them itself.  After the last tile an END marker takes a slot.  The mask of
-        // tile i+2 is fetched while tile i is handled, in three register buffers that rotate roles
-        // (the loop is unrolled by three), so the fetched values are not touched until needed.
-        using S8 = Slice<DT, 8>;
-        constexpr int NE8 = S8::kElems;
-        const int pd0 = slab_ch0 + lane * NE8;  // this lane's channels when it stores a masked-out tile
-        const bool p_ok = lane * 8 < SLAB_BYTES && pd0 < p.D;
-        uint32_t pconst[2] = {0u, 0u};
-        if (p.mask != nullptr && p_ok) {
-            float2 c[S8::kPairs];
-#pragma unroll
-            for (int q = 0; q < S8::kPairs; ++q) {
-                float v[2] = {0.f, 0.f};
-                if (p.bias != nullptr) {
-#pragma unroll
-                    for (int e = 0; e < 2; ++e)
-                        v[e] = (p.wdtype == VC1D_F32)
-                                   ? __ldg(reinterpret_cast<const float*>(p.bias) + pd0 + 2 * q + e)
-                                   : E::to_float(__ldg(reinterpret_cast<const typename E::type*>(p.bias) + pd0 + 2 * q + e));
-                }
-                c[q] = make_float2(v[0], v[1]);
-                if (ACT) c[q] = silu2<E::kPreciseSilu>(c[q]);
-            }
-            S8::pack(c, pconst);
-        }
-        TileIter it_fetch, it_load;  // tiles i+2 (mask fetch) and i (load)
-        it_load.init(j0, p.n_ttile, stride);
-        it_fetch = it_load;
+        // Walks the CTA's tiles.  Each tile takes the next ring slot (after the consumers of the
+        // slot's previous tile have arrived on done[s]); a tile with something to read is loaded by
+        // one bulk tensor copy, a tile in which every tap of every row is masked is only announced.
+        // After the last tile an END marker takes a slot.
         int s_ring = 0, n_ring = 0;  // next ring slot, tiles put into the ring so far
         uint32_t ph_ring = 0;        // how often the ring has wrapped, mod 2
         // claim the next slot: wait until its previous tile has been consumed
@@ -411,74 +396,61 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
                 ph_ring ^= 1;
             }
         };
-        auto step = [&](int i, float (&mk_use)[NMK], float (&mk_fill)[NMK]) -> bool {
-            if (p.mask != nullptr && i + 2 < n_my) {
-                it_fetch.next();
-                fetch_mask<NMK, G::kBoxRows, H, G::kTileRows>(p, it_fetch.b, it_fetch.t0(G::kTileRows), lane, mk_fill);
-            }
-            const int b = it_load.b;
-            const int t0 = it_load.t0(G::kTileRows);
-            int cls = TILE_FULL;
-            if (p.mask != nullptr) {
-                bool any = false, all_one = true;
-#pragma unroll
-                for (int q = 0; q < NMK; ++q) {
-                    const int jrow = lane + 32 * q;
-                    const int t = t0 - H + jrow;
-                    if (jrow < G::kBoxRows && t >= 0 && t < p.T) {
-                        any |= (mk_use[q] != 0.0f);
-                        all_one &= (mk_use[q] == 1.0f);
-                    }
-                }
-                any = __any_sync(0xffffffffu, any);
-                all_one = __all_sync(0xffffffffu, all_one);
-                cls = all_one ? TILE_FULL : ((any || !p.skip || p.res != nullptr) ? TILE_MIXED : TILE_EMPTY);
-            }
-            if (cls == TILE_EMPTY) {
-                if (p_ok) {
-                    char* yrow = p.y + (long long)b * p.syb + (long long)t0 * p.syt + (long long)pd0 * E::kBytes;
-                    const int nrows = min(G::kTileRows, p.T - t0);
-                    for (int r = 0; r < nrows; ++r) S8::stg(yrow + (long long)r * p.syt, pconst);
-                }
+        // Which tile comes next.  Static: this CTA's tiles are j0, j0 + G, j0 + 2G, ...  Dynamic
+        // (a zeroed counter per slab in caller-provided scratch memory): the next unclaimed tile of
+        // the slab, so that a CTA that met cheap (masked) tiles or runs on a faster SM takes more.
+        const bool dynamic = p.sched != nullptr && (p.mask == nullptr || p.gtable != nullptr);
+        int n_claimed = 0;
+        auto next_tile = [&]() -> int {
+            int rt;
+            if (dynamic) {
+                unsigned v = 0;
+                if (lane == 0) v = atomicAdd(p.sched + slab, 1u);
+                v = __shfl_sync(0xffffffffu, v, 0);
+                rt = v < (unsigned)p.n_rowtiles ? (int)v : -1;
             } else {
-                if (!claim()) return false;
-                const int s = s_ring;
-                if (cls == TILE_MIXED) {
-#pragma unroll
-                    for (int q = 0; q < NMK; ++q) {
-                        const int jrow = lane + 32 * q;
-                        if (jrow < G::kBoxRows) sts_f32(mask_base + (s * G::kMaskFloats + jrow) * 4, mk_use[q]);
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) {
-                    sts_s32(flags + 12 * s, cls);
-                    sts_s32(flags + 12 * s + 4, b);
-                    sts_s32(flags + 12 * s + 8, t0);
-                    const uint32_t full = bars + 8 * s;
+                rt = n_claimed < n_my ? j0 + n_claimed * stride : -1;
+            }
+            ++n_claimed;
+            return rt;
+        };
+        // class of a located tile: global table (pre-pass), this CTA's own table, or no mask at all
+        auto tile_class = [&](int i, int b, int t0) -> int {
+            if (p.mask == nullptr) return TILE_FULL;
+            if (p.gtable != nullptr) return (int)__ldg(p.gtable + (long long)b * p.n_ttile + t0 / G::kTileRows);
+            return lds_u8(table + i);
+        };
+        bool live = true;
+        // tile and class are fetched one tile ahead: their latency hides behind the current tile
+        int rt_next = next_tile(), b_next = 0, t0_next = 0, cls_next = TILE_FULL;
+        if (rt_next >= 0) {
+            locate(rt_next, b_next, t0_next);
+            cls_next = tile_class(0, b_next, t0_next);
+        }
+        for (int i = 0; live && rt_next >= 0; ++i) {
+            const int b = b_next, t0 = t0_next, cls = cls_next;
+            rt_next = next_tile();
+            if (rt_next >= 0) {
+                locate(rt_next, b_next, t0_next);
+                cls_next = tile_class(i + 1, b_next, t0_next);
+            }
+            live = claim();
+            if (!live) break;
+            const int s = s_ring;
+            if (lane == 0) {
+                sts_s32(flags + 12 * s, cls);
+                sts_s32(flags + 12 * s + 4, b);
+                sts_s32(flags + 12 * s + 8, t0);
+                const uint32_t full = bars + 8 * s;
+                if (cls != TILE_EMPTY) {
                     mbar_arrive_expect_tx(full, G::kBoxRows * G::kRowBytes);
                     tma_load_3d(base + s * G::kStageBytes, &tmap_x, slab_ch0, t0 - H, b, full);
+                } else {
+                    mbar_arrive(full);  // nothing to read: the consumers store act(bias)
                 }
-                __syncwarp();
-                advance();
             }
-            it_load.next();
-            return true;
-        };
-        float mk_a[NMK], mk_b[NMK], mk_c[NMK];
-#pragma unroll
-        for (int q = 0; q < NMK; ++q) mk_a[q] = mk_b[q] = mk_c[q] = 1.0f;
-        if (p.mask != nullptr && n_my > 0)
-            fetch_mask<NMK, G::kBoxRows, H, G::kTileRows>(p, it_fetch.b, it_fetch.t0(G::kTileRows), lane, mk_a);
-        if (p.mask != nullptr && n_my > 1) {
-            it_fetch.next();
-            fetch_mask<NMK, G::kBoxRows, H, G::kTileRows>(p, it_fetch.b, it_fetch.t0(G::kTileRows), lane, mk_b);
-        }
-        bool live = true;
-        for (int i = 0; live && i < n_my; i += 3) {
-            live = step(i, mk_a, mk_c);
-            if (live && i + 1 < n_my) live = step(i + 1, mk_b, mk_a);
-            if (live && i + 2 < n_my) live = step(i + 2, mk_c, mk_b);
+            __syncwarp();
+            advance();
         }
         // END marker: the consumers leave when they meet it
         if (live && claim()) {
@@ -487,6 +459,17 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
                 mbar_arrive(bars + 8 * s_ring);
             }
             __syncwarp();
+        }
+        // Dynamic scheduling leaves the scratch counters zeroed for the next launch: the last CTA
+        // of the grid to get here (every CTA has made its last claim by then) resets them.
+        if (dynamic && lane == 0) {
+            const unsigned n_ctas = gridDim.x * gridDim.y;
+            __threadfence();
+            const unsigned done = atomicAdd(p.sched + gridDim.x, 1u);
+            if (done == n_ctas - 1) {
+                for (unsigned k = 0; k <= gridDim.x; ++k) p.sched[k] = 0u;
+                __threadfence();
+            }
         }
     } else {
         // ================================ consumer warps =================================
@@ -499,6 +482,14 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         float2 wp[W][NP];
         float2 bp[NP];
         load_weights<DT, W, VB>(p, d0, ch_ok, wp, bp);
+        // value of a row whose W taps are all masked: act(bias)
+        uint32_t const_row[NW];
+        {
+            float2 c[NP];
+#pragma unroll
+            for (int q = 0; q < NP; ++q) c[q] = ACT ? silu2<E::kPreciseSilu>(bp[q]) : bp[q];
+            S::pack(c, const_row);
+        }
         const bool general_kernel = (p.mask != nullptr) || (p.res != nullptr);
 
         int s = -1;
@@ -514,31 +505,40 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
             if (cls == TILE_END) break;
             // box row of time t is (t - t0 + H); this thread reads box rows rbase .. rbase+R+H-1
             const uint32_t trow = base + s * G::kStageBytes + rbase * G::kRowBytes + cl * VB;
-            const uint32_t mk_addr = mask_base + (s * G::kMaskFloats + rbase) * 4;
             const bool mixed = (cls == TILE_MIXED);
             const int b = lds_s32(flags + 12 * s + 4);
             const int tfirst = lds_s32(flags + 12 * s + 8) + rbase;
+            const long long mrow = (long long)b * p.smb;
 
+            // rows of this thread that exist in the output
+            const int rows_ok = ch_ok ? min(R, max(0, p.T - tfirst)) : 0;
+            char* yrow = p.y + (long long)b * p.syb + (long long)tfirst * p.syt + (long long)d0 * E::kBytes;
+            if (cls == TILE_EMPTY) {
+                // every tap of every row is masked and nothing was loaded
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bars + 8 * (kStages + s));
+#pragma unroll
+                for (int k = 0; k < R; ++k)
+                    if (rows_ok > k) S::stg(yrow + (long long)k * p.syt, const_row);
+                continue;
+            }
             float2 hist[H > 0 ? H : 1][NP];
 #pragma unroll
             for (int w = 0; w < H; ++w) {
                 uint32_t raw[NW];
                 S::lds(trow + w * G::kRowBytes, raw);
                 S::unpack(raw, hist[w]);
-                if (mixed) apply_mask<DT, VB>(hist[w], lds_f32(mk_addr + w * 4), p.skip);
+                if (mixed) apply_mask<DT, VB>(hist[w], tile_mask(p, mrow, tfirst - H + w), p.skip);
             }
-            // rows of this thread that exist in the output
-            const int rows_ok = ch_ok ? min(R, max(0, p.T - tfirst)) : 0;
-            char* yrow = p.y + (long long)b * p.syb + (long long)tfirst * p.syt + (long long)d0 * E::kBytes;
             const char* rb = nullptr;
             if (p.res != nullptr && !p.res_is_x && ch_ok)
                 rb = p.res + (long long)b * p.srb + (long long)d0 * E::kBytes;
 
             if (!general_kernel || (cls == TILE_FULL && p.res == nullptr)) {
-                process_rows<DT, W, VB, RPT, ACT, false, G::kRowBytes>(trow, mk_addr, p, false, nullptr, yrow, tfirst,
+                process_rows<DT, W, VB, RPT, ACT, false, G::kRowBytes>(trow, mrow, p, false, nullptr, yrow, tfirst,
                                                                        rows_ok, hist, wp, bp);
             } else {
-                process_rows<DT, W, VB, RPT, ACT, true, G::kRowBytes>(trow, mk_addr, p, mixed, rb, yrow, tfirst,
+                process_rows<DT, W, VB, RPT, ACT, true, G::kRowBytes>(trow, mrow, p, mixed, rb, yrow, tfirst,
                                                                       rows_ok, hist, wp, bp);
             }
             __syncwarp();
@@ -617,9 +617,19 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     if (stages < 2) stages = 2;
     if (stages > kMaxStages) stages = kMaxStages;
     int per_sm = (a.tma_ctas_per_sm > 0 && a.tma_ctas_per_sm <= 32) ? a.tma_ctas_per_sm : 3;
-    while (stages > 2 && G::smem_bytes(stages) > 200 * 1024) --stages;
     p.stages = stages;
-    const int smem = G::smem_bytes(stages);
+    // persistent CTAs, split evenly over the channel slabs; with a mask every CTA keeps one class
+    // byte per tile in shared memory, so the grid grows before a CTA would own more than 8192 tiles
+    long long g = ((long long)sm_count() * per_sm) / n_slab;
+    if (g < 1) g = 1;
+    if (a.mask != nullptr && n_rowtiles > g * 8192) g = (n_rowtiles + 8191) / 8192;
+    if (g > n_rowtiles) g = n_rowtiles;
+    if (g > 65535) g = 65535;
+    p.ctas_per_slab = (int)g;
+    const long long tiles_per_cta = (n_rowtiles + g - 1) / g;
+    if (a.mask != nullptr && tiles_per_cta > 8192) return cudaErrorNotSupported;  // the direct kernel takes it
+    const int table_bytes = a.mask != nullptr ? (int)((tiles_per_cta + 15) / 16 * 16) : 0;
+    const int smem = G::smem_bytes(stages, table_bytes);
     {
         // opt in to > 48 KB of dynamic shared memory; the attribute is per device and sticky, so
         // remember the largest value set so far
@@ -633,12 +643,29 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
             if (dev >= 0 && dev < 64) granted[dev].store(smem, std::memory_order_release);
         }
     }
-    // persistent CTAs, split evenly over the channel slabs
-    long long g = ((long long)sm_count() * per_sm) / n_slab;
-    if (g < 1) g = 1;
-    if (g > n_rowtiles) g = n_rowtiles;
-    if (g > 65535) g = 65535;
-    p.ctas_per_slab = (int)g;
+    // scratch: [4096 bytes of counters (one per slab + one), zero between launches | class byte per
+    // (sequence, time tile)].  The counter region has a fixed size so that no launch's class bytes
+    // can land where a later launch with more slabs keeps its counters.
+    p.sched = nullptr;
+    p.gtable = nullptr;
+    const long long counters_bytes = kSchedCounterBytes;
+    const long long table_need = a.mask != nullptr ? n_rowtiles : 0;
+    if (4LL * (n_slab + 1) > counters_bytes) {
+        // more slabs than counters: static assignment
+    } else
+    if (a.scratch != nullptr && a.scratch_bytes >= counters_bytes + table_need &&
+        (reinterpret_cast<uintptr_t>(a.scratch) & 15u) == 0) {
+        p.sched = reinterpret_cast<unsigned int*>(a.scratch);
+        if (a.mask != nullptr) {
+            unsigned char* tab = reinterpret_cast<unsigned char*>(a.scratch) + counters_bytes;
+            const long long threads = n_rowtiles * 32;
+            k_classify_tiles<<<(unsigned)((threads + 255) / 256), 256, 0, s>>>(p, tab, G::kTileRows, G::kH);
+            const cudaError_t e = cudaGetLastError();
+            if (e != cudaSuccess) return e;
+            note_launch("classify");
+            p.gtable = tab;
+        }
+    }
     const dim3 grid((unsigned)n_slab, (unsigned)g);
     note_launch("tma");
     k_prefill_tma<DT, W, SLAB_BYTES, VB, RPT, ACT><<<grid, G::kThreads, smem, s>>>(tmap_x, p);

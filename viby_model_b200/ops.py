@@ -82,6 +82,21 @@ def _stream_handle(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+# Scratch of the dynamic tile scheduler: one small zeroed buffer per (device, stream), because
+# launches that can overlap on the GPU must not share it.  The kernel leaves it zeroed.
+_DYNAMIC_DEFAULT = True
+_SCRATCH = {}
+
+
+def _scheduler_scratch(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    key = (device.index, stream)
+    buf = _SCRATCH.get(key)
+    if buf is None or buf.numel() * 4 < nbytes:
+        buf = torch.zeros(max(16384, (nbytes + 3) // 4), dtype=torch.int32, device=device)
+        _SCRATCH[key] = buf
+    return buf
+
+
 def causal_conv1d_fn(
     x: torch.Tensor,
     weight: torch.Tensor,
@@ -102,6 +117,7 @@ def causal_conv1d_fn(
     block_threads: int = 0,
     unroll: int = 0,
     tma: Optional[dict] = None,
+    dynamic_schedule: Optional[bool] = None,
 ) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
     """Depthwise causal conv1d over ``x[batch, dim, seqlen]`` (prefill).
 
@@ -130,6 +146,9 @@ def causal_conv1d_fn(
       out: preallocated output; kernel / rows_per_thread / block_threads / unroll: tuning overrides;
       tma: dict of tuning overrides of the TMA-staged kernel (stages, ctas_per_sm, slab_bytes,
         rows_per_thread).
+      dynamic_schedule: let the CTAs of the TMA-staged kernel claim tiles from per-slab counters in a
+        small scratch buffer (one per device and stream, allocated on first use) instead of a fixed
+        assignment; evens out ragged batches.
     """
     if x.dim() != 3:
         raise ValueError(f"Expected 3D input tensor (batch, dim, seqlen), got {x.dim()}D")
@@ -231,11 +250,16 @@ def causal_conv1d_fn(
                 raise ValueError(f"unknown TMA tuning key {key!r}; expected one of {sorted(_TMA_TUNING)}")
             setattr(a, "tma_" + key, int(value))
 
+    stream = _stream_handle(x.device)
+    if dynamic_schedule or (dynamic_schedule is None and _DYNAMIC_DEFAULT):
+        sc = _scheduler_scratch(x.device, stream, 4096 + batch * ((seqlen + 31) // 32))
+        a.scratch = sc.data_ptr()
+        a.scratch_bytes = sc.numel() * sc.element_size()
     if x.device.index != torch.cuda.current_device():
         with torch.cuda.device(x.device):
-            st = _cabi.lib.vc1d_prefill(C.byref(a), _stream_handle(x.device))
+            st = _cabi.lib.vc1d_prefill(C.byref(a), stream)
     else:
-        st = _cabi.lib.vc1d_prefill(C.byref(a), _stream_handle(x.device))
+        st = _cabi.lib.vc1d_prefill(C.byref(a), stream)
     _cabi.check(st, "causal_conv1d_fn")
     if return_final_states or final_states_out is not None:
         return out, final_states
