@@ -134,6 +134,26 @@ typedef struct vc1d_prefill_args {
 VC1D_API int vc1d_prefill(const vc1d_prefill_args* args, void* stream);
 
 /*
+ * Prefill for callers that can neither allocate device memory nor hand over a scratch buffer
+ * (a serving loop whose memory plan is frozen, code running under another allocator's lock or
+ * callback, a host language whose binding owns no device allocator).  No counterpart in the
+ * reference.  Same arguments and results as vc1d_prefill with kernel = VC1D_KERNEL_TMA (so the
+ * layout must be channel-last without initial_state, else VC1D_E_STRIDE); `scratch`,
+ * `scratch_bytes` and `kernel` in *args are ignored.  The dynamic tile scheduler's scratch is a
+ * fixed 64 KB array inside the library's device image, so the call never allocates or frees.
+ *  - Limit: batch * ceil(seqlen / 32) <= VC1D_NOALLOC_MAX_TILES, else VC1D_E_TOO_LARGE and nothing
+ *    is launched.
+ *  - The first call on each device looks the array up (with that device current) and may make
+ *    the runtime load the device image: make it before any stream capture begins.
+ *  - One array per device, shared by every call on that device and holding the last call's
+ *    contents (each call clears what it needs on its own stream): calls whose execution may
+ *    overlap on one device -- different streams, different host threads -- race on it.  Order
+ *    them, or use vc1d_prefill with a scratch buffer per stream.
+ */
+#define VC1D_NOALLOC_MAX_TILES 61440
+VC1D_API int vc1d_prefill_noalloc(const vc1d_prefill_args* args, void* stream);
+
+/*
  * Decode: causal_conv1d_update.
  * Replaces the external CUDA kernel the reference calls at model/model.py:305-311 and
  * the PyTorch single step at model/model.py:372-398:

@@ -119,6 +119,7 @@ class UpdateArgs(C.Structure):
 # every symbol include/vc1d.h declares: name -> (restype, argtypes)
 EXPORTS = {
     "vc1d_prefill": (C.c_int, [C.POINTER(PrefillArgs), C.c_void_p]),
+    "vc1d_prefill_noalloc": (C.c_int, [C.POINTER(PrefillArgs), C.c_void_p]),
     "vc1d_update": (C.c_int, [C.POINTER(UpdateArgs), C.c_void_p]),
     "vc1d_abi_version": (C.c_int, []),
     "vc1d_sizeof_prefill_args": (C.c_uint32, []),

@@ -28,6 +28,7 @@ SOURCES = [
     "prefill_tma_f32.cu",
     "prefill_tma_bf16.cu",
     "prefill_tma_f16.cu",
+    "prefill_noalloc.cu",
     "update.cu",
 ]
 
