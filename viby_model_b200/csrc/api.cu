@@ -1,5 +1,6 @@
 // C-ABI layer: argument validation, kernel selection, bookkeeping.  No kernel lives here.
 #include <atomic>
+#include <cstdlib>
 #include <cstdio>
 #include <cstring>
 
@@ -21,6 +22,14 @@ int sm_count() {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
     g_sm_count[dev].store(n, std::memory_order_relaxed);
     return n;
+}
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("VC1D_NO_PDL");
+        return !(v != nullptr && v[0] == '1');
+    }();
+    return on;
 }
 
 void note_launch(const char* kernel_name) {

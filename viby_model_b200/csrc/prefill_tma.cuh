@@ -30,6 +30,7 @@
 #include <cuda.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <type_traits>
 
 #include "vc1d_common.cuh"
@@ -65,6 +66,7 @@ struct TmaParams {
     int mask_dtype;
     int skip;
     int res_is_x;
+    int table_in_smem;  // the pre-pass class table fits in shared memory and every CTA copies it there
     int state_len;
     int stages;      // ring depth (2..kMaxStages)
 };
@@ -121,6 +123,17 @@ __device__ __forceinline__ int lds_s32(uint32_t a) {
 __device__ __forceinline__ void sts_s32(uint32_t a, int v) {
     asm volatile("st.volatile.shared.s32 [%0], %1;" ::"r"(a), "r"(v) : "memory");
 }
+// tile descriptor head: {class, rows that exist, 64-bit output offset} in one 16-byte access
+__device__ __forceinline__ void sts_desc(uint32_t a, int cls, int rows, long long yoff) {
+    asm volatile("st.volatile.shared.v4.s32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(cls), "r"(rows),
+                 "r"((int)(unsigned)(unsigned long long)yoff), "r"((int)(unsigned)((unsigned long long)yoff >> 32))
+                 : "memory");
+}
+__device__ __forceinline__ void lds_desc(uint32_t a, int& cls, int& rows, long long& yoff) {
+    unsigned lo, hi;
+    asm volatile("ld.volatile.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(cls), "=r"(rows), "=r"(lo), "=r"(hi) : "r"(a));
+    yoff = (long long)(((unsigned long long)hi << 32) | lo);
+}
 __device__ __forceinline__ int lds_u8(uint32_t a) {
     int v;
     asm volatile("ld.volatile.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
@@ -144,10 +157,12 @@ struct Geometry {
     static constexpr int kRowBytes = SLAB_BYTES;
     static constexpr int kSlabElems = SLAB_BYTES / Elem<DT>::kBytes;
     static constexpr int kStageBytes = ((kBoxRows * kRowBytes + 127) / 128) * 128;
-    // layout for S stages: stages | full[S], done[S] | {class, b, t0}[S] | class table (one byte per tile)
+    // layout for S stages: stages | full[S], done[S] | tile descriptor[S] | class table (one byte per tile)
+    // tile descriptor, 32 bytes: {class, rows of the tile that exist, byte offset of its first output
+    // row (64 bits)} {sequence, first row, -, -}
     __host__ __device__ static constexpr int off_bars(int S) { return S * kStageBytes; }
     __host__ __device__ static constexpr int off_flags(int S) { return off_bars(S) + 2 * S * 8; }
-    __host__ __device__ static constexpr int off_table(int S) { return off_flags(S) + 3 * S * 4; }
+    __host__ __device__ static constexpr int off_table(int S) { return off_flags(S) + S * 32; }
     __host__ __device__ static constexpr int smem_bytes(int S, int table_bytes) {
         return off_table(S) + table_bytes + 128 /* base alignment slack */;
     }
@@ -217,11 +232,22 @@ __device__ __forceinline__ float tile_mask(const TmaParams& p, long long mrow, i
     return load_mask(p.mask, mrow + (long long)t * p.smt, p.mask_dtype);
 }
 
+// Address of row K of a thread's rows: one widening multiply-add.
+template <int K>
+__device__ __forceinline__ char* row_addr(char* yrow, unsigned pitch) {
+    if constexpr (K == 0) return yrow;
+    unsigned long long r;
+    asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(r) : "r"(pitch), "n"(K), "l"(reinterpret_cast<unsigned long long>(yrow)));
+    return reinterpret_cast<char*>(r);
+}
+
 // The R rows of one thread in one tile.  GENERAL adds the per-row mask and the residual.  Results go
 // straight to global memory with streaming stores (yrow is the address of the thread's first row).
+// In a mixed tile the mask value of box row j of this thread's row group sits in lane msrc + j
+// (mkv), fetched with one load per lane before the rows start.
 template <int DT, int W, int VB, int RPT, bool ACT, bool GENERAL, int ROW_BYTES>
-__device__ __forceinline__ void process_rows(uint32_t trow, long long mrow, const TmaParams& p, bool mixed,
-                                             const char* rb, char* yrow, int tfirst, int rows_ok,
+__device__ __forceinline__ void process_rows(uint32_t trow, float mkv, int msrc, const TmaParams& p, bool mixed,
+                                             const char* rb, char* yrow, unsigned pitch, int tfirst, int rows_ok,
                                              float2 (&hist)[W - 1 > 0 ? W - 1 : 1][Slice<DT, VB>::kPairs],
                                              const float2 (&wp)[W][Slice<DT, VB>::kPairs],
                                              const float2 (&bp)[Slice<DT, VB>::kPairs]) {
@@ -240,7 +266,7 @@ __device__ __forceinline__ void process_rows(uint32_t trow, long long mrow, cons
         float2 cur[NP];
         S::unpack(raw, cur);
         if constexpr (GENERAL) {
-            if (mixed) apply_mask<DT, VB>(cur, tile_mask(p, mrow, tfirst + k), p.skip);
+            if (mixed) apply_mask<DT, VB>(cur, __shfl_sync(0xffffffffu, mkv, msrc + H + k), p.skip);
         }
         float2 acc[NP];
 #pragma unroll
@@ -274,7 +300,7 @@ __device__ __forceinline__ void process_rows(uint32_t trow, long long mrow, cons
         }
         uint32_t outw[NW];
         S::pack(acc, outw);
-        if (rows_ok > k) S::stg(yrow + (long long)k * p.syt, outw);
+        S::template stg_row<k>(row_addr<k>(yrow, pitch), outw, rows_ok);
         if constexpr (H > 0) {
 #pragma unroll
             for (int q = 0; q < NP; ++q) hist[k % H][q] = cur[q];
@@ -301,8 +327,11 @@ __device__ __forceinline__ int classify_tile(const TmaParams& p, int b, int t0, 
 // Pre-pass of masked launches that schedule dynamically: the class of every (sequence, time tile),
 // one byte each, into scratch memory.  The mask is the same for every channel slab.
 constexpr int kSchedCounterBytes = 4096;
+constexpr int kSmemTableCap = 16384;  // largest pre-pass class table a CTA copies into shared memory
 
 static __global__ void __launch_bounds__(256) k_classify_tiles(const TmaParams p, unsigned char* table, int tile_rows, int H) {
+    griddep_wait();  // the table may still be read by the previous launch on this stream
+    griddep_launch_dependents();
     const int lane = threadIdx.x & 31;
     const long long tile = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (tile >= (long long)p.B * p.n_ttile) return;
@@ -330,7 +359,7 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
     const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
     const int kStages = p.stages;  // ring depth of this launch
     const uint32_t bars = base + G::off_bars(kStages);    // full[s] at bars + 8 s, done[s] at bars + 8 (kStages + s)
-    const uint32_t flags = base + G::off_flags(kStages);  // per stage {class, sequence, first row}
+    const uint32_t flags = base + G::off_flags(kStages);  // per stage: 32-byte tile descriptor
     const uint32_t table = base + G::off_table(kStages);  // class of each of this CTA's tiles (masked launches)
 
     const int warp = threadIdx.x >> 5;
@@ -362,6 +391,20 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
     // ---- prologue with a mask: classify all of this CTA's tiles, one warp per tile, all warps ----
     // at once.  The producer then only reads a byte per tile, so no mask latency ever sits between
     // two bulk copies.  (Tiles are assigned statically when there is a mask.)
+    // Launched with programmatic stream serialization, this grid may start while its predecessor in
+    // the stream is still running: nothing above touched global memory, everything below may.
+    griddep_wait();
+    griddep_launch_dependents();
+    if (p.gtable != nullptr && p.table_in_smem) {
+        const int n16 = p.n_rowtiles >> 4;
+        const uint4* src = reinterpret_cast<const uint4*>(p.gtable);
+        for (int i = threadIdx.x; i < n16; i += G::kThreads) {
+            const uint4 v = __ldg(src + i);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(table + 16 * i), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                         : "memory");
+        }
+        for (int i = (n16 << 4) + threadIdx.x; i < p.n_rowtiles; i += G::kThreads) sts_u8(table + i, __ldg(p.gtable + i));
+    }
     if (p.mask != nullptr && p.gtable == nullptr) {
         for (int i = warp; i < n_my; i += G::kThreads / 32) {
             int b, t0;
@@ -400,47 +443,37 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         // (a zeroed counter per slab in caller-provided scratch memory): the next unclaimed tile of
         // the slab, so that a CTA that met cheap (masked) tiles or runs on a faster SM takes more.
         const bool dynamic = p.sched != nullptr && (p.mask == nullptr || p.gtable != nullptr);
-        int n_claimed = 0;
+        int n_issued = 0;
         auto next_tile = [&]() -> int {
-            int rt;
+            unsigned raw;
             if (dynamic) {
-                unsigned v = 0;
-                if (lane == 0) v = atomicAdd(p.sched + slab, 1u);
-                v = __shfl_sync(0xffffffffu, v, 0);
-                rt = v < (unsigned)p.n_rowtiles ? (int)v : -1;
+                raw = 0u;
+                if (lane == 0) raw = atomicAdd(p.sched + slab, 1u);
+                raw = __shfl_sync(0xffffffffu, raw, 0);
             } else {
-                rt = n_claimed < n_my ? j0 + n_claimed * stride : -1;
+                raw = n_issued < n_my ? (unsigned)(j0 + n_issued * stride) : 0xffffffffu;
             }
-            ++n_claimed;
-            return rt;
+            ++n_issued;
+            return raw < (unsigned)p.n_rowtiles ? (int)raw : -1;
         };
-        // class of a located tile: global table (pre-pass), this CTA's own table, or no mask at all
+        // class of a located tile: the pre-pass table (copied to shared memory when it fits), this
+        // CTA's own table, or no mask at all
         auto tile_class = [&](int i, int b, int t0) -> int {
             if (p.mask == nullptr) return TILE_FULL;
-            if (p.gtable != nullptr) return (int)__ldg(p.gtable + (long long)b * p.n_ttile + t0 / G::kTileRows);
+            if (p.gtable != nullptr) {
+                const long long idx = (long long)b * p.n_ttile + t0 / G::kTileRows;
+                return p.table_in_smem ? lds_u8(table + (uint32_t)idx) : (int)__ldg(p.gtable + idx);
+            }
             return lds_u8(table + i);
         };
-        bool live = true;
-        // tile and class are fetched one tile ahead: their latency hides behind the current tile
-        int rt_next = next_tile(), b_next = 0, t0_next = 0, cls_next = TILE_FULL;
-        if (rt_next >= 0) {
-            locate(rt_next, b_next, t0_next);
-            cls_next = tile_class(0, b_next, t0_next);
-        }
-        for (int i = 0; live && rt_next >= 0; ++i) {
-            const int b = b_next, t0 = t0_next, cls = cls_next;
-            rt_next = next_tile();
-            if (rt_next >= 0) {
-                locate(rt_next, b_next, t0_next);
-                cls_next = tile_class(i + 1, b_next, t0_next);
-            }
-            live = claim();
-            if (!live) break;
+        // announce a tile in the next ring slot and start its copy
+        auto put_tile = [&](int b, int t0, int cls) {
             const int s = s_ring;
             if (lane == 0) {
-                sts_s32(flags + 12 * s, cls);
-                sts_s32(flags + 12 * s + 4, b);
-                sts_s32(flags + 12 * s + 8, t0);
+                const long long yoff = (long long)b * p.syb + (long long)t0 * p.syt;
+                sts_desc(flags + 32 * s, cls, p.T - t0, yoff);
+                sts_s32(flags + 32 * s + 16, b);
+                sts_s32(flags + 32 * s + 20, t0);
                 const uint32_t full = bars + 8 * s;
                 if (cls != TILE_EMPTY) {
                     mbar_arrive_expect_tx(full, G::kBoxRows * G::kRowBytes);
@@ -450,12 +483,32 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
                 }
             }
             __syncwarp();
+        };
+        // One claim ahead: the next tile and its class are fetched while the current tile waits for
+        // its ring slot.  (Claiming further ahead was measured slower: the tiles in flight spread out
+        // in memory and the tail of the launch gets longer.)
+        bool live = true;
+        int rt = next_tile(), b = 0, t0 = 0, cls = TILE_FULL;
+        if (rt >= 0) {
+            locate(rt, b, t0);
+            cls = tile_class(0, b, t0);
+        }
+        for (int i = 0; live && rt >= 0; ++i) {
+            const int b_now = b, t0_now = t0, cls_now = cls;
+            rt = next_tile();
+            if (rt >= 0) {
+                locate(rt, b, t0);
+                cls = tile_class(i + 1, b, t0);
+            }
+            live = claim();
+            if (!live) break;
+            put_tile(b_now, t0_now, cls_now);
             advance();
         }
         // END marker: the consumers leave when they meet it
         if (live && claim()) {
             if (lane == 0) {
-                sts_s32(flags + 12 * s_ring, TILE_END);
+                sts_desc(flags + 32 * s_ring, TILE_END, 0, 0);
                 mbar_arrive(bars + 8 * s_ring);
             }
             __syncwarp();
@@ -491,35 +544,42 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
             S::pack(c, const_row);
         }
         const bool general_kernel = (p.mask != nullptr) || (p.res != nullptr);
+        const unsigned pitch = (unsigned)p.syt;  // output row pitch in bytes; the launcher keeps 8 rows within 32 bits
+
+        // per-thread constants of the tile loop
+        char* const ybase = p.y + (long long)rbase * p.syt + (long long)d0 * E::kBytes;
+        const uint32_t tbase = base + rbase * G::kRowBytes + cl * VB;
+        const int rbase_lim = ch_ok ? rbase : (1 << 28);  // makes rows_ok 0 for channel slices past dim
 
         int s = -1;
-        uint32_t ph = 1;
+        uint32_t ph = 0;
+        uint32_t trow = tbase - G::kStageBytes;
         for (;;) {
-            if (++s == kStages) s = 0;
-            if (s == 0) ph ^= 1;
+            trow += G::kStageBytes;
+            if (++s == kStages) {
+                s = 0;
+                ph ^= 1;
+                trow = tbase;
+            }
             if (!mbar_wait(bars + 8 * s, ph)) {
                 if (lane == 0) atomicAdd(p.timeouts, 1u);
                 break;  // no barrier is shared with the other warps: each leaves on its own
             }
-            const int cls = lds_s32(flags + 12 * s);
+            int cls, rows_valid;
+            long long yoff;
+            lds_desc(flags + 32 * s, cls, rows_valid, yoff);
             if (cls == TILE_END) break;
-            // box row of time t is (t - t0 + H); this thread reads box rows rbase .. rbase+R+H-1
-            const uint32_t trow = base + s * G::kStageBytes + rbase * G::kRowBytes + cl * VB;
-            const bool mixed = (cls == TILE_MIXED);
-            const int b = lds_s32(flags + 12 * s + 4);
-            const int tfirst = lds_s32(flags + 12 * s + 8) + rbase;
-            const long long mrow = (long long)b * p.smb;
-
-            // rows of this thread that exist in the output
-            const int rows_ok = ch_ok ? min(R, max(0, p.T - tfirst)) : 0;
-            char* yrow = p.y + (long long)b * p.syb + (long long)tfirst * p.syt + (long long)d0 * E::kBytes;
+            // box row of time t is (t - t0 + H); this thread reads box rows rbase .. rbase+R+H-1 at trow
+            const int rows_ok = min(R, max(0, rows_valid - rbase_lim));  // rows of this thread that exist
+            char* yrow = ybase + yoff;
             if (cls == TILE_EMPTY) {
                 // every tap of every row is masked and nothing was loaded
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bars + 8 * (kStages + s));
-#pragma unroll
-                for (int k = 0; k < R; ++k)
-                    if (rows_ok > k) S::stg(yrow + (long long)k * p.syt, const_row);
+                static_for<0, R>([&](auto kc) {
+                    constexpr int k = decltype(kc)::value;
+                    S::template stg_row<k>(row_addr<k>(yrow, pitch), const_row, rows_ok);
+                });
                 continue;
             }
             float2 hist[H > 0 ? H : 1][NP];
@@ -528,17 +588,30 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
                 uint32_t raw[NW];
                 S::lds(trow + w * G::kRowBytes, raw);
                 S::unpack(raw, hist[w]);
-                if (mixed) apply_mask<DT, VB>(hist[w], tile_mask(p, mrow, tfirst - H + w), p.skip);
             }
-            const char* rb = nullptr;
-            if (p.res != nullptr && !p.res_is_x && ch_ok)
-                rb = p.res + (long long)b * p.srb + (long long)d0 * E::kBytes;
-
             if (!general_kernel || (cls == TILE_FULL && p.res == nullptr)) {
-                process_rows<DT, W, VB, RPT, ACT, false, G::kRowBytes>(trow, mrow, p, false, nullptr, yrow, tfirst,
+                process_rows<DT, W, VB, RPT, ACT, false, G::kRowBytes>(trow, 1.0f, 0, p, false, nullptr, yrow, pitch, 0,
                                                                        rows_ok, hist, wp, bp);
             } else {
-                process_rows<DT, W, VB, RPT, ACT, true, G::kRowBytes>(trow, mrow, p, mixed, rb, yrow, tfirst,
+                const bool mixed = (cls == TILE_MIXED);
+                const int b = lds_s32(flags + 32 * s + 16);
+                const int tfirst = lds_s32(flags + 32 * s + 20) + rbase;
+                // lanes of one row group (a warp holds one or two) fetch the group's R + H mask values
+                constexpr int GL = LPR < 32 ? LPR : 32;
+                static_assert(R + H <= GL, "one mask value per lane of a row group");
+                const int msrc = lane & ~(GL - 1);
+                float mkv = 1.0f;
+                if (mixed) {
+                    const int j = lane & (GL - 1);
+                    if (j < R + H) mkv = tile_mask(p, (long long)b * p.smb, tfirst - H + j);
+#pragma unroll
+                    for (int w = 0; w < H; ++w)
+                        apply_mask<DT, VB>(hist[w], __shfl_sync(0xffffffffu, mkv, msrc + w), p.skip);
+                }
+                const char* rb = nullptr;
+                if (p.res != nullptr && !p.res_is_x && ch_ok)
+                    rb = p.res + (long long)b * p.srb + (long long)d0 * E::kBytes;
+                process_rows<DT, W, VB, RPT, ACT, true, G::kRowBytes>(trow, mkv, msrc, p, mixed, rb, yrow, pitch, tfirst,
                                                                       rows_ok, hist, wp, bp);
             }
             __syncwarp();
@@ -592,6 +665,9 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     if (n_rowtiles > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
     p.n_rowtiles = (int)n_rowtiles;
 
+    // row offsets inside a tile are computed in 32 bits
+    if (a.y_stride_t < 0 || (long long)a.y_stride_t * eb >= (1LL << 28)) return cudaErrorNotSupported;
+
     EncodeFn enc = encode_fn();
     if (enc == nullptr) return cudaErrorNotSupported;
     const CUtensorMapDataType dt = (DT == VC1D_F32)    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
@@ -622,13 +698,38 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     // byte per tile in shared memory, so the grid grows before a CTA would own more than 8192 tiles
     long long g = ((long long)sm_count() * per_sm) / n_slab;
     if (g < 1) g = 1;
-    if (a.mask != nullptr && n_rowtiles > g * 8192) g = (n_rowtiles + 8191) / 8192;
+    if (a.mask != nullptr && n_rowtiles > g * 8192) g = (n_rowtiles + 8191) / 8192;  // only matters without scratch
     if (g > n_rowtiles) g = n_rowtiles;
     if (g > 65535) g = 65535;
     p.ctas_per_slab = (int)g;
     const long long tiles_per_cta = (n_rowtiles + g - 1) / g;
-    if (a.mask != nullptr && tiles_per_cta > 8192) return cudaErrorNotSupported;  // the direct kernel takes it
-    const int table_bytes = a.mask != nullptr ? (int)((tiles_per_cta + 15) / 16 * 16) : 0;
+
+    // scratch: [4096 bytes of counters (one per slab + one), zero between launches | class byte per
+    // (sequence, time tile)].  The counter region has a fixed size so that no launch's class bytes
+    // can land where a later launch with more slabs keeps its counters.
+    p.sched = nullptr;
+    p.gtable = nullptr;
+    p.table_in_smem = 0;
+    const long long table_need = a.mask != nullptr ? n_rowtiles : 0;
+    const bool use_scratch = a.scratch != nullptr && 4LL * (n_slab + 1) <= kSchedCounterBytes &&
+                             a.scratch_bytes >= kSchedCounterBytes + table_need &&
+                             (reinterpret_cast<uintptr_t>(a.scratch) & 15u) == 0;
+    unsigned char* tab = nullptr;
+    int table_bytes = 0;  // class bytes in shared memory
+    if (use_scratch) {
+        p.sched = reinterpret_cast<unsigned int*>(a.scratch);
+        if (a.mask != nullptr) {
+            tab = reinterpret_cast<unsigned char*>(a.scratch) + kSchedCounterBytes;
+            if (n_rowtiles <= kSmemTableCap) {
+                p.table_in_smem = 1;
+                table_bytes = (int)((n_rowtiles + 15) / 16 * 16);
+            }
+        }
+    } else if (a.mask != nullptr) {
+        // static assignment: every CTA classifies its own tiles into shared memory
+        if (tiles_per_cta > 8192) return cudaErrorNotSupported;  // the direct kernel takes it
+        table_bytes = (int)((tiles_per_cta + 15) / 16 * 16);
+    }
     const int smem = G::smem_bytes(stages, table_bytes);
     {
         // opt in to > 48 KB of dynamic shared memory; the attribute is per device and sticky, so
@@ -643,33 +744,32 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
             if (dev >= 0 && dev < 64) granted[dev].store(smem, std::memory_order_release);
         }
     }
-    // scratch: [4096 bytes of counters (one per slab + one), zero between launches | class byte per
-    // (sequence, time tile)].  The counter region has a fixed size so that no launch's class bytes
-    // can land where a later launch with more slabs keeps its counters.
-    p.sched = nullptr;
-    p.gtable = nullptr;
-    const long long counters_bytes = kSchedCounterBytes;
-    const long long table_need = a.mask != nullptr ? n_rowtiles : 0;
-    if (4LL * (n_slab + 1) > counters_bytes) {
-        // more slabs than counters: static assignment
-    } else
-    if (a.scratch != nullptr && a.scratch_bytes >= counters_bytes + table_need &&
-        (reinterpret_cast<uintptr_t>(a.scratch) & 15u) == 0) {
-        p.sched = reinterpret_cast<unsigned int*>(a.scratch);
-        if (a.mask != nullptr) {
-            unsigned char* tab = reinterpret_cast<unsigned char*>(a.scratch) + counters_bytes;
-            const long long threads = n_rowtiles * 32;
-            k_classify_tiles<<<(unsigned)((threads + 255) / 256), 256, 0, s>>>(p, tab, G::kTileRows, G::kH);
-            const cudaError_t e = cudaGetLastError();
-            if (e != cudaSuccess) return e;
-            note_launch("classify");
-            p.gtable = tab;
-        }
+    // A masked launch with a pre-pass uses programmatic stream serialization for both kernels: each
+    // may start while its predecessor in the stream drains, and waits (griddep_wait) before it
+    // touches global memory, which hides the pre-pass and both launch latencies.  Launches without
+    // a pre-pass are serialized normally: letting dense launches overlap was measured slower.
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = (pdl_enabled() && tab != nullptr) ? 1 : 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (tab != nullptr) {
+        const long long threads = n_rowtiles * 32;
+        cfg.gridDim = dim3((unsigned)((threads + 255) / 256));
+        cfg.blockDim = dim3(256);
+        cfg.dynamicSmemBytes = 0;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, k_classify_tiles, p, tab, (int)G::kTileRows, (int)G::kH);
+        if (e != cudaSuccess) return e;
+        note_launch("classify");
+        p.gtable = tab;
     }
-    const dim3 grid((unsigned)n_slab, (unsigned)g);
+    cfg.gridDim = dim3((unsigned)n_slab, (unsigned)g);
+    cfg.blockDim = dim3(G::kThreads);
+    cfg.dynamicSmemBytes = (size_t)smem;
     note_launch("tma");
-    k_prefill_tma<DT, W, SLAB_BYTES, VB, RPT, ACT><<<grid, G::kThreads, smem, s>>>(tmap_x, p);
-    return cudaGetLastError();
+    return cudaLaunchKernelEx(&cfg, k_prefill_tma<DT, W, SLAB_BYTES, VB, RPT, ACT>, tmap_x, p);
 }
 
 template <int DT, int W, int SLAB_BYTES>

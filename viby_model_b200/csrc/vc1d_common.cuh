@@ -71,6 +71,16 @@ __device__ __forceinline__ void st_vec(void* p, const uint4& v) {
 }
 
 // ---------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
+// attribute may begin before its predecessor in the stream has finished; griddep_wait() returns
+// once the predecessor has completed and its writes are visible (at once when the attribute is
+// absent), so every thread calls it before its first global access.  griddep_launch_dependents()
+// lets the next such kernel of the stream start its own prologue.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------
 // Packed fp32x2 arithmetic (sm_100 issues one instruction for two fp32 lanes).
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ unsigned long long f2_bits(float2 v) {
@@ -285,6 +295,20 @@ struct Slice {
                          : "memory");
         else
             asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(g), "r"(r[0]), "r"(r[1]) : "memory");
+    }
+    // Streaming store of row K of a thread's rows, predicated on K < rows_ok inside the instruction
+    // (a guarded store written in C++ around inline assembly becomes a branch per row instead).
+    template <int K>
+    __device__ __forceinline__ static void stg_row(void* g, const uint32_t (&r)[kWords], int rows_ok) {
+        if constexpr (VB == 16)
+            asm volatile(
+                "{\n .reg .pred p;\n setp.gt.s32 p, %5, %6;\n @p st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};\n}" ::"l"(g),
+                "r"(r[0]), "r"(r[1]), "r"(r[kWords > 2 ? 2 : 0]), "r"(r[kWords > 3 ? 3 : 0]), "r"(rows_ok), "n"(K)
+                : "memory");
+        else
+            asm volatile("{\n .reg .pred p;\n setp.gt.s32 p, %3, %4;\n @p st.global.cs.v2.u32 [%0], {%1,%2};\n}" ::"l"(g),
+                         "r"(r[0]), "r"(r[1]), "r"(rows_ok), "n"(K)
+                         : "memory");
     }
     __device__ __forceinline__ static void unpack(const uint32_t (&r)[kWords], float2 (&f)[kPairs]) {
         if constexpr (DT == VC1D_F32) {

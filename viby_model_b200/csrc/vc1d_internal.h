@@ -13,6 +13,10 @@ namespace vc1d {
 // Number of SMs of the current device (cached per device ordinal).
 int sm_count();
 
+// Programmatic dependent launch between this library's kernels (on unless the environment sets
+// VC1D_NO_PDL=1; read once).
+bool pdl_enabled();
+
 // Kernel launch bookkeeping shared by all launchers.
 void note_launch(const char* kernel_name);
 
