@@ -324,7 +324,9 @@ def main():
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record()
         for _ in range(e2e_steps):
-            pipe.run(x_host, w, b, cfg.activation, m_host, y_host)
+            # consecutive batches pipeline into each other; every one is copied in and read back
+            pipe.run(x_host, w, b, cfg.activation, m_host, y_host, join=False)
+        pipe.join()
         f1.record()
         barrier()
         e2e_ms_total = max_over_ranks(f0.elapsed_time(f1))
@@ -333,7 +335,7 @@ def main():
         decode = None
         if not args.no_decode:
             decode = bench_decode(V, WL, dev, rank, world, barrier, max_over_ranks)
-    e2e_ok = bool(torch.equal(y_host[:2].to(dev), y[:2]))
+    e2e_ok = bool(torch.equal(y_host.to(dev), y))
 
     ms_per_step = ms_total / steps
     value = world * padded_tokens / (ms_per_step * 1e-3)
@@ -389,6 +391,7 @@ def main():
             "ms_per_step": e2e_ms,
             "steps": e2e_steps,
             "matches_device_result": e2e_ok,
+            "note": "rows behind each sequence's last valid position are never read by the kernel and are not sent",
         },
         "gpu_launches": timed_launches,
         "roofline": roofline,

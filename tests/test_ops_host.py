@@ -63,3 +63,11 @@ def test_cpu_tensors_are_refused_not_computed():
     with pytest.raises(ValueError, match="must be on a CUDA device"):
         V.causal_conv1d_update(torch.randn(2, 4), torch.randn(2, 4, 3), torch.randn(4, 4))
     assert V.launch_count() == 0 or not torch.cuda.is_available()
+
+
+def test_valid_prefix_lengths_of_a_host_mask():
+    from viby_model_b200.host_io import HostPrefill
+
+    m = torch.tensor([[1, 1, 0, 0], [0, 0, 0, 0], [1, 0, 1, 0], [1, 1, 1, 1], [0, 0, 0, 2]])
+    assert HostPrefill.valid_prefix_lengths(m) == [2, 0, 3, 4, 4]
+    assert HostPrefill.valid_prefix_lengths(m.bool()) == [2, 0, 3, 4, 4]

@@ -3,7 +3,13 @@
 ``HostPrefill`` streams a pinned-host batch through the GPU in batch chunks on three CUDA
 streams -- host-to-device copy, kernel, device-to-host copy -- so the copies of one chunk
 overlap the kernel of the next and the two PCIe directions run concurrently.  The device
-buffers are allocated once, in the constructor; ``run`` allocates nothing.
+buffers are allocated once, in the constructor; ``run`` allocates nothing on the device.
+
+Two things keep the PCIe link, which bounds this path, busy with useful bytes only:
+  * rows behind a sequence's last valid position are never read by the kernels (masked loads are
+    skipped), so they are not sent: only ``x[b, :last_valid_b]`` crosses the link;
+  * with ``join=False`` consecutive ``run`` calls pipeline into each other (the copy-in of the next
+    batch overlaps the copy-out of the previous one); buffer reuse is ordered by events per chunk.
 """
 from __future__ import annotations
 
@@ -29,9 +35,14 @@ class HostPrefill:
         n = (batch + self.chunk - 1) // self.chunk
         self.ev_in = [torch.cuda.Event() for _ in range(n)]
         self.ev_run = [torch.cuda.Event() for _ in range(n)]
+        self.ev_out = [torch.cuda.Event() for _ in range(n)]
+        self.last_h2d_bytes = 0  # bytes the most recent run() sent to the device
 
     @property
     def h2d_bytes(self) -> int:
+        """Bytes the most recent run() copied to the device (all of x and the mask before any run)."""
+        if self.last_h2d_bytes:
+            return self.last_h2d_bytes
         n = self.x_dev.numel() * self.x_dev.element_size()
         if self.m_dev is not None:
             n += self.m_dev.numel() * self.m_dev.element_size()
@@ -41,32 +52,61 @@ class HostPrefill:
     def d2h_bytes(self) -> int:
         return self.y_dev.numel() * self.y_dev.element_size()
 
+    @staticmethod
+    def valid_prefix_lengths(mask_host: torch.Tensor) -> list:
+        """Per sequence, the index after its last non-zero mask entry (0 when all are zero)."""
+        nz = mask_host != 0
+        T = nz.shape[1]
+        last = T - nz.flip(1).to(torch.uint8).argmax(1)
+        return torch.where(nz.any(1), last, torch.zeros_like(last)).tolist()
+
     def run(self, x_host: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], activation,
-            mask_host: Optional[torch.Tensor], y_host: torch.Tensor) -> torch.Tensor:
+            mask_host: Optional[torch.Tensor], y_host: torch.Tensor, *, join: bool = True) -> torch.Tensor:
         """x_host, y_host: pinned ``[batch, seqlen, dim]``; mask_host: pinned ``[batch, seqlen]`` or None.
-        Returns y_host; on return all work has been ordered into the caller's current stream."""
+        Returns y_host.  With ``join=True`` all work has been ordered into the caller's current stream on
+        return; with ``join=False`` call ``join()`` (or wait on ``ev_out[-1]``) before reading y_host."""
         main = torch.cuda.current_stream(self.device)
-        for s in (self.s_h2d, self.s_run, self.s_d2h):
-            s.wait_stream(main)
+        self.s_h2d.wait_stream(main)  # the inputs may come from work queued on the caller's stream
+        masked = self.m_dev is not None and mask_host is not None
+        lens = self.valid_prefix_lengths(mask_host) if masked else None
+        row_bytes = self.dim * self.x_dev.element_size()
+        sent = 0
         for i, b0 in enumerate(range(0, self.batch, self.chunk)):
             b1 = min(b0 + self.chunk, self.batch)
             with torch.cuda.stream(self.s_h2d):
-                self.x_dev[b0:b1].copy_(x_host[b0:b1], non_blocking=True)
-                if self.m_dev is not None and mask_host is not None:
+                self.s_h2d.wait_event(self.ev_run[i])  # the previous batch's kernel has read this chunk
+                if masked:
+                    for b in range(b0, b1):
+                        if lens[b] > 0:
+                            self.x_dev[b, : lens[b]].copy_(x_host[b, : lens[b]], non_blocking=True)
+                            sent += lens[b] * row_bytes
                     self.m_dev[b0:b1].copy_(mask_host[b0:b1], non_blocking=True)
+                    sent += (b1 - b0) * self.seqlen * self.m_dev.element_size()
+                else:
+                    self.x_dev[b0:b1].copy_(x_host[b0:b1], non_blocking=True)
+                    sent += (b1 - b0) * self.seqlen * row_bytes
                 self.ev_in[i].record(self.s_h2d)
             with torch.cuda.stream(self.s_run):
                 self.s_run.wait_event(self.ev_in[i])
+                self.s_run.wait_event(self.ev_out[i])  # the previous batch's result has left this chunk
                 causal_conv1d_fn(
                     self.x_dev[b0:b1].transpose(1, 2), weight, bias, activation=activation,
-                    attention_mask=self.m_dev[b0:b1] if (self.m_dev is not None and mask_host is not None) else None,
+                    attention_mask=self.m_dev[b0:b1] if masked else None,
                     out=self.y_dev[b0:b1].transpose(1, 2),
                 )
                 self.ev_run[i].record(self.s_run)
             with torch.cuda.stream(self.s_d2h):
                 self.s_d2h.wait_event(self.ev_run[i])
                 y_host[b0:b1].copy_(self.y_dev[b0:b1], non_blocking=True)
+                self.ev_out[i].record(self.s_d2h)
+        self.last_h2d_bytes = sent
+        if join:
+            self.join()
+        return y_host
+
+    def join(self) -> None:
+        """Order everything queued so far into the caller's current stream."""
+        main = torch.cuda.current_stream(self.device)
         main.wait_stream(self.s_d2h)
         main.wait_stream(self.s_run)
         main.wait_stream(self.s_h2d)
-        return y_host
