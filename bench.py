@@ -46,7 +46,7 @@ UNIT = "tokens/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
 # capture summarised under profiles/ (None until a capture of the current kernel exists).
-NCU_TRAFFIC_BYTES = {"canon_d_prefill_bf16": None}
+NCU_TRAFFIC_BYTES = {"canon_d_prefill_bf16": 319_850_000}
 
 
 def measured_peak_gbs():
@@ -233,6 +233,8 @@ def main():
     ap.add_argument("--kernel", default=None, help="force a prefill kernel (channel_last | tma)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--decode-saturating-only", action="store_true",
+                    help="run only the bandwidth-bound decode shape and print its figures (for profiling)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -276,6 +278,14 @@ def main():
         t = torch.tensor([v], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         return float(t.item())
+
+    if args.decode_saturating_only:
+        res = bench_decode_saturating(V, WL, dev, world, barrier, max_over_ranks)
+        if rank == 0:
+            print(json.dumps({"decode_saturating": res}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- workload: this rank's 32 sequences ---------------------------------------------------
     cfg = WL.CANON_D_PREFILL
@@ -467,24 +477,7 @@ def bench_decode(V, WL, dev, rank, world, barrier, max_over_ranks):
     graph_ms = max_over_ranks(e0.elapsed_time(e1)) / reps
     step_bytes = WL.decode_bytes(cfg.batch, cfg.dim, cfg.width, cfg.state_len, 2)
 
-    # bandwidth-bound decode shape: as many (sequence, channel) rows as one Canon-D prefill batch
-    Bs, Ds, Ls = 32768, 3456, cfg.state_len
-    ws, bs = WL.weights(cfg.cfg, Ds, cfg.width, cfg.dtype, device=dev)
-    xs = torch.randn(Bs, Ds, device=dev).to(cfg.dtype)
-    ss = torch.randn(Bs, Ds, Ls, device=dev).to(cfg.dtype)
-    yo = torch.empty_like(xs)
-    for _ in range(5):
-        V.causal_conv1d_update(xs, ss, ws, bs, activation="silu", out=yo)
-    barrier()
-    n = 20
-    e0.record()
-    for _ in range(n):
-        V.causal_conv1d_update(xs, ss, ws, bs, activation="silu", out=yo)
-    e1.record()
-    barrier()
-    sat_ms = max_over_ranks(e0.elapsed_time(e1)) / n
-    sat_bytes = WL.decode_bytes(Bs, Ds, cfg.width, Ls, 2)
-    peak, _ = measured_peak_gbs()
+    saturating = bench_decode_saturating(V, WL, dev, world, barrier, max_over_ranks)
     return {
         "config": {"workload": cfg.name, "batch_per_gpu": cfg.batch, "channels": cfg.dim, "state_len": cfg.state_len,
                    "width": cfg.width, "steps": cfg.steps, "prefill_len": cfg.prefill_len},
@@ -494,13 +487,37 @@ def bench_decode(V, WL, dev, rank, world, barrier, max_over_ranks):
         "us_per_step_eager": eager_ms * 1e3 / cfg.steps,
         "bytes_per_step": step_bytes,
         "gbs_graph": step_bytes * cfg.steps / (graph_ms * 1e-3) / 1e9,
-        "saturating": {
-            "batch": Bs, "channels": Ds, "state_len": Ls, "activation": "silu",
-            "ms_per_step": sat_ms, "bytes_per_step": sat_bytes,
-            "achieved_gbs": sat_bytes / (sat_ms * 1e-3) / 1e9,
-            "frac_of_measured_peak": sat_bytes / (sat_ms * 1e-3) / 1e9 / peak,
-            "tokens_per_s": world * Bs / (sat_ms * 1e-3),
-        },
+        "saturating": saturating,
+    }
+
+
+def bench_decode_saturating(V, WL, dev, world, barrier, max_over_ranks):
+    """Bandwidth-bound decode shape: as many (sequence, channel) rows as one Canon-D prefill batch."""
+    cfg = WL.DECODE_CANON_B
+    Bs, Ds, Ls = 32768, 3456, cfg.state_len
+    ws, bs = WL.weights(cfg.cfg, Ds, cfg.width, cfg.dtype, device=dev)
+    xs = torch.randn(Bs, Ds, device=dev).to(cfg.dtype)
+    ss = torch.randn(Bs, Ds, Ls, device=dev).to(cfg.dtype)
+    yo = torch.empty_like(xs)
+    for _ in range(5):
+        V.causal_conv1d_update(xs, ss, ws, bs, activation="silu", out=yo)
+    barrier()
+    n = 20
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        V.causal_conv1d_update(xs, ss, ws, bs, activation="silu", out=yo)
+    e1.record()
+    barrier()
+    sat_ms = max_over_ranks(e0.elapsed_time(e1)) / n
+    sat_bytes = WL.decode_bytes(Bs, Ds, cfg.width, Ls, 2)
+    peak, _ = measured_peak_gbs()
+    return {
+        "batch": Bs, "channels": Ds, "state_len": Ls, "activation": "silu",
+        "ms_per_step": sat_ms, "bytes_per_step": sat_bytes,
+        "achieved_gbs": sat_bytes / (sat_ms * 1e-3) / 1e9,
+        "frac_of_measured_peak": sat_bytes / (sat_ms * 1e-3) / 1e9 / peak,
+        "tokens_per_s": world * Bs / (sat_ms * 1e-3),
     }
 
 
