@@ -271,3 +271,93 @@ def seeded(shape, seed: int, dist: str = "normal", dtype=torch.float32) -> torch
     else:
         raise ValueError(dist)
     return t.to(dtype)
+
+
+def causal_conv1d_bwd_ref(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    dy: torch.Tensor,
+    activation=None,
+    *,
+    attention_mask: Optional[torch.Tensor] = None,
+    residual: bool = False,
+    residual_masked: bool = False,
+    compute_dtype: torch.dtype = torch.float64,
+):
+    """Oracle of the backward pass of causal_conv1d_fn (+ fused mask / residual), as explicit
+    shifted sums.  x, dy [B,D,T]; weight [D,W]; returns (dx [B,D,T] in x's dtype, dweight [D,W],
+    dbias [D] or None), the last two in ``compute_dtype``.
+
+    Follows the arithmetic of causal-conv1d-mps/causal_conv1d_mps/causal_conv1d.metal:1354-1483
+    (fused BTD backward) and :803-854 (plain backward):
+        pre[t]   = bias + sum_w weight[w] * (x*mask)[t-(W-1-w)]
+        g[t]     = dy[t] * silu'(pre[t])           silu'(z) = s(z) * (1 + z*(1 - s(z)))
+        dx[t]    = [residual] dy[t] + mask[t] * sum_w weight[w] * g[t+(W-1-w)]
+        dweight[w] = sum_{b,t} (x*mask)[t-(W-1-w)] * g[t];   dbias = sum_{b,t} g[t]
+    ``residual`` adds the unmasked input (model/model.py:491); ``residual_masked`` the masked one
+    (the PyTorch branch, model/model.py:595-602, 675).
+    """
+    B, D, T = x.shape
+    W = weight.shape[1]
+    cd = compute_dtype
+    xm = apply_mask(x, attention_mask).to(cd)  # the mask multiply is rounded to the I/O dtype first
+    w = weight.to(x.dtype).to(cd) if weight.dtype != torch.float32 else weight.to(cd)
+    g = dy.to(cd).clone()
+    if _act(activation):
+        pre = torch.zeros(B, D, T, dtype=cd)
+        if bias is not None:
+            pre += (bias.to(x.dtype) if bias.dtype != torch.float32 else bias).to(cd).view(1, D, 1)
+        for k in range(W):
+            s = W - 1 - k
+            if s < T:
+                pre[..., s:] += w[:, k].view(1, D, 1) * xm[..., : T - s]
+        sig = torch.sigmoid(pre)
+        g = g * sig * (1 + pre * (1 - sig))
+    dconv = torch.zeros(B, D, T, dtype=cd)
+    dweight = torch.zeros(D, W, dtype=cd)
+    for k in range(W):
+        s = W - 1 - k
+        if s < T:
+            dconv[..., : T - s] += w[:, k].view(1, D, 1) * g[..., s:]
+            dweight[:, k] = (xm[..., : T - s] * g[..., s:]).sum(dim=(0, 2))
+    if attention_mask is not None:
+        m = attention_mask.to(cd).unsqueeze(1)
+        dconv = dconv * m
+    dx = dconv
+    if residual_masked:
+        dx = dx + dy.to(cd) * (attention_mask.to(cd).unsqueeze(1) if attention_mask is not None else 1)
+    elif residual:
+        dx = dx + dy.to(cd)
+    dbias = g.sum(dim=(0, 2)) if bias is not None else None
+    return dx.to(x.dtype), dweight, dbias
+
+
+def causal_conv1d_update_bwd_ref(x, conv_state, weight, bias, dy, activation=None, *, residual: bool = False,
+                                 compute_dtype: torch.dtype = torch.float64):
+    """Oracle of the backward pass of one decode step (shifting state), restating
+    causal_conv1d.metal:1738-1845 for a shifting state: cat = [state | x]; y = act(bias + cat[-W:] . weight) [+ x].
+    Returns (dx [B,D], dstate [B,D,L], dweight [D,W], dbias [D]|None); dstate is the gradient of y
+    with respect to the state the step started from (columns that no tap reads get zero)."""
+    B, D = x.shape
+    L = conv_state.shape[-1]
+    W = weight.shape[1]
+    cd = compute_dtype
+    cat = torch.cat([conv_state.to(cd), x.to(cd).unsqueeze(-1)], dim=-1)  # [B,D,L+1]
+    w = weight.to(x.dtype).to(cd) if weight.dtype != torch.float32 else weight.to(cd)
+    win = cat[..., -W:]
+    g = dy.to(cd).clone()
+    if _act(activation):
+        pre = (win * w.unsqueeze(0)).sum(-1)
+        if bias is not None:
+            pre = pre + (bias.to(x.dtype) if bias.dtype != torch.float32 else bias).to(cd)
+        sig = torch.sigmoid(pre)
+        g = g * sig * (1 + pre * (1 - sig))
+    dwin = g.unsqueeze(-1) * w.unsqueeze(0)  # [B,D,W]
+    dcat = torch.zeros_like(cat)
+    dcat[..., -W:] = dwin
+    dx = dcat[..., -1] + (dy.to(cd) if residual else 0)
+    dstate = dcat[..., :-1]
+    dweight = (g.unsqueeze(-1) * win).sum(0)
+    dbias = g.sum(0) if bias is not None else None
+    return dx.to(x.dtype), dstate.to(x.dtype), dweight, dbias

@@ -55,13 +55,15 @@ class GoldenCase:
                 f"act={m['activation']} mask={m['mask']}]")
 
 
-def load_golden():
-    z = np.load(GOLDEN)
+def load_golden(path=GOLDEN):
+    z = np.load(path)
     meta = json.loads(bytes(z["meta"]).decode())
     return [GoldenCase(m, z) for m in meta]
 
 
 GOLDEN_CASES = load_golden()
+# gradients of the reference's CanonLayer (generator: tests/golden/make_bwd_golden.py)
+GOLDEN_BWD_CASES = load_golden(ROOT / "tests" / "golden" / "canon_bwd_golden.npz")
 
 
 @pytest.fixture(scope="session")
