@@ -154,6 +154,53 @@ VC1D_API int vc1d_prefill(const vc1d_prefill_args* args, void* stream);
 VC1D_API int vc1d_prefill_noalloc(const vc1d_prefill_args* args, void* stream);
 
 /*
+ * Backward of prefill: gradients of causal_conv1d_fn with the fused mask / residual.
+ * Replaces what the reference gets from torch.autograd through F.conv1d (model/model.py:664-670)
+ * and from the backward kernels of its Metal package
+ * (causal-conv1d-mps/causal_conv1d_mps/causal_conv1d.metal:803-854 and :1354-1483; host side
+ * causal_conv1d_kernel.mm:517-670, 672-779; Python contract autograd.py:116-151, 305-338):
+ *     pre[t]  = bias + sum_w weight[w] * (x*mask)[t-(W-1-w)]
+ *     g[t]    = dy[t] * silu'(pre[t])                       (g = dy without activation)
+ *     dx[t]   = (residual ? dy[t] : 0) + mask[t] * sum_w weight[w] * g[t+(W-1-w)]
+ *     dweight[d,w] += sum_{b,t} (x*mask)[t-(W-1-w)] * g[t];    dbias[d] += sum_{b,t} g[t]
+ * x, dy, dx: logical [batch, dim, seqlen], element strides per tensor.  dweight [dim, width] and
+ * dbias [dim] are fp32, contiguous, and ACCUMULATED into (the caller zeroes them), as the
+ * reference accumulates in fp32 and casts afterwards (causal_conv1d_kernel.mm:553-557, 771-776).
+ * Sums over (batch, time) use atomic adds of per-CTA partial sums: their order is not fixed.
+ */
+typedef struct vc1d_prefill_bwd_args {
+    uint32_t struct_size;   /* sizeof(vc1d_prefill_bwd_args) */
+    int32_t dtype;          /* x, dy, dx */
+    int32_t wdtype;         /* weight and bias: same as dtype, or VC1D_F32 */
+    int32_t activation;     /* VC1D_ACT_* of the forward pass */
+    int32_t batch, dim, seqlen, width;
+    const void* x;
+    const void* dy;
+    void* dx;               /* must not overlap x or dy */
+    const void* weight;     /* [dim, width] */
+    const void* bias;       /* [dim] or NULL (the forward bias: needed to rebuild pre[t]) */
+    int64_t x_stride_b, x_stride_d, x_stride_t;   /* in elements */
+    int64_t dy_stride_b, dy_stride_d, dy_stride_t;
+    int64_t dx_stride_b, dx_stride_d, dx_stride_t;
+    int64_t w_stride_d, w_stride_w;
+    const void* mask;       /* [batch, seqlen] or NULL */
+    int32_t mask_dtype;
+    int32_t residual;       /* 1: the forward added x to its output, so dx += dy */
+    int64_t mask_stride_b, mask_stride_t;
+    float* dweight;         /* [dim, width] fp32, accumulated; NULL = not wanted */
+    float* dbias;           /* [dim] fp32, accumulated; NULL = not wanted */
+    int32_t kernel;         /* VC1D_KERNEL_AUTO | VC1D_KERNEL_GENERIC | VC1D_KERNEL_TMA */
+    int32_t tma_stages;     /* tuning of the TMA-staged kernel: 0 = automatic */
+    int32_t tma_ctas_per_sm;
+    int32_t reserved;
+    void* scratch;          /* as in vc1d_prefill_args (only the counter region is used) */
+    int64_t scratch_bytes;
+} vc1d_prefill_bwd_args;
+
+VC1D_API int vc1d_prefill_bwd(const vc1d_prefill_bwd_args* args, void* stream);
+VC1D_API uint32_t vc1d_sizeof_prefill_bwd_args(void);
+
+/*
  * Decode: causal_conv1d_update.
  * Replaces the external CUDA kernel the reference calls at model/model.py:305-311 and
  * the PyTorch single step at model/model.py:372-398:

@@ -1,0 +1,220 @@
+"""Backward pass of causal_conv1d_fn on the GPU: both kernels against the float64 oracle, the
+autograd wiring against finite differences (the reference's own gradient-test design,
+causal-conv1d-mps/test.py:8-80, 259-321), and size-independent properties at the bench shape."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+if not torch.cuda.is_available():
+    pytest.skip("needs a CUDA device", allow_module_level=True)
+
+import viby_model_b200 as V  # noqa: E402
+from oracle import canon_oracle as O  # noqa: E402
+
+DEV = torch.device("cuda", 0)
+ULP = {torch.float32: 2.0 ** -23, torch.bfloat16: 2.0 ** -7, torch.float16: 2.0 ** -10}  # relative spacing
+
+
+def make(B, T, D, W, dtype, seed, channel_last=True):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(B, T, D, generator=g).to(dtype)
+    dy = torch.randn(B, T, D, generator=g).to(dtype)
+    w = (torch.rand(D, W, generator=g) - 0.5).to(dtype)
+    b = (torch.rand(D, generator=g) - 0.5).to(dtype)
+    if channel_last:
+        x, dy = x.transpose(1, 2), dy.transpose(1, 2)
+    else:
+        x, dy = x.transpose(1, 2).contiguous(), dy.transpose(1, 2).contiguous()
+    return x, dy, w, b
+
+
+def mask_for(kind, B, T, seed):
+    g = torch.Generator().manual_seed(seed)
+    if kind == "none":
+        return None
+    if kind == "right":
+        lens = torch.randint(max(T // 3, 1), T + 1, (B,), generator=g)
+        m = (torch.arange(T)[None, :] < lens[:, None]).to(torch.int64)
+        m[0, :] = 1
+        if B > 1:
+            m[1, 2:] = 0
+        return m
+    return (torch.rand(B, T, generator=g) > 0.3).to(torch.int64)  # holes
+
+
+def magnitude(x, w, b, dy, act, m, residual):
+    """Per-element sum of |terms| of dx: the scale rounding errors are measured against."""
+    B, D, T = x.shape
+    W = w.shape[1]
+    _, dwa, _ = O.causal_conv1d_bwd_ref(x, w, b, dy, act, attention_mask=m)
+    dxa, _, _ = O.causal_conv1d_bwd_ref(x.abs(), w.abs(), None, dy.abs(), None, attention_mask=m, residual=residual)
+    return dxa.double(), dwa
+
+
+def check(x, dy, w, b, act, m, residual, kernel):
+    dev = lambda t: None if t is None else t.to(DEV)  # noqa: E731
+    before = V.launch_count()
+    dx, dw, db = V.causal_conv1d_bwd(dev(x), dev(w), dev(b), dev(dy), act, attention_mask=dev(m), residual=residual,
+                                     kernel=kernel)
+    assert V.launch_count() == before + 1
+    if kernel is not None:
+        assert V.last_kernel() == "bwd_" + kernel
+    rdx, rdw, rdb = O.causal_conv1d_bwd_ref(x, w, b, dy, act, attention_mask=m, residual=residual)
+    # dx: an fp32 sum rounded once; kernel and oracle may round a borderline value to neighbouring
+    # numbers, so the bound is one step of the output type at the scale of the summed |terms|
+    # (SiLU' scales each term by at most 1.1)
+    scale, _ = magnitude(x, w, b, dy, act, m, residual)
+    err = (dx.cpu().double() - rdx.double()).abs()
+    bound = 1.1 * scale * (ULP[x.dtype] * 1.01 + 4e-6) + 1e-7
+    assert bool((err <= bound).all()), f"dx: max err/bound {(err / bound).max().item():.2f}"
+    assert dx.stride() == x.stride() and dx.dtype == x.dtype
+    # parameter gradients: fp32 sums of exact products
+    n = x.shape[0] * x.shape[2]
+    wscale = rdw.abs().max().item() + 1e-3
+    assert torch.allclose(dw.cpu().double(), rdw, rtol=2e-4, atol=2e-5 * wscale * n ** 0.5)
+    if b is not None:
+        bscale = rdb.abs().max().item() + 1e-3
+        assert torch.allclose(db.cpu().double(), rdb, rtol=2e-4, atol=2e-5 * bscale * n ** 0.5)
+    else:
+        assert db is None
+    return dx, dw, db
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("W", [2, 3, 4])
+@pytest.mark.parametrize("act", [None, "silu"])
+@pytest.mark.parametrize("mask_kind", ["none", "right", "holes"])
+@pytest.mark.parametrize("kernel", ["generic", "tma"])
+def test_backward_kernels_match_oracle(dtype, W, act, mask_kind, kernel):
+    for (B, T, D) in ((2, 37, 64), (3, 200, 192), (1, 130, 1000 if dtype != torch.float32 else 500)):
+        x, dy, w, b = make(B, T, D, W, dtype, seed=B * T + W)
+        m = mask_for(mask_kind, B, T, seed=T)
+        for residual in (False, True):
+            check(x, dy, w, b, act, m, residual, kernel)
+    torch.cuda.synchronize()
+    assert V.tma_timeouts() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_backward_without_bias_and_time_major_layout(dtype):
+    x, dy, w, _ = make(2, 96, 128, 4, dtype, seed=3)
+    check(x, dy, w, None, "silu", mask_for("right", 2, 96, 1), True, None)
+    x, dy, w, b = make(2, 96, 40, 4, dtype, seed=4, channel_last=False)  # contiguous [B,D,T]: generic kernel
+    check(x, dy, w, b, "silu", None, False, None)
+    assert V.last_kernel() == "bwd_generic"
+
+
+def test_backward_kernels_agree_and_repeat():
+    """Both kernels produce the same dx bits; launches back to back reuse the scheduler scratch."""
+    x, dy, w, b = make(4, 700, 960, 4, torch.bfloat16, seed=9)
+    m = mask_for("right", 4, 700, 5)
+    dev = lambda t: t.to(DEV)  # noqa: E731
+    ref = None
+    for _ in range(3):
+        dx, dw, db = V.causal_conv1d_bwd(dev(x), dev(w), dev(b), dev(dy), "silu", attention_mask=dev(m), residual=True,
+                                         kernel="tma")
+        if ref is None:
+            ref = dx.clone()
+        assert torch.equal(dx, ref)
+    dxg, dwg, dbg = V.causal_conv1d_bwd(dev(x), dev(w), dev(b), dev(dy), "silu", attention_mask=dev(m), residual=True,
+                                        kernel="generic")
+    assert torch.equal(dxg, ref)
+    assert torch.allclose(dwg, dw, rtol=1e-4, atol=1e-3)
+    assert torch.allclose(dbg, db, rtol=1e-4, atol=1e-3)
+    torch.cuda.synchronize()
+    assert V.tma_timeouts() == 0
+
+
+def numerical_grads(f, inputs, eps=1e-3):
+    grads = []
+    for inp in inputs:
+        g = torch.zeros_like(inp)
+        flat, gflat = inp.data.view(-1), g.view(-1)
+        for j in range(flat.numel()):
+            keep = flat[j].item()
+            flat[j] = keep + eps
+            lp = f().sum().item()
+            flat[j] = keep - eps
+            lm = f().sum().item()
+            flat[j] = keep
+            gflat[j] = (lp - lm) / (2 * eps)
+        grads.append(g)
+    return grads
+
+
+@pytest.mark.parametrize("api", ["fn", "fused", "fwd"])
+def test_autograd_matches_finite_differences(api):
+    g = torch.Generator().manual_seed(11)
+    B, T, D, W = 2, 12, 8, 4
+    x = torch.randn(B, T, D, generator=g, dtype=torch.float32).to(DEV).requires_grad_(True)
+    w = torch.randn(D, W, generator=g).to(DEV).requires_grad_(True)
+    b = torch.randn(D, generator=g).to(DEV).requires_grad_(True)
+    mask = torch.ones(B, T, device=DEV)
+    mask[1, 9:] = 0
+    weights = torch.randn(B, T, D, generator=g).to(DEV)  # so that the loss is not a plain sum
+
+    def f():
+        if api == "fn":
+            y = V.causal_conv1d_fn(x.transpose(1, 2), w, b, activation="silu", attention_mask=mask,
+                                   residual=True).transpose(1, 2)
+        elif api == "fused":
+            y = V.short_conv_fused(x, w, b, attention_mask=mask, activation=True, residual=True)
+        else:
+            y = V.causal_conv1d_fwd(x.transpose(1, 2).contiguous(), w, b, True).transpose(1, 2)
+        return y * weights
+
+    for t in (x, w, b):
+        t.grad = None
+    f().sum().backward()
+    analytical = [x.grad.clone(), w.grad.clone(), b.grad.clone()]
+    with torch.no_grad():
+        numerical = numerical_grads(f, [x, w, b])
+    for a, n in zip(analytical, numerical):
+        assert torch.allclose(a, n, atol=2e-2, rtol=2e-2), (a - n).abs().max().item()
+
+
+def test_autograd_residual_tensor_and_no_grad_path():
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(2, 64, 128, generator=g).to(torch.bfloat16).to(DEV)
+    r = torch.randn(2, 64, 128, generator=g).to(torch.bfloat16).to(DEV).requires_grad_(True)
+    w = torch.randn(128, 4, generator=g).to(torch.bfloat16).to(DEV).requires_grad_(True)
+    y = V.causal_conv1d_fn(x.transpose(1, 2), w, None, activation="silu", residual=r.transpose(1, 2))
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    assert torch.equal(r.grad, dy.transpose(1, 2))
+    assert w.grad is not None and w.grad.dtype == torch.bfloat16
+    before = V.launch_count()
+    with torch.no_grad():
+        V.causal_conv1d_fn(x.transpose(1, 2), w, None, activation="silu")
+    assert V.launch_count() == before + 1
+    with pytest.raises(NotImplementedError):
+        V.causal_conv1d_fn(x.transpose(1, 2), w, None, initial_states=torch.zeros(2, 128, 3, dtype=torch.bfloat16, device=DEV))
+
+
+def test_backward_bench_shape_properties():
+    """Bench shape (32 x 1024 x 3456 bf16, masked): linearity in dy, no gradient into masked inputs
+    (residual aside), and dbias equal to the sum of g over rows, checked on a channel sample."""
+    from viby_model_b200 import workloads as WL
+
+    cfg = WL.CANON_D_PREFILL
+    w, b = WL.weights(cfg.cfg, cfg.dim, cfg.width, cfg.dtype, device=DEV)
+    x = WL.prefill_inputs(cfg, list(range(cfg.batch))).to(DEV)
+    m = WL.attention_mask(cfg, device=DEV, dtype=torch.bool)
+    g = torch.Generator(device=DEV).manual_seed(3)
+    dy = torch.randn(x.shape, generator=g, device=DEV).to(cfg.dtype)
+    xv, dyv = x.transpose(1, 2), dy.transpose(1, 2)
+    dx1, dw1, db1 = V.causal_conv1d_bwd(xv, w, b, dyv, "silu", attention_mask=m)
+    assert V.last_kernel() == "bwd_tma"
+    dx2, dw2, db2 = V.causal_conv1d_bwd(xv, w, b, (2 * dy).transpose(1, 2), "silu", attention_mask=m)
+    assert torch.equal(dx2, 2 * dx1)  # scaling by two is exact in binary floating point
+    assert torch.allclose(dw2, 2 * dw1, rtol=1e-4, atol=1e-2)
+    assert bool((dx1.transpose(1, 2)[~m] == 0).all())
+    # oracle on a slice of channels and sequences
+    ch = slice(1000, 1064)
+    rdx, rdw, rdb = O.causal_conv1d_bwd_ref(xv[:4, ch].cpu(), w[ch].cpu(), b[ch].cpu(), dyv[:4, ch].cpu(), "silu",
+                                            attention_mask=m[:4].cpu())
+    err = (dx1[:4, ch].cpu().double() - rdx.double()).abs().max().item()
+    assert err < 0.05
+    torch.cuda.synchronize()
+    assert V.tma_timeouts() == 0

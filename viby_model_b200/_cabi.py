@@ -82,6 +82,50 @@ class PrefillArgs(C.Structure):
     ]
 
 
+class PrefillBwdArgs(C.Structure):
+    """struct vc1d_prefill_bwd_args"""
+
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("dtype", C.c_int32),
+        ("wdtype", C.c_int32),
+        ("activation", C.c_int32),
+        ("batch", C.c_int32),
+        ("dim", C.c_int32),
+        ("seqlen", C.c_int32),
+        ("width", C.c_int32),
+        ("x", C.c_void_p),
+        ("dy", C.c_void_p),
+        ("dx", C.c_void_p),
+        ("weight", C.c_void_p),
+        ("bias", C.c_void_p),
+        ("x_stride_b", C.c_int64),
+        ("x_stride_d", C.c_int64),
+        ("x_stride_t", C.c_int64),
+        ("dy_stride_b", C.c_int64),
+        ("dy_stride_d", C.c_int64),
+        ("dy_stride_t", C.c_int64),
+        ("dx_stride_b", C.c_int64),
+        ("dx_stride_d", C.c_int64),
+        ("dx_stride_t", C.c_int64),
+        ("w_stride_d", C.c_int64),
+        ("w_stride_w", C.c_int64),
+        ("mask", C.c_void_p),
+        ("mask_dtype", C.c_int32),
+        ("residual", C.c_int32),
+        ("mask_stride_b", C.c_int64),
+        ("mask_stride_t", C.c_int64),
+        ("dweight", C.c_void_p),
+        ("dbias", C.c_void_p),
+        ("kernel", C.c_int32),
+        ("tma_stages", C.c_int32),
+        ("tma_ctas_per_sm", C.c_int32),
+        ("reserved", C.c_int32),
+        ("scratch", C.c_void_p),
+        ("scratch_bytes", C.c_int64),
+    ]
+
+
 class UpdateArgs(C.Structure):
     """struct vc1d_update_args"""
 
@@ -120,6 +164,8 @@ class UpdateArgs(C.Structure):
 EXPORTS = {
     "vc1d_prefill": (C.c_int, [C.POINTER(PrefillArgs), C.c_void_p]),
     "vc1d_prefill_noalloc": (C.c_int, [C.POINTER(PrefillArgs), C.c_void_p]),
+    "vc1d_prefill_bwd": (C.c_int, [C.POINTER(PrefillBwdArgs), C.c_void_p]),
+    "vc1d_sizeof_prefill_bwd_args": (C.c_uint32, []),
     "vc1d_update": (C.c_int, [C.POINTER(UpdateArgs), C.c_void_p]),
     "vc1d_abi_version": (C.c_int, []),
     "vc1d_sizeof_prefill_args": (C.c_uint32, []),
@@ -156,8 +202,10 @@ def _load() -> C.CDLL:
         fn.argtypes = argtypes
     if lib.vc1d_abi_version() != VC1D_ABI_VERSION:
         raise ImportError(f"{path}: ABI version {lib.vc1d_abi_version()} != binding {VC1D_ABI_VERSION}")
-    if lib.vc1d_sizeof_prefill_args() != C.sizeof(PrefillArgs) or lib.vc1d_sizeof_update_args() != C.sizeof(
-        UpdateArgs
+    if (
+        lib.vc1d_sizeof_prefill_args() != C.sizeof(PrefillArgs)
+        or lib.vc1d_sizeof_update_args() != C.sizeof(UpdateArgs)
+        or lib.vc1d_sizeof_prefill_bwd_args() != C.sizeof(PrefillBwdArgs)
     ):
         raise ImportError(f"{path}: argument struct layout differs from the binding; rebuild it")
     return lib

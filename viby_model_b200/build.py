@@ -29,6 +29,11 @@ SOURCES = [
     "prefill_tma_bf16.cu",
     "prefill_tma_f16.cu",
     "prefill_noalloc.cu",
+    "prefill_bwd_generic.cu",
+    "prefill_bwd_tma.cu",
+    "prefill_bwd_tma_f32.cu",
+    "prefill_bwd_tma_bf16.cu",
+    "prefill_bwd_tma_f16.cu",
     "update.cu",
 ]
 

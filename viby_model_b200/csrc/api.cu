@@ -123,6 +123,39 @@ bool time_major_ok(const vc1d_prefill_args* a) {
     return true;
 }
 
+int check_prefill_bwd(const vc1d_prefill_bwd_args* a) {
+    if (a == nullptr) return VC1D_E_NULL;
+    if (a->struct_size != sizeof(vc1d_prefill_bwd_args)) return VC1D_E_STRUCT;
+    if (!is_io_dtype(a->dtype)) return VC1D_E_DTYPE;
+    if (a->wdtype != a->dtype && a->wdtype != VC1D_F32) return VC1D_E_DTYPE;
+    if (a->activation != VC1D_ACT_NONE && a->activation != VC1D_ACT_SILU) return VC1D_E_ACTIVATION;
+    if (a->width < 2 || a->width > 4) return VC1D_E_WIDTH;
+    if (a->batch < 0 || a->dim < 0 || a->seqlen < 0) return VC1D_E_SHAPE;
+    if (a->mask != nullptr && !is_mask_dtype(a->mask_dtype)) return VC1D_E_DTYPE;
+    if (a->kernel != VC1D_KERNEL_AUTO && a->kernel != VC1D_KERNEL_GENERIC && a->kernel != VC1D_KERNEL_TMA)
+        return VC1D_E_SHAPE;
+    if ((long long)a->batch * a->dim * a->seqlen == 0) return VC1D_OK;
+    if (a->x == nullptr || a->dy == nullptr || a->dx == nullptr || a->weight == nullptr) return VC1D_E_NULL;
+    const int eb = elem_bytes(a->dtype);
+    const Range rx = extent3(a->x, eb, a->batch, a->x_stride_b, a->dim, a->x_stride_d, a->seqlen, a->x_stride_t);
+    const Range rg = extent3(a->dy, eb, a->batch, a->dy_stride_b, a->dim, a->dy_stride_d, a->seqlen, a->dy_stride_t);
+    const Range rd = extent3(a->dx, eb, a->batch, a->dx_stride_b, a->dim, a->dx_stride_d, a->seqlen, a->dx_stride_t);
+    if (overlaps(rx, rd) || overlaps(rg, rd)) return VC1D_E_ALIAS;  // neighbours' rows are read after dx rows are written
+    return VC1D_OK;
+}
+
+bool bwd_channel_last_ok(const vc1d_prefill_bwd_args* a) {
+    const int eb = elem_bytes(a->dtype);
+    const int vec = 16 / eb;
+    if (a->dim % vec != 0) return false;
+    if (a->x_stride_d != 1 || a->dy_stride_d != 1 || a->dx_stride_d != 1) return false;
+    if (!aligned16(a->x) || !aligned16(a->dy) || !aligned16(a->dx)) return false;
+    if (a->x_stride_b % vec || a->x_stride_t % vec || a->dy_stride_b % vec || a->dy_stride_t % vec ||
+        a->dx_stride_b % vec || a->dx_stride_t % vec)
+        return false;
+    return true;
+}
+
 int check_update(const vc1d_update_args* a) {
     if (a == nullptr) return VC1D_E_NULL;
     if (a->struct_size != sizeof(vc1d_update_args)) return VC1D_E_STRUCT;
@@ -200,6 +233,35 @@ VC1D_API int vc1d_prefill(const vc1d_prefill_args* a, void* stream) {
     }
     return (int)err;
 }
+
+VC1D_API int vc1d_prefill_bwd(const vc1d_prefill_bwd_args* a, void* stream) {
+    using namespace vc1d;
+    const int st = check_prefill_bwd(a);
+    if (st != VC1D_OK) return st;
+    if ((long long)a->batch * a->dim * a->seqlen == 0) return VC1D_OK;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const bool cl = bwd_channel_last_ok(a);
+    cudaError_t err;
+    switch (a->kernel) {
+        case VC1D_KERNEL_GENERIC:
+            err = launch_prefill_bwd_generic(*a, s);
+            break;
+        case VC1D_KERNEL_TMA:
+            if (!cl || !tma_available()) return VC1D_E_STRIDE;
+            err = launch_prefill_bwd_tma(*a, s);
+            break;
+        default: {
+            const long long elems = (long long)a->batch * a->dim * a->seqlen;
+            err = cudaErrorNotSupported;
+            if (cl && a->seqlen >= 16 && elems >= (1LL << 18) && tma_available()) err = launch_prefill_bwd_tma(*a, s);
+            if (err == cudaErrorNotSupported) err = launch_prefill_bwd_generic(*a, s);
+            break;
+        }
+    }
+    return (int)err;
+}
+
+VC1D_API uint32_t vc1d_sizeof_prefill_bwd_args(void) { return (uint32_t)sizeof(vc1d_prefill_bwd_args); }
 
 VC1D_API int vc1d_update(const vc1d_update_args* a, void* stream) {
     using namespace vc1d;

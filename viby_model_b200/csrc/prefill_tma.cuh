@@ -652,6 +652,8 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeFn encode_fn();
+// address, on the current device, of the counter of expired bounded waits
+unsigned int* timeouts_ptr();
 
 template <int DT, int W, int SLAB_BYTES, int VB, int RPT, bool ACT>
 cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cudaStream_t s) {

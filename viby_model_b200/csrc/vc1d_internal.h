@@ -39,6 +39,11 @@ cudaError_t launch_prefill_time_major(const vc1d_prefill_args& a, cudaStream_t s
 // Any strides, every option.
 cudaError_t launch_prefill_generic(const vc1d_prefill_args& a, cudaStream_t s);
 
+// Backward of prefill.  Generic: any strides.  TMA-staged: x, dy, dx channel-last (channel stride
+// 1, 16-byte aligned rows), dim * elem_size a multiple of 16.
+cudaError_t launch_prefill_bwd_generic(const vc1d_prefill_bwd_args& a, cudaStream_t s);
+cudaError_t launch_prefill_bwd_tma(const vc1d_prefill_bwd_args& a, cudaStream_t s);
+
 // Vectorised decode: x/y channel stride 1, conv_state strides (.., state_len, 1),
 // dim % vec == 0, aligned, state_len in {1,2,3,4,8}, no cache_seqlens.
 cudaError_t launch_update_vec(const vc1d_update_args& a, cudaStream_t s);

@@ -149,7 +149,37 @@ def causal_conv1d_fn(
       dynamic_schedule: let the CTAs of the TMA-staged kernel claim tiles from per-slab counters in a
         small scratch buffer (one per device and stream, allocated on first use) instead of a fixed
         assignment; evens out ragged batches.
+
+    Differentiable in ``x``, ``weight``, ``bias`` and a separate ``residual`` tensor (the contract of
+    causal-conv1d-mps autograd.py:116-151, 305-338): when any of them requires grad the backward
+    pass runs ``causal_conv1d_bwd``.  ``initial_states`` and ``out=`` are forward-only.
     """
+    needs_grad = torch.is_grad_enabled() and (
+        x.requires_grad or weight.requires_grad or (bias is not None and bias.requires_grad)
+        or (isinstance(residual, torch.Tensor) and residual.requires_grad)
+    )
+    kw = dict(attention_mask=attention_mask, skip_masked_loads=skip_masked_loads, residual=residual,
+              state_len=state_len, out=out, kernel=kernel, rows_per_thread=rows_per_thread,
+              block_threads=block_threads, unroll=unroll, tma=tma, dynamic_schedule=dynamic_schedule)
+    if not needs_grad:
+        return _prefill_forward(x, weight, bias, seq_idx, initial_states, return_final_states, final_states_out,
+                                activation, **kw)
+    if out is not None:
+        raise ValueError("out= cannot be used when a gradient is required")
+    if initial_states is not None:
+        raise NotImplementedError("backward with initial_states is not supported")
+    res_tensor = residual if isinstance(residual, torch.Tensor) else None
+    result = _CausalConv1dFunction.apply(x, weight, bias, res_tensor, activation, attention_mask,
+                                         residual is True, return_final_states, final_states_out, kw)
+    return result if (return_final_states or final_states_out is not None) else result[0]
+
+
+def _prefill_forward(
+    x, weight, bias=None, seq_idx=None, initial_states=None, return_final_states=False, final_states_out=None,
+    activation=None, *, attention_mask=None, skip_masked_loads=True, residual=None, state_len=None, out=None,
+    kernel=None, rows_per_thread=0, block_threads=0, unroll=0, tma=None, dynamic_schedule=None,
+):
+    """The forward launch behind causal_conv1d_fn (no autograd bookkeeping)."""
     if x.dim() != 3:
         raise ValueError(f"Expected 3D input tensor (batch, dim, seqlen), got {x.dim()}D")
     batch, dim, seqlen = x.shape
@@ -264,6 +294,134 @@ def causal_conv1d_fn(
     if return_final_states or final_states_out is not None:
         return out, final_states
     return out
+
+
+def causal_conv1d_bwd(
+    x: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    dy: torch.Tensor,
+    activation: Optional[str] = None,
+    *,
+    attention_mask: Optional[torch.Tensor] = None,
+    residual: bool = False,
+    need_dweight: bool = True,
+    need_dbias: bool = True,
+    kernel: Optional[str] = None,
+    dynamic_schedule: Optional[bool] = None,
+) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """Gradients of ``causal_conv1d_fn`` (with its fused mask / residual) for ``x[batch, dim, seqlen]``
+    and the upstream gradient ``dy`` of the same shape: returns ``(dx, dweight, dbias)``.
+
+    ``dx`` has the dtype and strides of ``x``; ``dweight[dim, width]`` and ``dbias[dim]`` are summed in
+    fp32 and returned in fp32 (the caller casts), as the reference's backward does
+    (causal-conv1d-mps/causal_conv1d_mps/causal_conv1d_kernel.mm:553-557, 771-776).
+    ``residual=True`` means the forward added ``x`` to its output.  Formulas: include/vc1d.h.
+    """
+    if x.dim() != 3:
+        raise ValueError(f"Expected 3D input tensor (batch, dim, seqlen), got {x.dim()}D")
+    if dy.shape != x.shape or dy.dtype != x.dtype or dy.device != x.device:
+        raise ValueError("dy must match x in shape, dtype and device")
+    batch, dim, seqlen = x.shape
+    width = _check_weight_shapes(weight, bias, dim)
+    if x.dtype not in _IO_DTYPES:
+        raise ValueError(f"unsupported dtype {x.dtype}: expected float32, bfloat16 or float16")
+    act = _activation_code(activation)
+    _require_cuda(x, "Input")
+    weight, bias = _align_weights(x, weight, bias)
+    # a gradient with several zero strides (e.g. from sum().backward()) is not addressable as a tensor map
+    if any(st == 0 for st, n in zip(dy.stride(), dy.shape) if n > 1):
+        dy = dy.contiguous() if x.stride(2) == 1 else dy.transpose(1, 2).contiguous().transpose(1, 2)
+    dx = torch.empty_like(x)
+    if dx.stride() != x.stride():
+        dx = torch.empty_strided(x.shape, x.stride(), dtype=x.dtype, device=x.device)
+    dweight = torch.zeros(dim, width, dtype=torch.float32, device=x.device) if need_dweight else None
+    dbias = torch.zeros(dim, dtype=torch.float32, device=x.device) if (need_dbias and bias is not None) else None
+
+    a = _cabi.PrefillBwdArgs()
+    a.struct_size = C.sizeof(_cabi.PrefillBwdArgs)
+    a.dtype = _IO_DTYPES[x.dtype]
+    a.wdtype = _IO_DTYPES[weight.dtype]
+    a.activation = act
+    a.batch, a.dim, a.seqlen, a.width = batch, dim, seqlen, width
+    a.x, a.dy, a.dx = x.data_ptr(), dy.data_ptr(), dx.data_ptr()
+    a.weight = weight.data_ptr()
+    a.bias = bias.data_ptr() if bias is not None else None
+    a.x_stride_b, a.x_stride_d, a.x_stride_t = x.stride()
+    a.dy_stride_b, a.dy_stride_d, a.dy_stride_t = dy.stride()
+    a.dx_stride_b, a.dx_stride_d, a.dx_stride_t = dx.stride()
+    a.w_stride_d, a.w_stride_w = weight.stride()
+    if attention_mask is not None:
+        m = attention_mask
+        _require_cuda(m, "Attention mask")
+        if tuple(m.shape) != (batch, seqlen):
+            raise ValueError(
+                f"Attention mask shape {tuple(m.shape)} does not match input shape ({batch}, {seqlen})"
+            )
+        if m.dtype not in _MASK_DTYPES:
+            raise ValueError(f"unsupported attention mask dtype {m.dtype}")
+        a.mask = m.data_ptr()
+        a.mask_dtype = _MASK_DTYPES[m.dtype]
+        a.mask_stride_b, a.mask_stride_t = m.stride()
+    a.residual = 1 if residual else 0
+    a.dweight = dweight.data_ptr() if dweight is not None else None
+    a.dbias = dbias.data_ptr() if dbias is not None else None
+    if kernel not in (None, "auto", "generic", "tma"):
+        raise ValueError(f"unknown backward kernel {kernel!r}")
+    a.kernel = _cabi.KERNEL_BY_NAME[kernel]
+    stream = _stream_handle(x.device)
+    if dynamic_schedule or (dynamic_schedule is None and _DYNAMIC_DEFAULT):
+        sc = _scheduler_scratch(x.device, stream, 4096)
+        a.scratch = sc.data_ptr()
+        a.scratch_bytes = sc.numel() * sc.element_size()
+    if x.device.index != torch.cuda.current_device():
+        with torch.cuda.device(x.device):
+            st = _cabi.lib.vc1d_prefill_bwd(C.byref(a), stream)
+    else:
+        st = _cabi.lib.vc1d_prefill_bwd(C.byref(a), stream)
+    _cabi.check(st, "causal_conv1d_bwd")
+    return dx, dweight, dbias
+
+
+class _CausalConv1dFunction(torch.autograd.Function):
+    """Autograd glue of causal_conv1d_fn: forward launches the prefill kernel, backward launches
+    causal_conv1d_bwd (contract: causal-conv1d-mps/causal_conv1d_mps/autograd.py:116-151, 305-338)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, res_tensor, activation, attention_mask, residual_is_x, return_final_states,
+                final_states_out, kw):
+        kw = dict(kw)
+        kw["residual"] = True if residual_is_x else res_tensor
+        result = _prefill_forward(x, weight, bias, None, None, return_final_states, final_states_out, activation, **kw)
+        y, state = result if isinstance(result, tuple) else (result, None)
+        ctx.save_for_backward(x, weight, bias if bias is not None else x.new_empty(0),
+                              attention_mask if attention_mask is not None else x.new_empty(0))
+        ctx.has_bias = bias is not None
+        ctx.has_mask = attention_mask is not None
+        ctx.activation = activation
+        ctx.residual_is_x = residual_is_x
+        ctx.has_res_tensor = res_tensor is not None
+        if state is None:
+            state = x.new_empty(0)
+        ctx.mark_non_differentiable(state)
+        return y, state
+
+    @staticmethod
+    def backward(ctx, dy, _dstate):
+        x, weight, bias, mask = ctx.saved_tensors
+        need_x, need_w, need_b = ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[2]
+        dx, dw, db = causal_conv1d_bwd(
+            x, weight, bias if ctx.has_bias else None, dy, ctx.activation,
+            attention_mask=mask if ctx.has_mask else None, residual=ctx.residual_is_x,
+            need_dweight=need_w, need_dbias=need_b and ctx.has_bias,
+        )
+        return (
+            dx if need_x else None,
+            dw.to(weight.dtype) if (need_w and dw is not None) else None,
+            db.to(bias.dtype) if (need_b and db is not None) else None,
+            dy if (ctx.has_res_tensor and ctx.needs_input_grad[3]) else None,
+            None, None, None, None, None, None,
+        )
 
 
 def causal_conv1d_update(
