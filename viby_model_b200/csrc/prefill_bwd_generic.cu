@@ -40,15 +40,25 @@ struct BGParams {
     int n_chunks;
 };
 
-template <bool PRECISE>
+// MODE 0: expf and an IEEE division (fp32 I/O); 1: ex2.approx + rcp.approx (fp16 I/O);
+// 2: s = 0.5 + 0.5 * tanh.approx(z / 2) (bf16 I/O) -- the same three forms, operation for
+// operation, as the TMA-staged kernel, so that both kernels return the same bits.
+template <int MODE>
 __device__ __forceinline__ float silu_grad(float z) {
     // d/dz [z * s(z)] = s(z) * (1 + z * (1 - s(z)))
     float s;
-    if (PRECISE)
+    if (MODE == 0) {
         s = 1.0f / (1.0f + expf(-z));
-    else
+    } else if (MODE == 1) {
         s = rcp_approx(1.0f + ex2_approx(z * -1.4426950408889634f));
-    return s * (1.0f + z * (1.0f - s));
+    } else {
+        float th;
+        const float t = z * 0.5f;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(t));
+        s = fmaf(th, 0.5f, 0.5f);
+    }
+    const float u = fmaf(s, -1.0f, 1.0f);
+    return s * fmaf(z, u, 1.0f);
 }
 
 template <int DT>
@@ -108,7 +118,7 @@ __global__ void __launch_bounds__(128) k_prefill_bwd_generic(const BGParams p) {
                 if (p.act) {
                     float pre = bv;
                     for (int w = 0; w < W; ++w) pre = fmaf(wt[w], xw[4 - W + w], pre);
-                    g *= silu_grad<E::kPreciseSilu>(pre);
+                    g *= silu_grad<(DT == VC1D_F32) ? 0 : (DT == VC1D_F16 ? 1 : 2)>(pre);
                 }
             }
             gw[0] = gw[1]; gw[1] = gw[2]; gw[2] = gw[3];

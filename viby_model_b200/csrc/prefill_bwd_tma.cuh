@@ -68,17 +68,27 @@ struct BwdGeometry {
     __host__ __device__ static constexpr int smem_bytes(int S) { return off_flags(S) + S * 32 + 128; }
 };
 
-// silu'(z) = s * (1 + z * (1 - s)), s = sigmoid(z), for a pair of lanes
-template <bool PRECISE>
+// silu'(z) = s * (1 + z * (1 - s)), s = sigmoid(z), for a pair of lanes.
+// MODE 0: expf and an IEEE division (fp32 I/O).  MODE 1: ex2.approx + rcp.approx (fp16 I/O).
+// MODE 2: s = 0.5 + 0.5 * tanh.approx(z / 2), one special-function op per element instead of two;
+// its absolute error of 2.5e-4 in s (4e-4 in silu') is 1/20 of a bf16 step at 1, so bf16 I/O uses it.
+template <int MODE>
 __device__ __forceinline__ float2 silu_grad2(float2 z) {
     float2 s;
-    if (PRECISE) {
+    if constexpr (MODE == 0) {
         s = make_float2(1.0f / (1.0f + expf(-z.x)), 1.0f / (1.0f + expf(-z.y)));
-    } else {
+    } else if constexpr (MODE == 1) {
         const float2 t = mul2(z, make_float2(-1.4426950408889634f, -1.4426950408889634f));
         float2 e = make_float2(ex2_approx(t.x), ex2_approx(t.y));
         e = add2(e, make_float2(1.0f, 1.0f));
         s = make_float2(rcp_approx(e.x), rcp_approx(e.y));
+    } else {
+        const float2 half = make_float2(0.5f, 0.5f);
+        const float2 t = mul2(z, half);
+        float2 th;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(th.x) : "f"(t.x));
+        asm("tanh.approx.f32 %0, %1;" : "=f"(th.y) : "f"(t.y));
+        s = fma2(th, half, half);
     }
     const float2 one = make_float2(1.0f, 1.0f);
     const float2 u = fma2(s, make_float2(-1.0f, -1.0f), one);  // 1 - s
@@ -226,8 +236,10 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES>::kThreads, 2)
     }
     float2 dwp[W][NP];
     float2 dbp[NP];
+    float2 sgb[NP];  // silu'(bias): the factor of g in rows whose inputs are all masked out
 #pragma unroll
     for (int q = 0; q < NP; ++q) {
+        sgb[q] = ACT ? silu_grad2<(DT == VC1D_F32) ? 0 : (DT == VC1D_F16 ? 1 : 2)>(bp[q]) : make_float2(1.0f, 1.0f);
         dbp[q] = make_float2(0.f, 0.f);
 #pragma unroll
         for (int w = 0; w < W; ++w) dwp[w][q] = make_float2(0.f, 0.f);
@@ -274,77 +286,105 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES>::kThreads, 2)
             mp.T = p.T;
             if (mj < R + 2 * H) mkv = tile_mask(mp, (long long)b * p.smb, tfirst - H + mj);
         }
-        float2 xw[W][NP];  // masked inputs: row n lives in slot n % W
-        float2 gw[W][NP];  // g: row jj lives in slot jj % W
-#pragma unroll
-        for (int n = 0; n < H; ++n) {
-            uint32_t raw[NW];
-            S::lds(xrow + n * G::kRowBytes, raw);
-            S::unpack(raw, xw[n % W]);
-            if (masked) apply_mask<DT, VB>(xw[n % W], __shfl_sync(0xffffffffu, mkv, msrc + n), 1);
-        }
-        static_for<0, R + H>([&](auto jc) {
-            constexpr int jj = decltype(jc)::value;
-            constexpr int n = H + jj;  // x box row of this step
-            {
+        // rows of this warp whose mask values are all one take the code without mask arithmetic
+        const bool warp_masked = masked && !__all_sync(0xffffffffu, mkv == 1.0f);
+        auto rows = [&](auto mk_c) {
+            constexpr bool MK = decltype(mk_c)::value;
+            float2 xw[W][NP];  // masked inputs: row n lives in slot n % W
+            float2 gw[W][NP];  // g: row jj lives in slot jj % W
+    #pragma unroll
+            for (int n = 0; n < H; ++n) {
                 uint32_t raw[NW];
                 S::lds(xrow + n * G::kRowBytes, raw);
                 S::unpack(raw, xw[n % W]);
-                if (masked) apply_mask<DT, VB>(xw[n % W], __shfl_sync(0xffffffffu, mkv, msrc + n), 1);
+                if constexpr (MK) apply_mask<DT, VB>(xw[n % W], __shfl_sync(0xffffffffu, mkv, msrc + n), 1);
             }
-            float2 g[NP];
-            {
-                uint32_t raw[NW];
-                S::lds(grow + jj * G::kRowBytes, raw);
-                S::unpack(raw, g);
-            }
-            if constexpr (ACT) {
-#pragma unroll
-                for (int q = 0; q < NP; ++q) {
-                    float2 pre = bp[q];
-#pragma unroll
-                    for (int w = 0; w < W; ++w) pre = fma2(wp[w][q], xw[(n + 1 + w) % W][q], pre);
-                    g[q] = mul2(g[q], silu_grad2<E::kPreciseSilu>(pre));
-                }
-            }
-#pragma unroll
-            for (int q = 0; q < NP; ++q) gw[jj % W][q] = g[q];
-            if constexpr (jj < R) {
-                // rows of this thread's own share of the tile: parameter gradients
-#pragma unroll
-                for (int q = 0; q < NP; ++q) {
-#pragma unroll
-                    for (int w = 0; w < W; ++w) dwp[w][q] = fma2(xw[(n + 1 + w) % W][q], g[q], dwp[w][q]);
-                    dbp[q] = add2(dbp[q], g[q]);
-                }
-            }
-            if constexpr (jj >= H) {
-                constexpr int k = jj - H;  // output row: dx[t] = sum_w weight[w] * g[t + (W-1-w)], t + H = jj
-                float2 acc[NP];
-#pragma unroll
-                for (int q = 0; q < NP; ++q) {
-                    acc[q] = mul2(wp[0][q], gw[jj % W][q]);
-#pragma unroll
-                    for (int w = 1; w < W; ++w) acc[q] = fma2(wp[w][q], gw[(jj - w + W) % W][q], acc[q]);
-                }
-                if (masked) {
-                    const float mk = __shfl_sync(0xffffffffu, mkv, msrc + H + k);
-#pragma unroll
-                    for (int q = 0; q < NP; ++q) acc[q] = mul2(acc[q], make_float2(mk, mk));
-                }
-                if (p.residual) {
+            static_for<0, R + H>([&](auto jc) {
+                constexpr int jj = decltype(jc)::value;
+                constexpr int n = H + jj;  // x box row of this step
+                {
                     uint32_t raw[NW];
-                    float2 dyk[NP];
-                    S::lds(grow + k * G::kRowBytes, raw);
-                    S::unpack(raw, dyk);
-#pragma unroll
-                    for (int q = 0; q < NP; ++q) acc[q] = add2(acc[q], dyk[q]);
+                    S::lds(xrow + n * G::kRowBytes, raw);
+                    S::unpack(raw, xw[n % W]);
+                    if constexpr (MK) apply_mask<DT, VB>(xw[n % W], __shfl_sync(0xffffffffu, mkv, msrc + n), 1);
                 }
-                uint32_t outw[NW];
-                S::pack(acc, outw);
-                S::template stg_row<k>(row_addr<k>(dxrow, pitch), outw, rows_ok);
-            }
-        });
+                float2 g[NP];
+                {
+                    uint32_t raw[NW];
+                    S::lds(grow + jj * G::kRowBytes, raw);
+                    S::unpack(raw, g);
+                }
+                if constexpr (ACT) {
+    #pragma unroll
+                    for (int q = 0; q < NP; ++q) {
+                        float2 pre = bp[q];
+    #pragma unroll
+                        for (int w = 0; w < W; ++w) pre = fma2(wp[w][q], xw[(n + 1 + w) % W][q], pre);
+                        g[q] = mul2(g[q], silu_grad2<(DT == VC1D_F32) ? 0 : (DT == VC1D_F16 ? 1 : 2)>(pre));
+                    }
+                }
+    #pragma unroll
+                for (int q = 0; q < NP; ++q) gw[jj % W][q] = g[q];
+                if constexpr (jj < R) {
+                    // rows of this thread's own share of the tile: parameter gradients
+    #pragma unroll
+                    for (int q = 0; q < NP; ++q) {
+    #pragma unroll
+                        for (int w = 0; w < W; ++w) dwp[w][q] = fma2(xw[(n + 1 + w) % W][q], g[q], dwp[w][q]);
+                        dbp[q] = add2(dbp[q], g[q]);
+                    }
+                }
+                if constexpr (jj >= H) {
+                    constexpr int k = jj - H;  // output row: dx[t] = sum_w weight[w] * g[t + (W-1-w)], t + H = jj
+                    float2 acc[NP];
+    #pragma unroll
+                    for (int q = 0; q < NP; ++q) {
+                        acc[q] = mul2(wp[0][q], gw[jj % W][q]);
+    #pragma unroll
+                        for (int w = 1; w < W; ++w) acc[q] = fma2(wp[w][q], gw[(jj - w + W) % W][q], acc[q]);
+                    }
+                    if constexpr (MK) {
+                        const float mk = __shfl_sync(0xffffffffu, mkv, msrc + H + k);
+    #pragma unroll
+                        for (int q = 0; q < NP; ++q) acc[q] = mul2(acc[q], make_float2(mk, mk));
+                    }
+                    if (p.residual) {
+                        uint32_t raw[NW];
+                        float2 dyk[NP];
+                        S::lds(grow + k * G::kRowBytes, raw);
+                        S::unpack(raw, dyk);
+    #pragma unroll
+                        for (int q = 0; q < NP; ++q) acc[q] = add2(acc[q], dyk[q]);
+                    }
+                    uint32_t outw[NW];
+                    S::pack(acc, outw);
+                    S::template stg_row<k>(row_addr<k>(dxrow, pitch), outw, rows_ok);
+                }
+            });
+        };
+        // rows whose inputs are all masked out: pre = bias, so g = dy * silu'(bias); no gradient reaches
+        // the weights or, residual aside, the inputs
+        const bool warp_zero = masked && __all_sync(0xffffffffu, mj >= R + 2 * H || mkv == 0.0f);
+        if (warp_zero) {
+            static_for<0, R>([&](auto kc) {
+                constexpr int k = decltype(kc)::value;
+                uint32_t raw[NW];
+                float2 g[NP];
+                S::lds(grow + k * G::kRowBytes, raw);
+                S::unpack(raw, g);
+                if (!p.residual) {
+#pragma unroll
+                    for (int i = 0; i < NW; ++i) raw[i] = 0u;
+                }
+                S::template stg_row<k>(row_addr<k>(dxrow, pitch), raw, rows_ok);  // dx = dy (residual) or +0
+#pragma unroll
+                for (int q = 0; q < NP; ++q) dbp[q] = fma2(g[q], sgb[q], dbp[q]);
+            });
+        } else if (warp_masked) {
+            rows(std::true_type{});
+        } else {
+            rows(std::false_type{});
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(bars + 8 * (kStages + s));
     }
