@@ -57,7 +57,7 @@ def check(x, dy, w, b, act, m, residual, kernel):
     before = V.launch_count()
     dx, dw, db = V.causal_conv1d_bwd(dev(x), dev(w), dev(b), dev(dy), act, attention_mask=dev(m), residual=residual,
                                      kernel=kernel)
-    assert V.launch_count() == before + 1
+    assert V.launch_count() - before in (1, 2)  # two with the tile-classification pre-pass of masked launches
     if kernel is not None:
         assert V.last_kernel() == "bwd_" + kernel
     rdx, rdw, rdb = O.causal_conv1d_bwd_ref(x, w, b, dy, act, attention_mask=m, residual=residual)

@@ -32,6 +32,7 @@ struct BwdParams {
     float* dweight;
     float* dbias;
     unsigned int* sched;     // per-slab claim counters in scratch memory (NULL: static assignment)
+    const unsigned char* gtable;  // class byte per (sequence, time tile) from the pre-pass, or NULL
     unsigned int* timeouts;
     long long sdb, sdt;      // dx strides in bytes
     long long smb, smt;      // mask strides in elements
@@ -178,19 +179,21 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES>::kThreads, 2)
         while (live && rt >= 0) {
             const int b = rt / p.n_ttile;
             const int t0 = (rt - b * p.n_ttile) * G::kTileRows;
+            // a tile whose x rows are all masked out needs no x: only its dy box is copied
+            const bool need_x = p.gtable == nullptr || __ldg(p.gtable + rt) != TILE_EMPTY;
             rt = next_tile();  // fetched while this tile waits for its slot
             live = claim();
             if (!live) break;
             const int s = s_ring;
             if (lane == 0) {
                 const long long off = (long long)b * p.sdb + (long long)t0 * p.sdt;
-                sts_desc(flags + 32 * s, TILE_FULL, p.T - t0, off);
+                sts_desc(flags + 32 * s, need_x ? TILE_FULL : TILE_EMPTY, p.T - t0, off);
                 sts_s32(flags + 32 * s + 16, b);
                 sts_s32(flags + 32 * s + 20, t0);
                 const uint32_t full = bars + 8 * s;
                 const uint32_t dst = base + s * G::kStageBytes;
-                mbar_arrive_expect_tx(full, G::kXBytes + G::kGBytes);
-                tma_load_3d(dst, &tmap_x, slab_ch0, t0 - H, b, full);
+                mbar_arrive_expect_tx(full, (need_x ? G::kXBytes : 0) + G::kGBytes);
+                if (need_x) tma_load_3d(dst, &tmap_x, slab_ch0, t0 - H, b, full);
                 tma_load_3d(dst + G::kXBytes, &tmap_g, slab_ch0, t0, b, full);
             }
             __syncwarp();
@@ -364,7 +367,8 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES>::kThreads, 2)
         };
         // rows whose inputs are all masked out: pre = bias, so g = dy * silu'(bias); no gradient reaches
         // the weights or, residual aside, the inputs
-        const bool warp_zero = masked && __all_sync(0xffffffffu, mj >= R + 2 * H || mkv == 0.0f);
+        // (a tile the producer classed as empty arrives without its x box: it must take this path)
+        const bool warp_zero = cls == TILE_EMPTY || (masked && __all_sync(0xffffffffu, mj >= R + 2 * H || mkv == 0.0f));
         if (warp_zero) {
             static_for<0, R>([&](auto kc) {
                 constexpr int k = decltype(kc)::value;
@@ -485,9 +489,32 @@ cudaError_t launch_bwd_kernel(const vc1d_prefill_bwd_args& a, const BwdParams& b
         }
     }
     p.sched = nullptr;
+    p.gtable = nullptr;
     if (a.scratch != nullptr && 4LL * (n_slab + 1) <= kSchedCounterBytes && a.scratch_bytes >= kSchedCounterBytes &&
-        (reinterpret_cast<uintptr_t>(a.scratch) & 15u) == 0)
+        (reinterpret_cast<uintptr_t>(a.scratch) & 15u) == 0) {
         p.sched = reinterpret_cast<unsigned int*>(a.scratch);
+        if (a.mask != nullptr && a.scratch_bytes >= kSchedCounterBytes + n_rowtiles) {
+            // class of every tile from its R + 2H mask rows (pre-pass shared with the forward kernel)
+            TmaParams cp;
+            cp.mask = a.mask;
+            cp.smb = a.mask_stride_b;
+            cp.smt = a.mask_stride_t;
+            cp.mask_dtype = a.mask_dtype;
+            cp.B = a.batch;
+            cp.T = a.seqlen;
+            cp.n_ttile = p.n_ttile;
+            cp.skip = 1;
+            cp.res = nullptr;
+            unsigned char* tab = reinterpret_cast<unsigned char*>(a.scratch) + kSchedCounterBytes;
+            const long long threads = n_rowtiles * 32;
+            k_classify_tiles<<<(unsigned)((threads + 255) / 256), 256, 0, s>>>(cp, tab, (int)G::kTileRows, (int)G::kH,
+                                                                             (int)G::kXRows);
+            const cudaError_t e = cudaGetLastError();
+            if (e != cudaSuccess) return e;
+            note_launch("classify");
+            p.gtable = tab;
+        }
+    }
     const dim3 grid((unsigned)n_slab, (unsigned)g);
     note_launch("bwd_tma");
     k_prefill_bwd_tma<DT, W, SLAB_BYTES, ACT><<<grid, G::kThreads, smem, s>>>(tmap_x, tmap_g, p);

@@ -325,11 +325,13 @@ __device__ __forceinline__ int classify_tile(const TmaParams& p, int b, int t0, 
 }
 
 // Pre-pass of masked launches that schedule dynamically: the class of every (sequence, time tile),
-// one byte each, into scratch memory.  The mask is the same for every channel slab.
+// one byte each, into scratch memory.  The mask is the same for every channel slab.  A tile's class
+// looks at box_rows mask rows starting H rows above the tile.
 constexpr int kSchedCounterBytes = 4096;
 constexpr int kSmemTableCap = 16384;  // largest pre-pass class table a CTA copies into shared memory
 
-static __global__ void __launch_bounds__(256) k_classify_tiles(const TmaParams p, unsigned char* table, int tile_rows, int H) {
+static __global__ void __launch_bounds__(256) k_classify_tiles(const TmaParams p, unsigned char* table, int tile_rows, int H,
+                                                               int box_rows) {
     griddep_wait();  // the table may still be read by the previous launch on this stream
     griddep_launch_dependents();
     const int lane = threadIdx.x & 31;
@@ -337,7 +339,7 @@ static __global__ void __launch_bounds__(256) k_classify_tiles(const TmaParams p
     if (tile >= (long long)p.B * p.n_ttile) return;
     const int b = (int)(tile / p.n_ttile);
     const int tt = (int)(tile - (long long)b * p.n_ttile);
-    const int cls = classify_tile(p, b, tt * tile_rows, H, tile_rows + H, lane);
+    const int cls = classify_tile(p, b, tt * tile_rows, H, box_rows, lane);
     if (lane == 0) table[tile] = (unsigned char)cls;
 }
 
@@ -762,7 +764,7 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
         cfg.gridDim = dim3((unsigned)((threads + 255) / 256));
         cfg.blockDim = dim3(256);
         cfg.dynamicSmemBytes = 0;
-        const cudaError_t e = cudaLaunchKernelEx(&cfg, k_classify_tiles, p, tab, (int)G::kTileRows, (int)G::kH);
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, k_classify_tiles, p, tab, (int)G::kTileRows, (int)G::kH, (int)G::kBoxRows);
         if (e != cudaSuccess) return e;
         note_launch("classify");
         p.gtable = tab;

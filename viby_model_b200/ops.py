@@ -371,7 +371,7 @@ def causal_conv1d_bwd(
     a.kernel = _cabi.KERNEL_BY_NAME[kernel]
     stream = _stream_handle(x.device)
     if dynamic_schedule or (dynamic_schedule is None and _DYNAMIC_DEFAULT):
-        sc = _scheduler_scratch(x.device, stream, 4096)
+        sc = _scheduler_scratch(x.device, stream, 4096 + batch * ((seqlen + 31) // 32))
         a.scratch = sc.data_ptr()
         a.scratch_bytes = sc.numel() * sc.element_size()
     if x.device.index != torch.cuda.current_device():
