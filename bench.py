@@ -233,6 +233,7 @@ def main():
     ap.add_argument("--kernel", default=None, help="force a prefill kernel (channel_last | tma)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-backward", action="store_true")
     ap.add_argument("--decode-saturating-only", action="store_true",
                     help="run only the bandwidth-bound decode shape and print its figures (for profiling)")
     args = ap.parse_args()
@@ -343,6 +344,12 @@ def main():
         barrier()
         e2e_ms_total = max_over_ranks(f0.elapsed_time(f1))
 
+        # ---- backward of the same workload (training step of the Canon-D layer) ------------------
+        backward = None
+        if not args.no_backward:
+            backward = bench_backward(V, cfg, xv, w, b, m, valid_tokens, padded_tokens, world, barrier,
+                                      max_over_ranks)
+
         # ---- decode ---------------------------------------------------------------------------
         decode = None
         if not args.no_decode:
@@ -409,6 +416,8 @@ def main():
         "roofline": roofline,
         "clocks": clocks,
     }
+    if backward is not None:
+        line["backward"] = backward
     if decode is not None:
         line["decode"] = decode
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -428,6 +437,39 @@ def main():
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def bench_backward(V, cfg, xv, w, b, m, valid_tokens, padded_tokens, world, barrier, max_over_ranks):
+    """Gradients (dx, dweight, dbias) of the bench workload: one causal_conv1d_bwd launch per step,
+    device-resident.  Algorithmic bytes: x read where valid + dy read + dx written."""
+    g = torch.Generator(device=xv.device).manual_seed(11)
+    dy = torch.randn(xv.shape[0], xv.shape[2], xv.shape[1], generator=g, device=xv.device).to(cfg.dtype).transpose(1, 2)
+    def step():
+        return V.causal_conv1d_bwd(xv, w, b, dy, cfg.activation, attention_mask=m)
+    for _ in range(5):
+        step()
+    barrier()
+    n = 50
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        step()
+    e1.record()
+    barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1)) / n
+    elem = 2
+    nbytes = (valid_tokens + 2 * padded_tokens) * cfg.dim * elem
+    peak, _ = measured_peak_gbs()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    return {
+        "kernel": V.last_kernel(),
+        "ms_per_step": ms,
+        "tokens_per_s": world * padded_tokens / (ms * 1e-3),
+        "algorithmic_bytes_per_launch": nbytes,
+        "achieved_gbs": gbs,
+        "frac_of_measured_peak": gbs / peak,
+        "note": "includes the zeroing of the fp32 dweight/dbias accumulators and the tile-classification pre-pass",
+    }
 
 
 def bench_decode(V, WL, dev, rank, world, barrier, max_over_ranks):

@@ -180,14 +180,17 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES>::kThreads, 2)
             const int b = rt / p.n_ttile;
             const int t0 = (rt - b * p.n_ttile) * G::kTileRows;
             // a tile whose x rows are all masked out needs no x: only its dy box is copied
-            const bool need_x = p.gtable == nullptr || __ldg(p.gtable + rt) != TILE_EMPTY;
+            // class from the pre-pass: all mask rows one, mixed, or every x row masked out (no x box)
+            const int cls_now = p.gtable != nullptr ? (int)__ldg(p.gtable + rt)
+                                                    : (p.mask != nullptr ? (int)TILE_MIXED : (int)TILE_FULL);
+            const bool need_x = cls_now != TILE_EMPTY;
             rt = next_tile();  // fetched while this tile waits for its slot
             live = claim();
             if (!live) break;
             const int s = s_ring;
             if (lane == 0) {
                 const long long off = (long long)b * p.sdb + (long long)t0 * p.sdt;
-                sts_desc(flags + 32 * s, need_x ? TILE_FULL : TILE_EMPTY, p.T - t0, off);
+                sts_desc(flags + 32 * s, cls_now, p.T - t0, off);
                 sts_s32(flags + 32 * s + 16, b);
                 sts_s32(flags + 32 * s + 20, t0);
                 const uint32_t full = bars + 8 * s;
@@ -279,7 +282,7 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES>::kThreads, 2)
         const uint32_t grow = xrow + G::kXBytes;  // this thread's first dy row
         // x box row n of this thread is time tfirst - H + n (n = 0 .. R+2H-1); dy box row n is tfirst + n
         float mkv = 1.0f;
-        if (masked) {
+        if (cls == TILE_MIXED) {  // only mixed tiles look at their mask rows
             const int b = lds_s32(flags + 32 * s + 16);
             const int tfirst = lds_s32(flags + 32 * s + 20) + rbase;
             TmaParams mp;
@@ -290,7 +293,7 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES>::kThreads, 2)
             if (mj < R + 2 * H) mkv = tile_mask(mp, (long long)b * p.smb, tfirst - H + mj);
         }
         // rows of this warp whose mask values are all one take the code without mask arithmetic
-        const bool warp_masked = masked && !__all_sync(0xffffffffu, mkv == 1.0f);
+        const bool warp_masked = cls == TILE_MIXED && !__all_sync(0xffffffffu, mkv == 1.0f);
         auto rows = [&](auto mk_c) {
             constexpr bool MK = decltype(mk_c)::value;
             float2 xw[W][NP];  // masked inputs: row n lives in slot n % W
@@ -368,7 +371,7 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES>::kThreads, 2)
         // rows whose inputs are all masked out: pre = bias, so g = dy * silu'(bias); no gradient reaches
         // the weights or, residual aside, the inputs
         // (a tile the producer classed as empty arrives without its x box: it must take this path)
-        const bool warp_zero = cls == TILE_EMPTY || (masked && __all_sync(0xffffffffu, mj >= R + 2 * H || mkv == 0.0f));
+        const bool warp_zero = cls == TILE_EMPTY || (cls == TILE_MIXED && __all_sync(0xffffffffu, mj >= R + 2 * H || mkv == 0.0f));
         if (warp_zero) {
             static_for<0, R>([&](auto kc) {
                 constexpr int k = decltype(kc)::value;
@@ -471,7 +474,12 @@ cudaError_t launch_bwd_kernel(const vc1d_prefill_bwd_args& a, const BwdParams& b
     if (stages > kMaxStages) stages = kMaxStages;
     const int per_sm = (a.tma_ctas_per_sm > 0 && a.tma_ctas_per_sm <= 8) ? a.tma_ctas_per_sm : 2;
     p.stages = stages;
-    long long g = ((long long)sm_count() * per_sm) / n_slab;
+    const bool use_sched = a.scratch != nullptr && 4LL * (n_slab + 1) <= kSchedCounterBytes &&
+                           a.scratch_bytes >= kSchedCounterBytes && (reinterpret_cast<uintptr_t>(a.scratch) & 15u) == 0;
+    // CTAs per slab: with dynamic claims round up, so that no resident slot stays empty (a CTA that
+    // starts late simply claims what is left); with static assignment round down
+    const long long slots = (long long)sm_count() * per_sm;
+    long long g = use_sched ? (slots + n_slab - 1) / n_slab : slots / n_slab;
     if (g < 1) g = 1;
     if (g > n_rowtiles) g = n_rowtiles;
     if (g > 65535) g = 65535;
@@ -490,8 +498,7 @@ cudaError_t launch_bwd_kernel(const vc1d_prefill_bwd_args& a, const BwdParams& b
     }
     p.sched = nullptr;
     p.gtable = nullptr;
-    if (a.scratch != nullptr && 4LL * (n_slab + 1) <= kSchedCounterBytes && a.scratch_bytes >= kSchedCounterBytes &&
-        (reinterpret_cast<uintptr_t>(a.scratch) & 15u) == 0) {
+    if (use_sched) {
         p.sched = reinterpret_cast<unsigned int*>(a.scratch);
         if (a.mask != nullptr && a.scratch_bytes >= kSchedCounterBytes + n_rowtiles) {
             // class of every tile from its R + 2H mask rows (pre-pass shared with the forward kernel)
