@@ -235,6 +235,43 @@ typedef struct vc1d_update_args {
 
 VC1D_API int vc1d_update(const vc1d_update_args* args, void* stream);
 
+/*
+ * Backward of one decode step (causal_conv1d_update), for the state the step STARTED from:
+ *     win = last W entries of [conv_state | x] (or the circular history);  pre = bias + win . weight
+ *     g = dy * silu'(pre);   dx = weight[W-1] * g (+ dy with residual);   dstate[col of tap w] = weight[w] * g
+ *     dweight[d,w] += sum_b win[w] * g;   dbias[d] += sum_b g
+ * Replaces short_conv_update_bwd of causal-conv1d-mps (causal_conv1d.metal:1738-1845, host side
+ * causal_conv1d_kernel.mm:781-888, Python contract autograd.py:455-482).  dstate columns that no tap
+ * reads are set to zero.  dweight / dbias: fp32, accumulated, caller-zeroed, as in vc1d_prefill_bwd.
+ */
+typedef struct vc1d_update_bwd_args {
+    uint32_t struct_size;
+    int32_t dtype;          /* x, conv_state, dy, dx, dstate */
+    int32_t wdtype;
+    int32_t activation;
+    int32_t batch, dim, width, state_len;
+    const void* x;          /* [batch, dim] */
+    const void* conv_state; /* [batch, dim, state_len]: the state before the step */
+    const void* dy;         /* [batch, dim] */
+    void* dx;               /* [batch, dim] */
+    void* dstate;           /* [batch, dim, state_len] contiguous, or NULL */
+    const void* weight;
+    const void* bias;
+    int64_t x_stride_b, x_stride_d;
+    int64_t dy_stride_b, dy_stride_d;
+    int64_t dx_stride_b, dx_stride_d;
+    int64_t s_stride_b, s_stride_d, s_stride_l;
+    int64_t w_stride_d, w_stride_w;
+    const int32_t* cache_seqlens; /* [batch] or NULL: circular state as in vc1d_update */
+    int32_t residual;
+    int32_t reserved;
+    float* dweight;         /* [dim, width] fp32, accumulated; NULL = not wanted */
+    float* dbias;           /* [dim] fp32, accumulated; NULL = not wanted */
+} vc1d_update_bwd_args;
+
+VC1D_API int vc1d_update_bwd(const vc1d_update_bwd_args* args, void* stream);
+VC1D_API uint32_t vc1d_sizeof_update_bwd_args(void);
+
 /* ABI version of the loaded library (VC1D_ABI_VERSION it was built with). */
 VC1D_API int vc1d_abi_version(void);
 

@@ -218,3 +218,73 @@ def test_backward_bench_shape_properties():
     assert err < 0.05
     torch.cuda.synchronize()
     assert V.tma_timeouts() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("L", [3, 4, 8])
+@pytest.mark.parametrize("act", [None, "silu"])
+@pytest.mark.parametrize("W", [2, 4])
+def test_update_backward_matches_oracle(dtype, L, act, W):
+    g = torch.Generator().manual_seed(L * 10 + W)
+    B, D = 37, 200
+    x = torch.randn(B, D, generator=g).to(dtype)
+    st = torch.randn(B, D, L, generator=g).to(dtype)
+    dy = torch.randn(B, D, generator=g).to(dtype)
+    w = (torch.rand(D, W, generator=g) - 0.5).to(dtype)
+    b = (torch.rand(D, generator=g) - 0.5).to(dtype)
+    dev = lambda t: t.to(DEV)  # noqa: E731
+    for residual in (False, True):
+        dx, dst, dw, db = V.causal_conv1d_update_bwd(dev(x), dev(st), dev(w), dev(b), dev(dy), act, residual=residual)
+        assert V.last_kernel() == "update_bwd"
+        rdx, rdst, rdw, rdb = O.causal_conv1d_update_bwd_ref(x, st, w, b, dy, act, residual=residual)
+        tol = dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=2e-2, atol=2e-2)
+        assert torch.allclose(dx.cpu().float(), rdx.float(), **tol)
+        assert torch.allclose(dst.cpu().float(), rdst.float(), **tol)
+        assert torch.allclose(dw.cpu().double(), rdw, rtol=1e-3, atol=1e-3)
+        assert torch.allclose(db.cpu().double(), rdb, rtol=1e-3, atol=1e-3)
+
+
+def test_update_autograd_matches_finite_differences():
+    """The reference's own test design for the decode step (causal-conv1d-mps/test.py:296-321):
+    circular state with cache_seqlens, activation and residual on."""
+    g = torch.Generator().manual_seed(2)
+    B, D, W, L = 2, 8, 4, 8
+    x = torch.randn(B, D, generator=g).to(DEV).requires_grad_(True)
+    st = torch.randn(B, D, L, generator=g).to(DEV).requires_grad_(True)
+    w = torch.randn(D, W, generator=g).to(DEV).requires_grad_(True)
+    b = torch.randn(D, generator=g).to(DEV).requires_grad_(True)
+    seqlens = torch.tensor([5, 11], dtype=torch.int32, device=DEV)
+    coef = torch.randn(B, D, generator=g).to(DEV)
+
+    def f():
+        return V.short_conv_update(x, st.clone(), w, b, seqlens, activation=True, residual=True) * coef
+
+    f().sum().backward()
+    analytical = [x.grad.clone(), st.grad.clone(), w.grad.clone(), b.grad.clone()]
+    with torch.no_grad():
+        numerical = numerical_grads(f, [x, st, w, b])
+    for a, n in zip(analytical, numerical):
+        assert torch.allclose(a, n, atol=2e-2, rtol=2e-2), (a - n).abs().max().item()
+
+
+def test_gradient_flows_through_two_decode_steps():
+    """Back-propagation through time over two steps: the second step reads what the first wrote."""
+    g = torch.Generator().manual_seed(8)
+    B, D, W, L = 2, 6, 4, 4
+    x1 = torch.randn(B, D, generator=g).to(DEV).requires_grad_(True)
+    x2 = torch.randn(B, D, generator=g).to(DEV).requires_grad_(True)
+    st0 = torch.randn(B, D, L, generator=g).to(DEV).requires_grad_(True)
+    w = torch.randn(D, W, generator=g).to(DEV).requires_grad_(True)
+
+    def f():
+        st = st0.clone()
+        y1 = V.causal_conv1d_update(x1, st, w, None, activation="silu")
+        y2 = V.causal_conv1d_update(x2, st, w, None, activation="silu")
+        return y1 * 0.5 + y2
+
+    f().sum().backward()
+    analytical = [x1.grad.clone(), x2.grad.clone(), st0.grad.clone(), w.grad.clone()]
+    with torch.no_grad():
+        numerical = numerical_grads(f, [x1, x2, st0, w])
+    for a, n in zip(analytical, numerical):
+        assert torch.allclose(a, n, atol=2e-2, rtol=2e-2), (a - n).abs().max().item()

@@ -3,7 +3,7 @@
 Public surface:
   causal_conv1d_fn, causal_conv1d_update  -- the CUDA slot of the reference's CanonLayer
                                              (model/model.py:20-30, 305-311, 460-466)
-  causal_conv1d_bwd                       -- their backward pass (causal_conv1d_fn is differentiable;
+  causal_conv1d_bwd, causal_conv1d_update_bwd  -- their backward passes (causal_conv1d_fn is differentiable;
                                              contract: causal_conv1d_mps/autograd.py:116-151, 305-338)
   causal_conv1d_fwd, short_conv_fused,
   short_conv_update                       -- the [B,T,D] operators of causal-conv1d-mps
@@ -15,13 +15,14 @@ The operators call hand-written CUDA kernels through the C ABI of include/vc1d.h
 that library raises ImportError: there is no CPU or PyTorch fallback.
 """
 from ._cabi import last_kernel, launch_count, library_path, tma_timeouts
-from .ops import causal_conv1d_bwd, causal_conv1d_fn, causal_conv1d_update
+from .ops import causal_conv1d_bwd, causal_conv1d_fn, causal_conv1d_update, causal_conv1d_update_bwd
 from .short_conv import causal_conv1d_fwd, short_conv_fused, short_conv_update
 
 __all__ = [
     "causal_conv1d_fn",
     "causal_conv1d_update",
     "causal_conv1d_bwd",
+    "causal_conv1d_update_bwd",
     "causal_conv1d_fwd",
     "short_conv_fused",
     "short_conv_update",

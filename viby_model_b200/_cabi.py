@@ -160,6 +160,44 @@ class UpdateArgs(C.Structure):
     ]
 
 
+class UpdateBwdArgs(C.Structure):
+    """struct vc1d_update_bwd_args"""
+
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("dtype", C.c_int32),
+        ("wdtype", C.c_int32),
+        ("activation", C.c_int32),
+        ("batch", C.c_int32),
+        ("dim", C.c_int32),
+        ("width", C.c_int32),
+        ("state_len", C.c_int32),
+        ("x", C.c_void_p),
+        ("conv_state", C.c_void_p),
+        ("dy", C.c_void_p),
+        ("dx", C.c_void_p),
+        ("dstate", C.c_void_p),
+        ("weight", C.c_void_p),
+        ("bias", C.c_void_p),
+        ("x_stride_b", C.c_int64),
+        ("x_stride_d", C.c_int64),
+        ("dy_stride_b", C.c_int64),
+        ("dy_stride_d", C.c_int64),
+        ("dx_stride_b", C.c_int64),
+        ("dx_stride_d", C.c_int64),
+        ("s_stride_b", C.c_int64),
+        ("s_stride_d", C.c_int64),
+        ("s_stride_l", C.c_int64),
+        ("w_stride_d", C.c_int64),
+        ("w_stride_w", C.c_int64),
+        ("cache_seqlens", C.c_void_p),
+        ("residual", C.c_int32),
+        ("reserved", C.c_int32),
+        ("dweight", C.c_void_p),
+        ("dbias", C.c_void_p),
+    ]
+
+
 # every symbol include/vc1d.h declares: name -> (restype, argtypes)
 EXPORTS = {
     "vc1d_prefill": (C.c_int, [C.POINTER(PrefillArgs), C.c_void_p]),
@@ -167,6 +205,8 @@ EXPORTS = {
     "vc1d_prefill_bwd": (C.c_int, [C.POINTER(PrefillBwdArgs), C.c_void_p]),
     "vc1d_sizeof_prefill_bwd_args": (C.c_uint32, []),
     "vc1d_update": (C.c_int, [C.POINTER(UpdateArgs), C.c_void_p]),
+    "vc1d_update_bwd": (C.c_int, [C.POINTER(UpdateBwdArgs), C.c_void_p]),
+    "vc1d_sizeof_update_bwd_args": (C.c_uint32, []),
     "vc1d_abi_version": (C.c_int, []),
     "vc1d_sizeof_prefill_args": (C.c_uint32, []),
     "vc1d_sizeof_update_args": (C.c_uint32, []),
@@ -206,6 +246,7 @@ def _load() -> C.CDLL:
         lib.vc1d_sizeof_prefill_args() != C.sizeof(PrefillArgs)
         or lib.vc1d_sizeof_update_args() != C.sizeof(UpdateArgs)
         or lib.vc1d_sizeof_prefill_bwd_args() != C.sizeof(PrefillBwdArgs)
+        or lib.vc1d_sizeof_update_bwd_args() != C.sizeof(UpdateBwdArgs)
     ):
         raise ImportError(f"{path}: argument struct layout differs from the binding; rebuild it")
     return lib

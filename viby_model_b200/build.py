@@ -35,6 +35,7 @@ SOURCES = [
     "prefill_bwd_tma_bf16.cu",
     "prefill_bwd_tma_f16.cu",
     "update.cu",
+    "update_bwd.cu",
 ]
 
 NVCC_FLAGS = [

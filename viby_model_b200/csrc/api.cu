@@ -277,6 +277,23 @@ VC1D_API int vc1d_update(const vc1d_update_args* a, void* stream) {
     return (int)err;
 }
 
+VC1D_API int vc1d_update_bwd(const vc1d_update_bwd_args* a, void* stream) {
+    using namespace vc1d;
+    if (a == nullptr) return VC1D_E_NULL;
+    if (a->struct_size != sizeof(vc1d_update_bwd_args)) return VC1D_E_STRUCT;
+    if (!is_io_dtype(a->dtype)) return VC1D_E_DTYPE;
+    if (a->wdtype != a->dtype && a->wdtype != VC1D_F32) return VC1D_E_DTYPE;
+    if (a->activation != VC1D_ACT_NONE && a->activation != VC1D_ACT_SILU) return VC1D_E_ACTIVATION;
+    if (a->width < 2 || a->width > 4) return VC1D_E_WIDTH;
+    if (a->batch < 0 || a->dim < 0 || a->state_len < a->width - 1) return VC1D_E_SHAPE;
+    if ((long long)a->batch * a->dim == 0) return VC1D_OK;
+    if (a->x == nullptr || a->conv_state == nullptr || a->dy == nullptr || a->dx == nullptr || a->weight == nullptr)
+        return VC1D_E_NULL;
+    return (int)launch_update_bwd(*a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+VC1D_API uint32_t vc1d_sizeof_update_bwd_args(void) { return (uint32_t)sizeof(vc1d_update_bwd_args); }
+
 VC1D_API int vc1d_abi_version(void) { return VC1D_ABI_VERSION; }
 VC1D_API uint32_t vc1d_sizeof_prefill_args(void) { return (uint32_t)sizeof(vc1d_prefill_args); }
 VC1D_API uint32_t vc1d_sizeof_update_args(void) { return (uint32_t)sizeof(vc1d_update_args); }

@@ -52,6 +52,9 @@ bool update_vec_supports(int state_len, int width);
 // Any strides, shifting or circular state.
 cudaError_t launch_update_generic(const vc1d_update_args& a, cudaStream_t s);
 
+// Backward of one decode step: any strides, shifting or circular state.
+cudaError_t launch_update_bwd(const vc1d_update_bwd_args& a, cudaStream_t s);
+
 inline int elem_bytes(int dtype) {
     switch (dtype) {
         case VC1D_F32: return 4;

@@ -437,6 +437,154 @@ def causal_conv1d_update(
     kernel: Optional[str] = None,
     block_threads: int = 0,
 ) -> torch.Tensor:
+    """Single-token causal conv step against a rolling ``conv_state`` (decode); see ``_update_forward``
+    for the arithmetic.  Differentiable in ``x``, ``conv_state`` (the state before the step),
+    ``weight`` and ``bias`` like ``short_conv_update_fn`` of causal-conv1d-mps (autograd.py:322-482):
+    when one of them requires grad, the state before the step is kept for the backward pass."""
+    needs_grad = torch.is_grad_enabled() and (
+        x.requires_grad or weight.requires_grad or conv_state.requires_grad
+        or (bias is not None and bias.requires_grad)
+    )
+    if not needs_grad:
+        return _update_forward(x, conv_state, weight, bias, activation, cache_seqlens, residual=residual, out=out,
+                               kernel=kernel, block_threads=block_threads)
+    if out is not None:
+        raise ValueError("out= cannot be used when a gradient is required")
+    return _CausalConv1dUpdateFunction.apply(x, conv_state, weight, bias, activation, cache_seqlens, residual)[0]
+
+
+def causal_conv1d_update_bwd(
+    x: torch.Tensor,
+    conv_state: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor],
+    dy: torch.Tensor,
+    activation: Optional[str] = None,
+    cache_seqlens: Optional[torch.Tensor] = None,
+    *,
+    residual: bool = False,
+    need_dstate: bool = True,
+):
+    """Gradients of one decode step: ``(dx, dstate, dweight, dbias)`` for ``x[batch, dim]``,
+    ``conv_state[batch, dim, state_len]`` AS IT WAS BEFORE the step, and the upstream ``dy[batch, dim]``.
+    ``dweight`` / ``dbias`` are fp32 sums (causal-conv1d-mps causal_conv1d.metal:1738-1845)."""
+    if x.dim() != 2 or conv_state.dim() != 3:
+        raise ValueError("expected x [batch, dim] and conv_state [batch, dim, state_len]")
+    batch, dim = x.shape
+    L = conv_state.shape[2]
+    if tuple(conv_state.shape[:2]) != (batch, dim) or dy.shape != x.shape:
+        raise ValueError("x, dy and conv_state do not agree in batch/dim")
+    width = _check_weight_shapes(weight, bias, dim)
+    if L < width - 1:
+        raise ValueError(f"conv_state length {L} is shorter than width-1 = {width - 1}")
+    if x.dtype not in _IO_DTYPES or conv_state.dtype != x.dtype or dy.dtype != x.dtype:
+        raise ValueError("x, conv_state and dy must share one of float32, bfloat16, float16")
+    act = _activation_code(activation)
+    _require_cuda(x, "Input")
+    _require_cuda(conv_state, "Convolution state")
+    weight, bias = _align_weights(x, weight, bias)
+    dx = torch.empty_like(x)
+    dstate = torch.empty((batch, dim, L), dtype=x.dtype, device=x.device) if need_dstate else None
+    dweight = torch.zeros(dim, width, dtype=torch.float32, device=x.device)
+    dbias = torch.zeros(dim, dtype=torch.float32, device=x.device) if bias is not None else None
+    a = _cabi.UpdateBwdArgs()
+    a.struct_size = C.sizeof(_cabi.UpdateBwdArgs)
+    a.dtype = _IO_DTYPES[x.dtype]
+    a.wdtype = _IO_DTYPES[weight.dtype]
+    a.activation = act
+    a.batch, a.dim, a.width, a.state_len = batch, dim, width, L
+    a.x, a.conv_state, a.dy, a.dx = x.data_ptr(), conv_state.data_ptr(), dy.data_ptr(), dx.data_ptr()
+    a.dstate = dstate.data_ptr() if dstate is not None else None
+    a.weight = weight.data_ptr()
+    a.bias = bias.data_ptr() if bias is not None else None
+    a.x_stride_b, a.x_stride_d = x.stride()
+    a.dy_stride_b, a.dy_stride_d = dy.stride()
+    a.dx_stride_b, a.dx_stride_d = dx.stride()
+    a.s_stride_b, a.s_stride_d, a.s_stride_l = conv_state.stride()
+    a.w_stride_d, a.w_stride_w = weight.stride()
+    if cache_seqlens is not None:
+        _require_cuda(cache_seqlens, "cache_seqlens")
+        if cache_seqlens.dtype != torch.int32 or not cache_seqlens.is_contiguous():
+            cache_seqlens = cache_seqlens.to(torch.int32).contiguous()
+        a.cache_seqlens = cache_seqlens.data_ptr()
+    a.residual = 1 if residual else 0
+    a.dweight = dweight.data_ptr()
+    a.dbias = dbias.data_ptr() if dbias is not None else None
+    if x.device.index != torch.cuda.current_device():
+        with torch.cuda.device(x.device):
+            st = _cabi.lib.vc1d_update_bwd(C.byref(a), _stream_handle(x.device))
+    else:
+        st = _cabi.lib.vc1d_update_bwd(C.byref(a), _stream_handle(x.device))
+    _cabi.check(st, "causal_conv1d_update_bwd")
+    return dx, dstate, dweight, dbias
+
+
+class _CausalConv1dUpdateFunction(torch.autograd.Function):
+    """Autograd glue of causal_conv1d_update.  The kernel overwrites conv_state, so the state the step
+    started from is cloned for the backward pass (as autograd.py:440-447 of causal-conv1d-mps does)."""
+
+    @staticmethod
+    def forward(ctx, x, conv_state, weight, bias, activation, cache_seqlens, residual):
+        before = conv_state.detach().clone()
+        y = _update_forward(x.detach(), conv_state.detach(), weight.detach(),
+                            bias.detach() if bias is not None else None, activation, cache_seqlens, residual=residual)
+        ctx.mark_dirty(conv_state)
+        ctx.save_for_backward(x, before, weight, bias if bias is not None else x.new_empty(0),
+                              cache_seqlens if cache_seqlens is not None else x.new_empty(0))
+        ctx.has_bias = bias is not None
+        ctx.has_seqlens = cache_seqlens is not None
+        ctx.activation = activation
+        ctx.residual = residual
+        ctx.squeeze = x.dim() == 3
+        return y, conv_state
+
+    @staticmethod
+    def backward(ctx, dy, dstate_after):
+        x, before, weight, bias, seqlens = ctx.saved_tensors
+        x2 = x.squeeze(-1) if ctx.squeeze else x
+        dy2 = dy.squeeze(-1) if ctx.squeeze else dy
+        dx, dstate, dw, db = causal_conv1d_update_bwd(
+            x2, before, weight, bias if ctx.has_bias else None, dy2.contiguous(), ctx.activation,
+            seqlens if ctx.has_seqlens else None, residual=ctx.residual, need_dstate=ctx.needs_input_grad[1],
+        )
+        if dstate_after is not None:
+            # gradient arriving through the updated state: the step moved the old columns (or kept
+            # them, circular) and stored x in one column
+            L = before.shape[2]
+            if ctx.has_seqlens:
+                pos = (seqlens.long() % L).view(-1, 1, 1).expand(-1, before.shape[1], 1)
+                dx = dx + dstate_after.gather(2, pos).squeeze(-1)
+                if dstate is not None:
+                    dstate = dstate + dstate_after.scatter(2, pos, 0.0)
+            else:
+                dx = dx + dstate_after[..., L - 1]
+                if dstate is not None and L > 1:
+                    dstate = dstate.clone()
+                    dstate[..., 1:] += dstate_after[..., : L - 1]
+        if ctx.squeeze:
+            dx = dx.unsqueeze(-1)
+        return (
+            dx if ctx.needs_input_grad[0] else None,
+            dstate if ctx.needs_input_grad[1] else None,
+            dw.to(weight.dtype) if ctx.needs_input_grad[2] else None,
+            db.to(bias.dtype) if (ctx.has_bias and ctx.needs_input_grad[3]) else None,
+            None, None, None,
+        )
+
+
+def _update_forward(
+    x: torch.Tensor,
+    conv_state: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    activation: Optional[str] = None,
+    cache_seqlens: Optional[torch.Tensor] = None,
+    *,
+    residual: bool = False,
+    out: Optional[torch.Tensor] = None,
+    kernel: Optional[str] = None,
+    block_threads: int = 0,
+) -> torch.Tensor:
     """Single-token causal conv step against a rolling ``conv_state`` (decode).
 
     ``cat = [conv_state | x]``; ``y = act(bias + cat[..., -W:] . weight)``;
