@@ -1,0 +1,71 @@
+"""torch.compile(fullgraph=True) over code that calls the operators (the reference compiles its
+model this way for evaluation, eval_model.py:157): the operators must trace as single graph nodes
+and give the eager results, forward and backward."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+if not torch.cuda.is_available():
+    pytest.skip("needs a CUDA device", allow_module_level=True)
+
+import viby_model_b200 as V  # noqa: E402
+
+DEV = torch.device("cuda", 0)
+
+
+def canon_like(x, w, b, mask):
+    """The fused CanonLayer body: mask, conv, SiLU, residual, final state; then a scaling to have
+    ordinary torch ops on both sides of the operator."""
+    y, state = V.causal_conv1d_fn((x * 1.0).transpose(1, 2), w, b, activation="silu", attention_mask=mask,
+                                  residual=True, return_final_states=True, state_len=4)
+    return y.transpose(1, 2) * 2.0, state
+
+
+def decode_like(xt, state, w, b):
+    y = V.causal_conv1d_update(xt, state, w, b, activation="silu")
+    return y + 1.0
+
+
+def test_compiled_prefill_and_decode_match_eager():
+    g = torch.Generator().manual_seed(0)
+    B, T, D = 3, 96, 256
+    x = torch.randn(B, T, D, generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randn(D, 4, generator=g).to(torch.bfloat16).to(DEV)
+    b = torch.randn(D, generator=g).to(torch.bfloat16).to(DEV)
+    mask = (torch.arange(T, device=DEV)[None, :] < torch.tensor([96, 40, 7], device=DEV)[:, None])
+    y_ref, st_ref = canon_like(x, w, b, mask)
+    before = V.launch_count()
+    compiled = torch.compile(canon_like, backend="aot_eager", fullgraph=True)
+    y, st = compiled(x, w, b, mask)
+    assert V.launch_count() > before, "the compiled graph did not reach the CUDA kernels"
+    assert torch.equal(y, y_ref) and torch.equal(st, st_ref)
+
+    xt = torch.randn(B, D, generator=g).to(torch.bfloat16).to(DEV)
+    s_eager, s_comp = st_ref.clone(), st_ref.clone()
+    y1 = decode_like(xt, s_eager, w, b)
+    y2 = torch.compile(decode_like, backend="aot_eager", fullgraph=True)(xt, s_comp, w, b)
+    assert torch.equal(y1, y2)
+    assert torch.equal(s_eager, s_comp), "the in-place state update was lost in the compiled graph"
+
+
+def test_compiled_backward_matches_eager():
+    g = torch.Generator().manual_seed(1)
+    B, T, D = 2, 64, 128
+    w0 = torch.randn(D, 4, generator=g).to(DEV)
+    b0 = torch.randn(D, generator=g).to(DEV)
+    x0 = torch.randn(B, T, D, generator=g).to(DEV)
+    mask = torch.ones(B, T, device=DEV, dtype=torch.bool)
+    mask[1, 50:] = False
+
+    def loss_fn(x, w, b):
+        y, _ = canon_like(x, w, b, mask)
+        return (y * y).sum()
+
+    grads = []
+    for fn in (loss_fn, torch.compile(loss_fn, backend="aot_eager", fullgraph=True)):
+        x, w, b = (t.clone().requires_grad_(True) for t in (x0, w0, b0))
+        fn(x, w, b).backward()
+        grads.append((x.grad, w.grad, b.grad))
+    for a, c in zip(*grads):
+        assert torch.allclose(a, c, rtol=1e-4, atol=1e-3)

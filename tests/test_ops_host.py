@@ -71,3 +71,23 @@ def test_valid_prefix_lengths_of_a_host_mask():
     m = torch.tensor([[1, 1, 0, 0], [0, 0, 0, 0], [1, 0, 1, 0], [1, 1, 1, 1], [0, 0, 0, 2]])
     assert HostPrefill.valid_prefix_lengths(m) == [2, 0, 3, 4, 4]
     assert HostPrefill.valid_prefix_lengths(m.bool()) == [2, 0, 3, 4, 4]
+
+
+def test_custom_ops_have_shape_functions():
+    """torch.ops.vc1d.* (what torch.compile sees) infer output shapes, strides and dtypes without a GPU."""
+    import viby_model_b200  # noqa: F401
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    with FakeTensorMode():
+        x = torch.empty(2, 16, 64, device="cuda", dtype=torch.bfloat16).transpose(1, 2)
+        w = torch.empty(64, 4, device="cuda", dtype=torch.bfloat16)
+        b = torch.empty(64, device="cuda", dtype=torch.bfloat16)
+        y, st = torch.ops.vc1d.prefill(x, w, b, None, None, None, 1, True, True, 4)
+        assert y.shape == x.shape and y.stride() == x.stride() and y.dtype == x.dtype
+        assert st.shape == (2, 64, 4)
+        y2, st2 = torch.ops.vc1d.prefill(x, w, None, None, None, None, 0, False, True, 0)
+        assert st2.numel() == 0
+        dx, dw, db = torch.ops.vc1d.prefill_bwd(x, w, b, y, None, 1, True)
+        assert dx.stride() == x.stride() and dw.shape == (64, 4) and dw.dtype == torch.float32 and db.shape == (64,)
+        s = torch.empty(2, 64, 4, device="cuda", dtype=torch.bfloat16)
+        assert torch.ops.vc1d.update(x[..., 0], s, w, b, None, 1, False).shape == (2, 64)

@@ -154,6 +154,19 @@ def causal_conv1d_fn(
     causal-conv1d-mps autograd.py:116-151, 305-338): when any of them requires grad the backward
     pass runs ``causal_conv1d_bwd``.  ``initial_states`` and ``out=`` are forward-only.
     """
+    if torch.compiler.is_compiling():
+        # inside torch.compile the operator is one opaque graph node (compile_ops.py)
+        if seq_idx is not None:
+            raise NotImplementedError("seq_idx is not supported")
+        if out is not None or final_states_out is not None:
+            raise ValueError("out= / final_states_out= cannot be used under torch.compile")
+        want_state = bool(return_final_states)
+        L = int(state_len) if state_len is not None else weight.shape[1] - 1
+        y, state = torch.ops.vc1d.prefill(
+            x, weight, bias, attention_mask, residual if isinstance(residual, torch.Tensor) else None,
+            initial_states, _activation_code(activation), residual is True, bool(skip_masked_loads),
+            L if want_state else 0)
+        return (y, state) if want_state else y
     needs_grad = torch.is_grad_enabled() and (
         x.requires_grad or weight.requires_grad or (bias is not None and bias.requires_grad)
         or (isinstance(residual, torch.Tensor) and residual.requires_grad)
@@ -441,6 +454,13 @@ def causal_conv1d_update(
     for the arithmetic.  Differentiable in ``x``, ``conv_state`` (the state before the step),
     ``weight`` and ``bias`` like ``short_conv_update_fn`` of causal-conv1d-mps (autograd.py:322-482):
     when one of them requires grad, the state before the step is kept for the backward pass."""
+    if torch.compiler.is_compiling():
+        if out is not None:
+            raise ValueError("out= cannot be used under torch.compile")
+        squeeze = x.dim() == 3
+        y = torch.ops.vc1d.update(x.squeeze(-1) if squeeze else x, conv_state, weight, bias, cache_seqlens,
+                                  _activation_code(activation), bool(residual))
+        return y.unsqueeze(-1) if squeeze else y
     needs_grad = torch.is_grad_enabled() and (
         x.requires_grad or weight.requires_grad or conv_state.requires_grad
         or (bias is not None and bias.requires_grad)
