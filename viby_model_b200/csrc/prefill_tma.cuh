@@ -715,7 +715,9 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     p.gtable = nullptr;
     p.table_in_smem = 0;
     const long long table_need = a.mask != nullptr ? n_rowtiles : 0;
-    const bool use_scratch = a.scratch != nullptr && 4LL * (n_slab + 1) <= kSchedCounterBytes &&
+    // dynamic claims pay off once a CTA has several tiles; with two or three the claim round trips
+    // (and, with a mask, the pre-pass) cost more than the balance gains
+    const bool use_scratch = tiles_per_cta >= 4 && a.scratch != nullptr && 4LL * (n_slab + 1) <= kSchedCounterBytes &&
                              a.scratch_bytes >= kSchedCounterBytes + table_need &&
                              (reinterpret_cast<uintptr_t>(a.scratch) & 15u) == 0;
     unsigned char* tab = nullptr;

@@ -42,6 +42,11 @@ __global__ void __launch_bounds__(256) k_update_vec(const UParams p) {
     using PK = Pack<DT>;
     constexpr int VEC = E::kVec;
     constexpr int UB = 2;  // sequences in flight per thread
+    // Launched with programmatic stream serialization: consecutive decode steps depend on each other
+    // through conv_state, so every thread waits for the previous kernel before its first access,
+    // while the launch itself and the scheduling of the CTAs overlap the previous step's tail.
+    griddep_wait();
+    griddep_launch_dependents();
     const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (g >= p.total) return;
     const int lane = (int)(g % p.nvec);
@@ -237,21 +242,35 @@ UParams make_params(const vc1d_update_args& a) {
     return p;
 }
 
+template <class Kernel>
+cudaError_t launch_pdl(Kernel kernel, const UParams& p, dim3 grid, int block, cudaStream_t s) {
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, p);
+}
+
 template <int DT, int W>
 cudaError_t launch_vec_l(const UParams& p, dim3 grid, int block, cudaStream_t s) {
     switch (p.L) {
         case 1:
-            if (W == 2) k_update_vec<DT, (W == 2 ? W : 2), 1><<<grid, block, 0, s>>>(p);
-            break;
+            if (W == 2) return launch_pdl(k_update_vec<DT, (W == 2 ? W : 2), 1>, p, grid, block, s);
+            return cudaErrorInvalidValue;
         case 2:
-            if (W <= 3) k_update_vec<DT, (W <= 3 ? W : 2), 2><<<grid, block, 0, s>>>(p);
-            break;
-        case 3: k_update_vec<DT, W, 3><<<grid, block, 0, s>>>(p); break;
-        case 4: k_update_vec<DT, W, 4><<<grid, block, 0, s>>>(p); break;
-        case 8: k_update_vec<DT, W, 8><<<grid, block, 0, s>>>(p); break;
+            if (W <= 3) return launch_pdl(k_update_vec<DT, (W <= 3 ? W : 2), 2>, p, grid, block, s);
+            return cudaErrorInvalidValue;
+        case 3: return launch_pdl(k_update_vec<DT, W, 3>, p, grid, block, s);
+        case 4: return launch_pdl(k_update_vec<DT, W, 4>, p, grid, block, s);
+        case 8: return launch_pdl(k_update_vec<DT, W, 8>, p, grid, block, s);
         default: return cudaErrorInvalidValue;
     }
-    return cudaGetLastError();
 }
 
 template <int DT>
