@@ -12,6 +12,7 @@ There is no PyTorch or CPU implementation behind these functions.
 from __future__ import annotations
 
 import ctypes as C
+import threading
 from typing import Optional, Tuple, Union
 
 import torch
@@ -78,7 +79,12 @@ def _align_weights(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
     return weight, bias
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream_handle(device: torch.device) -> int:
+    if _raw_stream is not None and device.index is not None:
+        return _raw_stream(device.index)
     return torch.cuda.current_stream(device).cuda_stream
 
 
@@ -592,6 +598,40 @@ class _CausalConv1dUpdateFunction(torch.autograd.Function):
         )
 
 
+# Prepared vc1d_update_args per call signature (shapes, strides, dtypes, options): a decode step is
+# launch-bound, so a repeated call only refreshes the five pointers instead of re-validating and
+# re-filling the whole struct.
+_TLS = threading.local()  # per host thread: the library call releases the GIL while it reads the struct
+
+
+def _update_fast(x, conv_state, weight, bias, activation, cache_seqlens, residual, out, kernel, block_threads):
+    """The cached-signature path of _update_forward; returns None when the signature is new."""
+    key = (x.shape, x.stride(), x.dtype, x.device.index, conv_state.shape, conv_state.stride(), conv_state.dtype,
+           weight.shape, weight.stride(), weight.dtype,
+           None if bias is None else (bias.shape, bias.dtype, bias.stride()),
+           activation, bool(residual), kernel, block_threads, None if out is None else (out.shape, out.stride(), out.dtype))
+    cache = getattr(_TLS, "update_args", None)
+    a = cache.get(key) if cache is not None else None
+    if a is None:
+        return None, key
+    if out is None:
+        out = torch.empty_like(x)
+    a.x = x.data_ptr()
+    a.y = out.data_ptr()
+    a.conv_state = conv_state.data_ptr()
+    a.weight = weight.data_ptr()
+    a.bias = bias.data_ptr() if bias is not None else None
+    dev = x.device
+    if dev.index != torch.cuda.current_device():
+        with torch.cuda.device(dev):
+            st = _cabi.lib.vc1d_update(C.byref(a), _stream_handle(dev))
+    else:
+        st = _cabi.lib.vc1d_update(C.byref(a), _stream_handle(dev))
+    if st != 0:
+        _cabi.check(st, "causal_conv1d_update")
+    return out, key
+
+
 def _update_forward(
     x: torch.Tensor,
     conv_state: torch.Tensor,
@@ -622,6 +662,12 @@ def _update_forward(
     if x.dim() == 3 and x.shape[-1] == 1:
         x = x.squeeze(-1)
         squeeze = True
+    fast_key = None
+    if cache_seqlens is None and x.is_cuda and conv_state.is_cuda and weight.is_cuda and (bias is None or bias.is_cuda):
+        y, fast_key = _update_fast(x, conv_state, weight, bias, activation, cache_seqlens, residual, out, kernel,
+                                   block_threads)
+        if y is not None:
+            return y.unsqueeze(-1) if squeeze else y
     if x.dim() != 2:
         raise ValueError(f"Expected 2D input tensor (batch, dim), got {x.dim()}D")
     if conv_state.dim() != 3:
@@ -640,6 +686,7 @@ def _update_forward(
     act = _activation_code(activation)
     _require_cuda(x, "Input")
     _require_cuda(conv_state, "Convolution state")
+    weight_given, bias_given = weight, bias
     weight, bias = _align_weights(x, weight, bias)
 
     if out is None:
@@ -683,4 +730,12 @@ def _update_forward(
     else:
         st = _cabi.lib.vc1d_update(C.byref(a), _stream_handle(x.device))
     _cabi.check(st, "causal_conv1d_update")
+    # remember the validated struct for calls with the same signature (weights whose dtype had to be
+    # converted are a fresh tensor every call: those keep the full path)
+    if fast_key is not None and weight is weight_given and bias is bias_given:
+        cache = getattr(_TLS, "update_args", None)
+        if cache is None:
+            cache = _TLS.update_args = {}
+        if len(cache) < 256:
+            cache[fast_key] = a
     return out.unsqueeze(-1) if squeeze else out
