@@ -469,3 +469,22 @@ def test_config5_ragged_shard_properties():
     # (5) sharding is invisible: a sub-batch gives the same bits
     y_sub = V.causal_conv1d_fn(x[8:24].transpose(1, 2), w, b, activation="silu", attention_mask=m[8:24])
     assert torch.equal(y_sub, y[8:24])
+
+
+def test_multi_tensor_call_equals_concatenated_call():
+    """q | k | v (or gate | up) given as separate tensors: same bits as the reference's cat-conv-split."""
+    g = torch.Generator().manual_seed(21)
+    B, T = 3, 200
+    dims = (640, 160, 160)
+    xs = [torch.randn(B, T, d, generator=g).to(torch.bfloat16).to(DEV) for d in dims]
+    w = torch.randn(sum(dims), 4, generator=g).to(torch.bfloat16).to(DEV)
+    b = torch.randn(sum(dims), generator=g).to(torch.bfloat16).to(DEV)
+    m = dev(right_pad_mask(B, T, 3))
+    cat = torch.cat(xs, dim=-1)
+    ref = V.causal_conv1d_fn(cat.transpose(1, 2), w, b, activation="silu", attention_mask=m, residual=True)
+    outs = V.causal_conv1d_fn_multi([x.transpose(1, 2) for x in xs], w, b, activation="silu", attention_mask=m,
+                                    residual=True)
+    d0 = 0
+    for o, d in zip(outs, dims):
+        assert torch.equal(o, ref[:, d0:d0 + d])
+        d0 += d

@@ -193,6 +193,28 @@ def causal_conv1d_fn(
     return result if (return_final_states or final_states_out is not None) else result[0]
 
 
+def causal_conv1d_fn_multi(xs, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, activation=None, **kwargs):
+    """``causal_conv1d_fn`` over tensors that together form the channel dimension, without
+    concatenating them: ``xs`` is a sequence of ``[batch, dim_i, seqlen]`` tensors (e.g. the q, k and
+    v projections, or gate and up), ``weight[sum(dim_i), width]`` / ``bias[sum(dim_i)]`` cover them in
+    order.  Returns the list of outputs.  Replaces the ``torch.cat`` before and the split after the
+    Canon-B and Canon-D calls of the reference (model/model.py:772-789, 962-971): one launch per
+    tensor on its own rows of the weights, no extra pass over the activations.  Keyword arguments
+    are those of ``causal_conv1d_fn`` (``residual=True`` adds each tensor to its own output)."""
+    total = sum(int(x.shape[1]) for x in xs)
+    if weight.dim() != 2 or weight.shape[0] != total:
+        raise ValueError(f"weight rows {tuple(weight.shape)} do not match the summed dims {total}")
+    if isinstance(kwargs.get("residual"), torch.Tensor) or kwargs.get("out") is not None:
+        raise ValueError("a residual tensor or out= applies to one tensor: call causal_conv1d_fn per tensor")
+    outs, d0 = [], 0
+    for x in xs:
+        d1 = d0 + int(x.shape[1])
+        outs.append(causal_conv1d_fn(x, weight[d0:d1], None if bias is None else bias[d0:d1], activation=activation,
+                                     **kwargs))
+        d0 = d1
+    return outs
+
+
 def _prefill_forward(
     x, weight, bias=None, seq_idx=None, initial_states=None, return_final_states=False, final_states_out=None,
     activation=None, *, attention_mask=None, skip_masked_loads=True, residual=None, state_len=None, out=None,
