@@ -256,9 +256,15 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        # keep stdout for the one JSON line: NCCL's own banner and logs go to stderr
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        # Keep stdout for the one JSON line: NCCL prints its version banner (and, with NCCL_DEBUG
+        # set, its logs) straight to file descriptor 1, so fd 1 is pointed at stderr for the run and
+        # the result is written to a private copy of the original stdout.
+        sys.stdout.flush()
+        result_out = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=dev)
+    else:
+        result_out = sys.stdout
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
 
@@ -285,7 +291,7 @@ def main():
     if args.decode_saturating_only:
         res = bench_decode_saturating(V, WL, dev, world, barrier, max_over_ranks)
         if rank == 0:
-            print(json.dumps({"decode_saturating": res}))
+            print(json.dumps({"decode_saturating": res}), file=result_out, flush=True)
         if world > 1:
             dist.destroy_process_group()
         return
@@ -434,7 +440,7 @@ def main():
             "ms": best * 1e3,
         }
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=result_out, flush=True)
     if world > 1:
         dist.destroy_process_group()
 

@@ -448,10 +448,13 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         int n_issued = 0;
         auto next_tile = [&]() -> int {
             unsigned raw;
-            if (dynamic) {
+            if (dynamic && n_issued > 0) {
+                // the counter hands out the tiles behind the first one of every CTA of the slab
                 raw = 0u;
                 if (lane == 0) raw = atomicAdd(p.sched + slab, 1u);
-                raw = __shfl_sync(0xffffffffu, raw, 0);
+                raw = __shfl_sync(0xffffffffu, raw, 0) + (unsigned)stride;
+            } else if (dynamic) {
+                raw = (unsigned)j0;  // a CTA's first tile needs no claim: the copy starts a round trip earlier
             } else {
                 raw = n_issued < n_my ? (unsigned)(j0 + n_issued * stride) : 0xffffffffu;
             }
