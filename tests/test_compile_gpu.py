@@ -27,7 +27,8 @@ def decode_like(xt, state, w, b):
     return y + 1.0
 
 
-def test_compiled_prefill_and_decode_match_eager():
+@pytest.mark.parametrize("backend", ["aot_eager", "inductor"])
+def test_compiled_prefill_and_decode_match_eager(backend):
     g = torch.Generator().manual_seed(0)
     B, T, D = 3, 96, 256
     x = torch.randn(B, T, D, generator=g).to(torch.bfloat16).to(DEV)
@@ -36,7 +37,7 @@ def test_compiled_prefill_and_decode_match_eager():
     mask = (torch.arange(T, device=DEV)[None, :] < torch.tensor([96, 40, 7], device=DEV)[:, None])
     y_ref, st_ref = canon_like(x, w, b, mask)
     before = V.launch_count()
-    compiled = torch.compile(canon_like, backend="aot_eager", fullgraph=True)
+    compiled = torch.compile(canon_like, backend=backend, fullgraph=True)
     y, st = compiled(x, w, b, mask)
     assert V.launch_count() > before, "the compiled graph did not reach the CUDA kernels"
     assert torch.equal(y, y_ref) and torch.equal(st, st_ref)
@@ -44,12 +45,13 @@ def test_compiled_prefill_and_decode_match_eager():
     xt = torch.randn(B, D, generator=g).to(torch.bfloat16).to(DEV)
     s_eager, s_comp = st_ref.clone(), st_ref.clone()
     y1 = decode_like(xt, s_eager, w, b)
-    y2 = torch.compile(decode_like, backend="aot_eager", fullgraph=True)(xt, s_comp, w, b)
+    y2 = torch.compile(decode_like, backend=backend, fullgraph=True)(xt, s_comp, w, b)
     assert torch.equal(y1, y2)
     assert torch.equal(s_eager, s_comp), "the in-place state update was lost in the compiled graph"
 
 
-def test_compiled_backward_matches_eager():
+@pytest.mark.parametrize("backend", ["aot_eager", "inductor"])
+def test_compiled_backward_matches_eager(backend):
     g = torch.Generator().manual_seed(1)
     B, T, D = 2, 64, 128
     w0 = torch.randn(D, 4, generator=g).to(DEV)
@@ -63,7 +65,7 @@ def test_compiled_backward_matches_eager():
         return (y * y).sum()
 
     grads = []
-    for fn in (loss_fn, torch.compile(loss_fn, backend="aot_eager", fullgraph=True)):
+    for fn in (loss_fn, torch.compile(loss_fn, backend=backend, fullgraph=True)):
         x, w, b = (t.clone().requires_grad_(True) for t in (x0, w0, b0))
         fn(x, w, b).backward()
         grads.append((x.grad, w.grad, b.grad))
