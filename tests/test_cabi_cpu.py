@@ -127,3 +127,31 @@ def test_missing_library_fails_loudly(tmp_path, monkeypatch):
     monkeypatch.setenv("VC1D_LIBRARY", str(tmp_path / "nope.so"))
     with pytest.raises(ImportError, match="no CPU or PyTorch fallback"):
         _cabi._load()
+
+
+def test_header_is_plain_c(tmp_path):
+    """include/vc1d.h is the boundary for C, cgo, JNI or FFI callers: it must compile as C99 on its own,
+    and the struct sizes a C compiler computes must be the ones the library was built with."""
+    import shutil
+    import subprocess
+
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "probe.c"
+    src.write_text(
+        '#include <stdio.h>\n#include "vc1d.h"\n'
+        "int main(void) {\n"
+        "  vc1d_prefill_args a = {0}; vc1d_update_args u = {0}; vc1d_prefill_bwd_args g = {0}; vc1d_update_bwd_args h = {0};\n"
+        "  a.struct_size = sizeof a; u.struct_size = sizeof u; g.struct_size = sizeof g; h.struct_size = sizeof h;\n"
+        '  printf("%u %u %u %u %d\\n", a.struct_size, u.struct_size, g.struct_size, h.struct_size, VC1D_NOALLOC_MAX_TILES);\n'
+        "  return 0;\n}\n"
+    )
+    exe = tmp_path / "probe"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-pedantic", "-I", str(ROOT / "include"), str(src), "-o", str(exe)],
+                   check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    sizes = [int(v) for v in out[:4]]
+    assert sizes == [_cabi.lib.vc1d_sizeof_prefill_args(), _cabi.lib.vc1d_sizeof_update_args(),
+                     _cabi.lib.vc1d_sizeof_prefill_bwd_args(), _cabi.lib.vc1d_sizeof_update_bwd_args()]
+    assert int(out[4]) == 61440
