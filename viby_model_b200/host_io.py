@@ -22,10 +22,12 @@ from .ops import causal_conv1d_fn
 
 class HostPrefill:
     def __init__(self, batch: int, seqlen: int, dim: int, dtype: torch.dtype, device="cuda",
-                 chunk_batch: int = 4, masked: bool = True, mask_dtype: torch.dtype = torch.int64):
+                 chunk_batch: int = 4, masked: bool = True, mask_dtype: torch.dtype = torch.int64,
+                 send_masked_rows: bool = False):
         self.device = torch.device(device)
         self.batch, self.seqlen, self.dim, self.dtype = batch, seqlen, dim, dtype
         self.chunk = max(1, min(chunk_batch, batch))
+        self.send_masked_rows = send_masked_rows  # True: copy all of x, also the rows no kernel reads
         self.x_dev = torch.empty(batch, seqlen, dim, dtype=dtype, device=self.device)
         self.y_dev = torch.empty_like(self.x_dev)
         self.m_dev = torch.empty(batch, seqlen, dtype=mask_dtype, device=self.device) if masked else None
@@ -69,6 +71,8 @@ class HostPrefill:
         self.s_h2d.wait_stream(main)  # the inputs may come from work queued on the caller's stream
         masked = self.m_dev is not None and mask_host is not None
         lens = self.valid_prefix_lengths(mask_host) if masked else None
+        if self.send_masked_rows and lens is not None:
+            lens = [self.seqlen] * self.batch
         row_bytes = self.dim * self.x_dev.element_size()
         sent = 0
         for i, b0 in enumerate(range(0, self.batch, self.chunk)):
