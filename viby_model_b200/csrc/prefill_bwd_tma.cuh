@@ -63,6 +63,10 @@ struct BwdGeometry {
     static constexpr int kXBytes = kXRows * kRowBytes;
     static constexpr int kGBytes = kGRows * kRowBytes;
     static constexpr int kStageBytes = kXBytes + kGBytes;  // rows are 128 or 256 bytes: stays 128-byte aligned
+    // fp32 I/O (one channel pair per thread) fits 72 registers: 3 CTAs per SM with a 2-stage ring.  16-bit I/O
+    // (two pairs) needs 96: 2 CTAs per SM with 3 stages; squeezed to 72 it spills and runs at half the speed.
+    static constexpr int kCtasPerSm = (DT == VC1D_F32) ? 3 : 2;
+    static constexpr int kDefaultStages = (DT == VC1D_F32) ? 2 : 3;
     // layout for S stages: stages | full[S], done[S] | tile descriptor[S]
     __host__ __device__ static constexpr int off_bars(int S) { return S * kStageBytes; }
     __host__ __device__ static constexpr int off_flags(int S) { return off_bars(S) + 2 * S * 8; }
@@ -101,7 +105,7 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
 }
 
 template <int DT, int W, int SLAB_BYTES, bool ACT>
-__global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES>::kThreads, 2)
+__global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES>::kThreads, BwdGeometry<DT, W, SLAB_BYTES>::kCtasPerSm)
     k_prefill_bwd_tma(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_g,
                       const BwdParams p) {
     using E = Elem<DT>;
@@ -469,10 +473,10 @@ cudaError_t launch_bwd_kernel(const vc1d_prefill_bwd_args& a, const BwdParams& b
     if (!make_map(&tmap_x, a.x, a.x_stride_t, a.x_stride_b, G::kXRows)) return cudaErrorNotSupported;
     if (!make_map(&tmap_g, a.dy, a.dy_stride_t, a.dy_stride_b, G::kGRows)) return cudaErrorNotSupported;
 
-    int stages = a.tma_stages > 0 ? a.tma_stages : 3;
+    int stages = a.tma_stages > 0 ? a.tma_stages : G::kDefaultStages;
     if (stages < 2) stages = 2;
     if (stages > kMaxStages) stages = kMaxStages;
-    const int per_sm = (a.tma_ctas_per_sm > 0 && a.tma_ctas_per_sm <= 8) ? a.tma_ctas_per_sm : 2;
+    const int per_sm = (a.tma_ctas_per_sm > 0 && a.tma_ctas_per_sm <= 8) ? a.tma_ctas_per_sm : G::kCtasPerSm;
     p.stages = stages;
     const bool use_sched = a.scratch != nullptr && 4LL * (n_slab + 1) <= kSchedCounterBytes &&
                            a.scratch_bytes >= kSchedCounterBytes && (reinterpret_cast<uintptr_t>(a.scratch) & 15u) == 0;
