@@ -396,7 +396,6 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
     // Launched with programmatic stream serialization, this grid may start while its predecessor in
     // the stream is still running: nothing above touched global memory, everything below may.
     griddep_wait();
-    griddep_launch_dependents();
     if (p.gtable != nullptr && p.table_in_smem) {
         const int n16 = p.n_rowtiles >> 4;
         const uint4* src = reinterpret_cast<const uint4*>(p.gtable);
@@ -510,6 +509,10 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
             put_tile(b_now, t0_now, cls_now);
             advance();
         }
+        // Every tile of this CTA is on its way: a dependent launch of the stream may now take the slots
+        // that CTAs free as they finish (triggering at the top was measured slower: the early
+        // CTAs of the next launch disturb the steady state of this one).
+        griddep_launch_dependents();
         // END marker: the consumers leave when they meet it
         if (live && claim()) {
             if (lane == 0) {
@@ -756,7 +759,7 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     // A masked launch with a pre-pass uses programmatic stream serialization for both kernels: each
     // may start while its predecessor in the stream drains, and waits (griddep_wait) before it
     // touches global memory, which hides the pre-pass and both launch latencies.  Launches without
-    // a pre-pass are serialized normally: letting dense launches overlap was measured slower.
+    // a pre-pass are serialized normally: letting dense launches overlap brought nothing.
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = (pdl_enabled() && tab != nullptr) ? 1 : 0;
