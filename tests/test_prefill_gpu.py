@@ -230,7 +230,7 @@ def test_final_state_and_residual(T, L, dtype, kernel):
                        ref_s.view(torch.int16 if dtype != torch.float32 else torch.int32))
 
 
-@pytest.mark.parametrize("kernel", ["channel_last", "generic"])
+@pytest.mark.parametrize("kernel", ["channel_last", "generic", "tma"])
 @pytest.mark.parametrize("W", [2, 3, 4])
 @pytest.mark.parametrize("T2", [1, 2, 5, 37])
 def test_initial_states_continue_a_sequence(T2, W, kernel):
@@ -488,3 +488,39 @@ def test_multi_tensor_call_equals_concatenated_call():
     for o, d in zip(outs, dims):
         assert torch.equal(o, ref[:, d0:d0 + d])
         d0 += d
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_tma_chunked_continuation_with_masks(dtype):
+    """A long prefill cut into chunks that hand their state on (the reference's chunked continuation,
+    model/model.py:607-661), several tiles per chunk, masked tails: every chunk through the TMA-staged
+    kernel equals the register-window kernel and the oracle, outputs and states."""
+    B, D, W, L = 3, 640, 4, 4
+    chunks = (200, 1, 130, 77)
+    T = sum(chunks)
+    x, w, b = make(B, D, T, W, dtype, True, seed=77)
+    m = right_pad_mask(B, T, 9)
+    m[1, 150:] = 0  # a sequence whose later chunks are entirely masked: first tile still sees history
+    xd, wd, bd, md = dev(x), dev(w), dev(b), dev(m)
+    states = {"tma": None, "channel_last": None}
+    ref_state = None
+    t0 = 0
+    for n in chunks:
+        sl = slice(t0, t0 + n)
+        outs = {}
+        for kernel in states:
+            y, st = V.causal_conv1d_fn(xd[..., sl], wd, bd, activation="silu", attention_mask=md[:, sl],
+                                       initial_states=states[kernel], return_final_states=True, state_len=L,
+                                       kernel=kernel)
+            assert V.last_kernel() == kernel
+            outs[kernel] = y
+            states[kernel] = st
+        assert torch.equal(outs["tma"], outs["channel_last"])
+        assert torch.equal(states["tma"], states["channel_last"])
+        ref_y, ref_state = O.causal_conv1d_ref(x[..., sl], w, b, "silu", attention_mask=m[:, sl],
+                                               initial_states=ref_state, state_len=L)
+        assert_close_to_oracle(outs["tma"], ref_y)
+        assert torch.equal(states["tma"].cpu(), ref_state)
+        t0 += n
+    torch.cuda.synchronize()
+    assert V.tma_timeouts() == 0

@@ -204,7 +204,7 @@ VC1D_API int vc1d_prefill(const vc1d_prefill_args* a, void* stream) {
             err = launch_prefill_channel_last(*a, s);
             break;
         case VC1D_KERNEL_TMA:
-            if (!cl || a->initial_state != nullptr || !tma_available()) return VC1D_E_STRIDE;
+            if (!cl || !tma_available()) return VC1D_E_STRIDE;
             err = launch_prefill_tma(*a, s);
             break;
         case VC1D_KERNEL_TIME_MAJOR:
@@ -221,7 +221,7 @@ VC1D_API int vc1d_prefill(const vc1d_prefill_args* a, void* stream) {
                 // take the direct kernel, as does anything the tensor map cannot describe
                 const long long elems = (long long)a->batch * a->dim * a->seqlen;
                 err = cudaErrorNotSupported;
-                if (a->initial_state == nullptr && a->seqlen >= 16 && elems >= (1LL << 20) && tma_available())
+                if (a->seqlen >= 16 && elems >= (1LL << 20) && tma_available())
                     err = launch_prefill_tma(*a, s);
                 if (err == cudaErrorNotSupported) err = launch_prefill_channel_last(*a, s);
             } else if (tm) {

@@ -516,6 +516,7 @@ cudaError_t launch_bwd_kernel(const vc1d_prefill_bwd_args& a, const BwdParams& b
             cp.n_ttile = p.n_ttile;
             cp.skip = 1;
             cp.res = nullptr;
+            cp.init = nullptr;
             unsigned char* tab = reinterpret_cast<unsigned char*>(a.scratch) + kSchedCounterBytes;
             const long long threads = n_rowtiles * 32;
             k_classify_tiles<<<(unsigned)((threads + 255) / 256), 256, 0, s>>>(cp, tab, (int)G::kTileRows, (int)G::kH,

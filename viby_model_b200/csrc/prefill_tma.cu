@@ -60,6 +60,8 @@ cudaError_t launch_prefill_tma(const vc1d_prefill_args& a, cudaStream_t s) {
     p.syt = a.y_stride_t * eb;
     p.x = reinterpret_cast<const char*>(a.x);
     p.res = reinterpret_cast<const char*>(a.residual);
+    p.init = reinterpret_cast<const char*>(a.initial_state);
+    p.init_len = a.init_len;
     p.weight = a.weight;
     p.bias = a.bias;
     p.mask = a.mask;

@@ -49,6 +49,7 @@ struct TmaParams {
     long long syb, syt;
     const char* x;  // for the final-state pass
     const char* res;
+    const char* init;   // initial state [B, D, init_len] (history instead of zeros left of t = 0), or NULL
     const void* weight;
     const void* bias;
     const void* mask;
@@ -65,6 +66,7 @@ struct TmaParams {
     int n_ttile, n_rowtiles, ctas_per_slab;
     int mask_dtype;
     int skip;
+    int init_len;
     int res_is_x;
     int table_in_smem;  // the pre-pass class table fits in shared memory and every CTA copies it there
     int state_len;
@@ -321,7 +323,9 @@ __device__ __forceinline__ int classify_tile(const TmaParams& p, int b, int t0, 
     }
     any = __any_sync(0xffffffffu, any);
     all_one = __all_sync(0xffffffffu, all_one);
-    return all_one ? TILE_FULL : ((any || !p.skip || p.res != nullptr) ? TILE_MIXED : TILE_EMPTY);
+    // (with an initial state the first rows of a sequence see history even if every input is masked)
+    const bool history = p.init != nullptr && t0 == 0;
+    return all_one ? TILE_FULL : ((any || !p.skip || p.res != nullptr || history) ? TILE_MIXED : TILE_EMPTY);
 }
 
 // Pre-pass of masked launches that schedule dynamically: the class of every (sequence, time tile),
@@ -597,6 +601,23 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
                 S::lds(trow + w * G::kRowBytes, raw);
                 S::unpack(raw, hist[w]);
             }
+            if (p.init != nullptr && rbase == 0 && ch_ok && lds_s32(flags + 32 * s + 20) == 0) {
+                // first rows of a sequence: the W-1 rows above them come from the initial state
+                using T = typename E::type;
+                const int b = lds_s32(flags + 32 * s + 16);
+                const T* in = reinterpret_cast<const T*>(p.init) + ((long long)b * p.D + d0) * p.init_len;
+#pragma unroll
+                for (int w = 0; w < H; ++w) {
+                    T vals[NE];
+#pragma unroll
+                    for (int c = 0; c < NE; ++c) vals[c] = in[(long long)c * p.init_len + (p.init_len - H + w)];
+                    uint32_t raw[NW];
+                    const uint32_t* vw = reinterpret_cast<const uint32_t*>(vals);
+#pragma unroll
+                    for (int i = 0; i < NW; ++i) raw[i] = vw[i];
+                    S::unpack(raw, hist[w]);
+                }
+            }
             if (!general_kernel || (cls == TILE_FULL && p.res == nullptr)) {
                 process_rows<DT, W, VB, RPT, ACT, false, G::kRowBytes>(trow, 1.0f, 0, p, false, nullptr, yrow, pitch, 0,
                                                                        rows_ok, hist, wp, bp);
@@ -644,6 +665,9 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
                         if (t >= 0) {
                             v = xb[(long long)t * (p.sxt / E::kBytes) + c];
                             if (mkv != 1.0f) v = E::from_float(E::to_float(v) * mkv);
+                        } else if (p.init != nullptr && p.init_len + t >= 0) {
+                            v = reinterpret_cast<const T*>(p.init)[((long long)b * p.D + d0 + c) * p.init_len +
+                                                                    (p.init_len + t)];
                         }
                         out[(long long)c * L + jc] = v;
                     }

@@ -24,7 +24,7 @@ void note_launch(const char* kernel_name);
 // base pointer and every batch/time stride is 16-byte aligned.
 cudaError_t launch_prefill_channel_last(const vc1d_prefill_args& a, cudaStream_t s);
 
-// Same preconditions as channel-last plus: no initial_state, dim*elem_size % 16 == 0
+// Same preconditions as channel-last plus: dim*elem_size % 16 == 0
 // (tensor-map stride rule).  Stages (rows + halo) x channel tiles through shared memory
 // with cp.async.bulk.tensor.
 cudaError_t launch_prefill_tma(const vc1d_prefill_args& a, cudaStream_t s);
