@@ -5,23 +5,35 @@
 //
 // Geometry.  A tile is kTileRows time rows x one 128- or 256-byte slab of channels of one
 // sequence.  Its input box, (kTileRows + W-1) rows starting W-1 rows ABOVE the tile, arrives in
-// shared memory by one cp.async.bulk.tensor.3d load (no multicast); rows before t = 0 are
+// shared memory by one cp.async.bulk.tensor.3d load issued by its own CTA; rows before t = 0 are
 // out of bounds for the tensor map and are zero-filled by the hardware, which is exactly the
-// causal left padding.  The grid is (channel slabs) x (persistent CTAs per slab): a CTA keeps
-// the weights of its slab in registers for its whole life and walks row tiles
-// j, j + G, j + 2G, ... of that slab, so neighbouring CTAs touch neighbouring rows and the
-// (W-1)-row halo of a tile is an L2 hit.
+// causal left padding (with an initial state, the first tile of a sequence reads those rows from
+// the state instead).  The grid is (channel slabs) x (persistent CTAs per slab): a CTA keeps the
+// weights of its slab in registers for its whole life.
+//
+// Which tile a CTA takes next.  With scratch memory from the caller, the CTAs of a slab claim
+// tiles from one counter per slab (atomicAdd, one tile ahead; a CTA's first tile needs no claim),
+// so a CTA that met cheap tiles or runs on a faster SM takes more; the last CTA to finish resets
+// the counters.  Without scratch, or when a CTA would own fewer than four tiles, CTA j of a slab
+// walks tiles j, j + G, j + 2G, ...  Either way neighbouring CTAs touch neighbouring rows at
+// about the same time, so the (W-1)-row halo of a tile is an L2 hit.
+//
+// Masks.  Every tile has a class: all of its mask rows are one (the maskless code runs), mixed, or
+// every tap of every row is masked.  A tile of the last class takes a ring slot but no bulk copy:
+// no byte of it is requested from HBM and the consumers store act(bias).  The classes come from
+// a pre-pass kernel (one byte per tile in scratch memory, copied to shared memory by every CTA)
+// or, without scratch, from the CTA's own prologue; the main kernel is launched as a programmatic
+// dependent of the pre-pass.  Mask values are looked at again only inside mixed tiles.
 //
 // Pipeline.  One producer warp and eight consumer warps share a ring of stages guarded by
-// full/done mbarriers.  The producer fetches the tile's mask rows two tiles ahead (32 lanes, a
-// few loads each) and classifies the tile: all rows valid, mixed, or nothing to read.  A tile
-// with nothing to read takes a ring slot but no bulk copy: no byte of it is requested from HBM
-// and the consumers store act(bias).  Bytes in flight are set by the ring
-// depth, not by registers.  Each consumer thread owns 8 bytes of channels and 8 consecutive
-// rows of the tile: a register window over shared memory rotated by index, fp32x2 FMAs, fused
-// mask / bias / SiLU / residual epilogue, streaming 8-byte stores (a warp writes 256 contiguous
-// bytes per row).  No consumer warp waits on HBM for its input, and none waits for another
-// warp: the only synchronisation is the pair of mbarriers per stage.
+// full/done mbarriers.  For every tile the producer writes a 32-byte descriptor (class, rows that
+// exist, 64-bit offset of the first output row, sequence, first row) next to the stage, so the
+// consumers do no index arithmetic.  Bytes in flight are set by the ring depth, not by registers.
+// Each consumer thread owns 8 bytes of channels and 8 consecutive rows of the tile: a register
+// window over shared memory rotated by index, packed fp32x2 FMAs, fused mask / bias / SiLU /
+// residual epilogue, streaming 8-byte stores predicated inside the instruction (a warp writes 256
+// contiguous bytes per row).  No consumer warp waits on HBM for its input, and none waits for
+// another warp: the only synchronisation is the pair of mbarriers per stage.
 //
 // Every mbarrier wait is bounded; on expiry the warp records the event in a device counter
 // (read by vc1d_tma_timeouts()) and leaves its loop.
