@@ -215,12 +215,65 @@ def causal_conv1d_fn_multi(xs, weight: torch.Tensor, bias: Optional[torch.Tensor
     return outs
 
 
+def _prefill_fast(x, weight, bias, activation, attention_mask, skip_masked_loads, residual, want_state, state_len):
+    """Cached-signature path of _prefill_forward for the calls a Canon layer makes (no initial state,
+    no preallocated outputs, no tuning overrides).  Returns (result, key); result is None when the
+    signature has not been validated yet."""
+    m = attention_mask
+    key = (x.shape, x.stride(), x.dtype, x.device.index, weight.shape, weight.stride(), weight.dtype,
+           None if bias is None else (bias.shape, bias.stride(), bias.dtype), activation,
+           None if m is None else (m.shape, m.stride(), m.dtype, m.device.index), bool(skip_masked_loads),
+           residual is True, want_state, state_len)
+    cache = getattr(_TLS, "prefill_args", None)
+    a = cache.get(key) if cache is not None else None
+    if a is None:
+        return None, key
+    out = torch.empty_like(x)
+    a.x = x.data_ptr()
+    a.y = out.data_ptr()
+    a.weight = weight.data_ptr()
+    a.bias = bias.data_ptr() if bias is not None else None
+    if m is not None:
+        a.mask = m.data_ptr()
+    if residual is True:
+        a.residual = a.x
+    final_states = None
+    if want_state:
+        final_states = torch.empty((x.shape[0], x.shape[1], a.state_len), dtype=x.dtype, device=x.device)
+        a.final_state = final_states.data_ptr()
+    dev = x.device
+    stream = _stream_handle(dev)
+    if _DYNAMIC_DEFAULT:
+        sc = _scheduler_scratch(dev, stream, 4096 + x.shape[0] * ((x.shape[2] + 31) // 32))
+        a.scratch = sc.data_ptr()
+        a.scratch_bytes = sc.numel() * 4
+    if dev.index != torch.cuda.current_device():
+        with torch.cuda.device(dev):
+            st = _cabi.lib.vc1d_prefill(C.byref(a), stream)
+    else:
+        st = _cabi.lib.vc1d_prefill(C.byref(a), stream)
+    if st != 0:
+        _cabi.check(st, "causal_conv1d_fn")
+    return ((out, final_states) if want_state else out), key
+
+
 def _prefill_forward(
     x, weight, bias=None, seq_idx=None, initial_states=None, return_final_states=False, final_states_out=None,
     activation=None, *, attention_mask=None, skip_masked_loads=True, residual=None, state_len=None, out=None,
     kernel=None, rows_per_thread=0, block_threads=0, unroll=0, tma=None, dynamic_schedule=None,
 ):
     """The forward launch behind causal_conv1d_fn (no autograd bookkeeping)."""
+    fast_key = None
+    plain = (seq_idx is None and initial_states is None and final_states_out is None and out is None
+             and kernel is None and tma is None and dynamic_schedule is None and rows_per_thread == 0
+             and block_threads == 0 and unroll == 0 and (residual is None or residual is True)
+             and x.is_cuda and weight.is_cuda)
+    if plain:
+        result, fast_key = _prefill_fast(x, weight, bias, activation, attention_mask, skip_masked_loads, residual,
+                                         bool(return_final_states), state_len)
+        if result is not None:
+            return result
+    weight_given, bias_given = weight, bias
     if x.dim() != 3:
         raise ValueError(f"Expected 3D input tensor (batch, dim, seqlen), got {x.dim()}D")
     batch, dim, seqlen = x.shape
@@ -332,6 +385,13 @@ def _prefill_forward(
     else:
         st = _cabi.lib.vc1d_prefill(C.byref(a), stream)
     _cabi.check(st, "causal_conv1d_fn")
+    if fast_key is not None and weight is weight_given and bias is bias_given:
+        # remember the validated struct for later calls with the same shapes, strides and options
+        cache = getattr(_TLS, "prefill_args", None)
+        if cache is None:
+            cache = _TLS.prefill_args = {}
+        if len(cache) < 256:
+            cache[fast_key] = a
     if return_final_states or final_states_out is not None:
         return out, final_states
     return out
