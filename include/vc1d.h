@@ -193,8 +193,16 @@ typedef struct vc1d_prefill_bwd_args {
     int32_t tma_stages;     /* tuning of the TMA-staged kernel: 0 = automatic */
     int32_t tma_ctas_per_sm;
     int32_t reserved;
-    void* scratch;          /* as in vc1d_prefill_args (only the counter region is used) */
+    void* scratch;          /* as in vc1d_prefill_args */
     int64_t scratch_bytes;
+    /* History of a chunked continuation (model/model.py:607-617), as in vc1d_prefill_args: the
+     * forward read its last width-1 columns instead of zeros left of t = 0.  dinitial_state, when
+     * given, receives the gradient for every column (zero for columns no tap reads).  Launches with
+     * an initial state take the generic kernel. */
+    const void* initial_state;  /* [batch, dim, init_len] contiguous, or NULL */
+    void* dinitial_state;       /* [batch, dim, init_len] contiguous, or NULL */
+    int32_t init_len;
+    int32_t reserved2;
 } vc1d_prefill_bwd_args;
 
 VC1D_API int vc1d_prefill_bwd(const vc1d_prefill_bwd_args* args, void* stream);

@@ -188,8 +188,6 @@ def test_autograd_residual_tensor_and_no_grad_path():
     with torch.no_grad():
         V.causal_conv1d_fn(x.transpose(1, 2), w, None, activation="silu")
     assert V.launch_count() == before + 1
-    with pytest.raises(NotImplementedError):
-        V.causal_conv1d_fn(x.transpose(1, 2), w, None, initial_states=torch.zeros(2, 128, 3, dtype=torch.bfloat16, device=DEV))
 
 
 def test_backward_bench_shape_properties():
@@ -288,3 +286,39 @@ def test_gradient_flows_through_two_decode_steps():
         numerical = numerical_grads(f, [x1, x2, st0, w])
     for a, n in zip(analytical, numerical):
         assert torch.allclose(a, n, atol=2e-2, rtol=2e-2), (a - n).abs().max().item()
+
+
+@pytest.mark.parametrize("W", [2, 4])
+def test_gradients_of_a_chunked_continuation(W):
+    """Two chunks handing a state over: gradients of the second chunk, including the one with
+    respect to the state it started from, against autograd over the whole sequence."""
+    g = torch.Generator().manual_seed(13)
+    B, D, T1, T2 = 2, 12, 9, 11
+    x = torch.randn(B, T1 + T2, D, generator=g, dtype=torch.float64)
+    w = torch.randn(D, W, generator=g, dtype=torch.float64)
+    b = torch.randn(D, generator=g, dtype=torch.float64)
+    coef = torch.randn(B, T2, D, generator=g, dtype=torch.float64)
+    # float64 reference: the second chunk's outputs as a function of the first chunk's inputs
+    xr = x.clone().requires_grad_(True)
+    wr, br = w.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    yr = torch.nn.functional.silu(torch.nn.functional.conv1d(
+        torch.nn.functional.pad(xr.transpose(1, 2), (W - 1, 0)), wr.unsqueeze(1), br, groups=D))
+    (yr[..., T1:].transpose(1, 2) * coef).sum().backward()
+    # kernels: state = last L columns of chunk 1, chunk 2 continues from it
+    L = W + 1
+    x2 = x[:, T1:].float().to(DEV).requires_grad_(True)
+    st = x[:, T1 - L:T1].transpose(1, 2).contiguous().float().to(DEV).requires_grad_(True)
+    wd, bd = w.float().to(DEV).requires_grad_(True), b.float().to(DEV).requires_grad_(True)
+    y2 = V.causal_conv1d_fn(x2.transpose(1, 2), wd, bd, activation="silu", initial_states=st)
+    assert V.last_kernel() in ("channel_last", "tma", "generic")
+    before = V.launch_count()
+    (y2.transpose(1, 2) * coef.float().to(DEV)).sum().backward()
+    assert V.launch_count() == before + 1  # (the backward runs on an autograd thread: last_kernel() is per thread)
+    assert torch.allclose(x2.grad.cpu().double(), xr.grad[:, T1:], rtol=1e-4, atol=1e-4)
+    ref_dst = xr.grad[:, T1 - L:T1].transpose(1, 2)
+    assert torch.allclose(st.grad.cpu().double(), ref_dst, rtol=1e-4, atol=1e-4)
+    assert bool((st.grad[..., : L - (W - 1)] == 0).all())
+    # parameter gradients of chunk 2 alone equal the whole-sequence ones because the loss only
+    # looks at chunk 2
+    assert torch.allclose(wd.grad.cpu().double(), wr.grad, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(bd.grad.cpu().double(), br.grad, rtol=1e-4, atol=1e-4)

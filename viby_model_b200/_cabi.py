@@ -123,6 +123,10 @@ class PrefillBwdArgs(C.Structure):
         ("reserved", C.c_int32),
         ("scratch", C.c_void_p),
         ("scratch_bytes", C.c_int64),
+        ("initial_state", C.c_void_p),
+        ("dinitial_state", C.c_void_p),
+        ("init_len", C.c_int32),
+        ("reserved2", C.c_int32),
     ]
 
 

@@ -25,6 +25,8 @@ struct BGParams {
     const void* weight;
     const void* bias;
     const void* mask;
+    const void* init;   // [B, D, init_len] history, or NULL
+    void* dinit;        // its gradient, or NULL
     float* dweight;
     float* dbias;
     long long sxb, sxd, sxt;  // elements
@@ -38,6 +40,7 @@ struct BGParams {
     int mask_dtype;
     int residual;
     int n_chunks;
+    int init_len;
 };
 
 // MODE 0: expf and an IEEE division (fp32 I/O); 1: ex2.approx + rcp.approx (fp16 I/O);
@@ -94,7 +97,11 @@ __global__ void __launch_bounds__(128) k_prefill_bwd_generic(const BGParams p) {
 
         auto masked_x = [&](int t, float& mk) -> float {
             mk = 1.f;
-            if (t < 0 || t >= p.T) return 0.f;
+            if (t < 0) {  // history of a chunked continuation, already masked when it was stored
+                if (p.init == nullptr || p.init_len + t < 0) return 0.f;
+                return E::to_float(reinterpret_cast<const T*>(p.init)[(b * p.D + d) * p.init_len + (p.init_len + t)]);
+            }
+            if (t >= p.T) return 0.f;
             if (p.mask != nullptr) mk = load_mask(p.mask, b * p.smb + (long long)t * p.smt, p.mask_dtype);
             if (mk == 0.f) return 0.f;
             float v = E::to_float(x[b * p.sxb + (long long)d * p.sxd + (long long)t * p.sxt]);
@@ -102,6 +109,10 @@ __global__ void __launch_bounds__(128) k_prefill_bwd_generic(const BGParams p) {
             return v;
         };
 
+        if (c0 == 0 && p.dinit != nullptr) {  // history columns that no tap reads get no gradient
+            T* drow = reinterpret_cast<T*>(p.dinit) + (b * p.D + d) * p.init_len;
+            for (int col = 0; col < p.init_len - H; ++col) drow[col] = E::from_float(0.f);
+        }
         // xw[3] is xm[j], xw[2] xm[j-1], ...; gw likewise for g
         float xw[4] = {0.f, 0.f, 0.f, 0.f};
         float gw[4] = {0.f, 0.f, 0.f, 0.f};
@@ -128,6 +139,12 @@ __global__ void __launch_bounds__(128) k_prefill_bwd_generic(const BGParams p) {
                 db += g;
             }
             const int t = j - H;
+            if (t < 0 && c0 == 0 && p.dinit != nullptr && p.init_len + t >= 0) {
+                // gradient of the history rows: the taps of the first W-1 outputs that reached back
+                float acc = 0.f;
+                for (int w = 0; w < W; ++w) acc = fmaf(wt[w], gw[3 - w], acc);
+                reinterpret_cast<T*>(p.dinit)[(b * p.D + d) * p.init_len + (p.init_len + t)] = E::from_float(acc);
+            }
             if (t >= c0) {  // t < c1 holds by the loop bound
                 float acc = 0.f;
                 for (int w = 0; w < W; ++w) acc = fmaf(wt[w], gw[3 - w], acc);
@@ -148,6 +165,7 @@ cudaError_t launch_prefill_bwd_generic(const vc1d_prefill_bwd_args& a, cudaStrea
     BGParams p;
     p.x = a.x; p.dy = a.dy; p.dx = a.dx;
     p.weight = a.weight; p.bias = a.bias; p.mask = a.mask;
+    p.init = a.initial_state; p.dinit = a.dinitial_state; p.init_len = a.init_len;
     p.dweight = a.dweight; p.dbias = a.dbias;
     p.sxb = a.x_stride_b; p.sxd = a.x_stride_d; p.sxt = a.x_stride_t;
     p.sgb = a.dy_stride_b; p.sgd = a.dy_stride_d; p.sgt = a.dy_stride_t;

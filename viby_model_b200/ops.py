@@ -158,7 +158,7 @@ def causal_conv1d_fn(
 
     Differentiable in ``x``, ``weight``, ``bias`` and a separate ``residual`` tensor (the contract of
     causal-conv1d-mps autograd.py:116-151, 305-338): when any of them requires grad the backward
-    pass runs ``causal_conv1d_bwd``.  ``initial_states`` and ``out=`` are forward-only.
+    pass runs ``causal_conv1d_bwd`` (``initial_states`` receives a gradient too).  ``out=`` is forward-only.
     """
     if torch.compiler.is_compiling():
         # inside torch.compile the operator is one opaque graph node (compile_ops.py)
@@ -176,6 +176,7 @@ def causal_conv1d_fn(
     needs_grad = torch.is_grad_enabled() and (
         x.requires_grad or weight.requires_grad or (bias is not None and bias.requires_grad)
         or (isinstance(residual, torch.Tensor) and residual.requires_grad)
+        or (initial_states is not None and initial_states.requires_grad)
     )
     kw = dict(attention_mask=attention_mask, skip_masked_loads=skip_masked_loads, residual=residual,
               state_len=state_len, out=out, kernel=kernel, rows_per_thread=rows_per_thread,
@@ -185,11 +186,10 @@ def causal_conv1d_fn(
                                 activation, **kw)
     if out is not None:
         raise ValueError("out= cannot be used when a gradient is required")
-    if initial_states is not None:
-        raise NotImplementedError("backward with initial_states is not supported")
     res_tensor = residual if isinstance(residual, torch.Tensor) else None
     result = _CausalConv1dFunction.apply(x, weight, bias, res_tensor, activation, attention_mask,
-                                         residual is True, return_final_states, final_states_out, kw)
+                                         residual is True, return_final_states, final_states_out, kw,
+                                         initial_states)
     return result if (return_final_states or final_states_out is not None) else result[0]
 
 
@@ -406,11 +406,12 @@ def causal_conv1d_bwd(
     *,
     attention_mask: Optional[torch.Tensor] = None,
     residual: bool = False,
+    initial_states: Optional[torch.Tensor] = None,
     need_dweight: bool = True,
     need_dbias: bool = True,
     kernel: Optional[str] = None,
     dynamic_schedule: Optional[bool] = None,
-) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
+):
     """Gradients of ``causal_conv1d_fn`` (with its fused mask / residual) for ``x[batch, dim, seqlen]``
     and the upstream gradient ``dy`` of the same shape: returns ``(dx, dweight, dbias)``.
 
@@ -418,6 +419,8 @@ def causal_conv1d_bwd(
     fp32 and returned in fp32 (the caller casts), as the reference's backward does
     (causal-conv1d-mps/causal_conv1d_mps/causal_conv1d_kernel.mm:553-557, 771-776).
     ``residual=True`` means the forward added ``x`` to its output.  Formulas: include/vc1d.h.
+    With ``initial_states[batch, dim, >=width-1]`` (the history of a chunked continuation) a fourth
+    result is returned: the gradient with respect to it.
     """
     if x.dim() != 3:
         raise ValueError(f"Expected 3D input tensor (batch, dim, seqlen), got {x.dim()}D")
@@ -467,6 +470,21 @@ def causal_conv1d_bwd(
     a.residual = 1 if residual else 0
     a.dweight = dweight.data_ptr() if dweight is not None else None
     a.dbias = dbias.data_ptr() if dbias is not None else None
+    dinit = None
+    if initial_states is not None:
+        s0 = initial_states
+        if s0.dim() != 3 or s0.shape[0] != batch or s0.shape[1] != dim or s0.shape[2] < width - 1:
+            raise ValueError(
+                f"initial_states shape {tuple(s0.shape)} does not match (batch, dim, >=width-1) = "
+                f"({batch}, {dim}, >={width - 1})"
+            )
+        if s0.dtype != x.dtype or s0.device != x.device:
+            raise ValueError("initial_states must match x in dtype and device")
+        s0 = s0.contiguous()
+        dinit = torch.empty_like(s0)
+        a.initial_state = s0.data_ptr()
+        a.dinitial_state = dinit.data_ptr()
+        a.init_len = s0.shape[2]
     if kernel not in (None, "auto", "generic", "tma"):
         raise ValueError(f"unknown backward kernel {kernel!r}")
     a.kernel = _cabi.KERNEL_BY_NAME[kernel]
@@ -481,6 +499,8 @@ def causal_conv1d_bwd(
     else:
         st = _cabi.lib.vc1d_prefill_bwd(C.byref(a), stream)
     _cabi.check(st, "causal_conv1d_bwd")
+    if initial_states is not None:
+        return dx, dweight, dbias, dinit
     return dx, dweight, dbias
 
 
@@ -490,13 +510,16 @@ class _CausalConv1dFunction(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, weight, bias, res_tensor, activation, attention_mask, residual_is_x, return_final_states,
-                final_states_out, kw):
+                final_states_out, kw, initial_states):
         kw = dict(kw)
         kw["residual"] = True if residual_is_x else res_tensor
-        result = _prefill_forward(x, weight, bias, None, None, return_final_states, final_states_out, activation, **kw)
+        result = _prefill_forward(x, weight, bias, None, initial_states, return_final_states, final_states_out,
+                                  activation, **kw)
         y, state = result if isinstance(result, tuple) else (result, None)
         ctx.save_for_backward(x, weight, bias if bias is not None else x.new_empty(0),
-                              attention_mask if attention_mask is not None else x.new_empty(0))
+                              attention_mask if attention_mask is not None else x.new_empty(0),
+                              initial_states if initial_states is not None else x.new_empty(0))
+        ctx.has_init = initial_states is not None
         ctx.has_bias = bias is not None
         ctx.has_mask = attention_mask is not None
         ctx.activation = activation
@@ -509,19 +532,23 @@ class _CausalConv1dFunction(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy, _dstate):
-        x, weight, bias, mask = ctx.saved_tensors
+        x, weight, bias, mask, init = ctx.saved_tensors
         need_x, need_w, need_b = ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[2]
-        dx, dw, db = causal_conv1d_bwd(
+        grads = causal_conv1d_bwd(
             x, weight, bias if ctx.has_bias else None, dy, ctx.activation,
             attention_mask=mask if ctx.has_mask else None, residual=ctx.residual_is_x,
+            initial_states=init if ctx.has_init else None,
             need_dweight=need_w, need_dbias=need_b and ctx.has_bias,
         )
+        dx, dw, db = grads[0], grads[1], grads[2]
+        dinit = grads[3] if ctx.has_init else None
         return (
             dx if need_x else None,
             dw.to(weight.dtype) if (need_w and dw is not None) else None,
             db.to(bias.dtype) if (need_b and db is not None) else None,
             dy if (ctx.has_res_tensor and ctx.needs_input_grad[3]) else None,
             None, None, None, None, None, None,
+            dinit if (ctx.has_init and ctx.needs_input_grad[10]) else None,
         )
 
 
