@@ -291,16 +291,19 @@ VC1D_API uint32_t vc1d_sizeof_update_args(void);
 /* Name of a return code: VC1D_E_* or a cudaError_t.  Never NULL; static storage. */
 VC1D_API const char* vc1d_status_string(int status);
 
-/* Number of kernel launches this process has made through the library (all threads).
+/* Number of kernel launches this process has made through the library (all threads; the tile
+ * classification pre-pass of a masked launch counts as a launch of its own).
  * The reference swallows kernel exceptions and silently falls back
  * (model/model.py:314-317, 492-495); callers use this to prove the kernels ran. */
 VC1D_API uint64_t vc1d_launch_count(void);
 
-/* Name of the kernel the most recent launcher call on this thread selected
- * ("channel_last", "time_major", "generic", "tma", "update_vec", "update_generic"). */
+/* Name of the kernel the most recent launcher call on this thread selected ("channel_last",
+ * "time_major", "generic", "tma", "update_vec", "update_generic", "bwd_tma", "bwd_generic",
+ * "update_bwd").  Per host thread: a backward pass run by an autograd worker thread does not show
+ * up in the thread that called the forward. */
 VC1D_API const char* vc1d_last_kernel(void);
 
-/* Number of bounded mbarrier waits that expired inside the TMA prefill kernel since the process
+/* Number of bounded mbarrier waits that expired inside the TMA-staged kernels since the process
  * started (0 in a healthy run; a CTA whose wait expires abandons its remaining tiles).  Reads a
  * device counter with a synchronising copy: call it after the stream has been synchronised. */
 VC1D_API unsigned int vc1d_tma_timeouts(void);
