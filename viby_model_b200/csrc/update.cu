@@ -36,7 +36,7 @@ struct UParams {
 };
 
 template <int DT, int W, int L>
-__global__ void __launch_bounds__(256) k_update_vec(const UParams p) {
+__global__ void __launch_bounds__(256, 2) k_update_vec(const UParams p) {
     using E = Elem<DT>;
     using T = typename E::type;
     using PK = Pack<DT>;
