@@ -129,6 +129,9 @@ __device__ __forceinline__ float lds_f32(uint32_t a) {
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
     return v;
 }
+__device__ __forceinline__ void sts_f32(uint32_t a, float v) {
+    asm volatile("st.volatile.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory");
+}
 __device__ __forceinline__ int lds_s32(uint32_t a) {
     int v;
     asm volatile("ld.volatile.shared.s32 %0, [%1];" : "=r"(v) : "r"(a));
@@ -171,12 +174,15 @@ struct Geometry {
     static constexpr int kRowBytes = SLAB_BYTES;
     static constexpr int kSlabElems = SLAB_BYTES / Elem<DT>::kBytes;
     static constexpr int kStageBytes = ((kBoxRows * kRowBytes + 127) / 128) * 128;
-    // layout for S stages: stages | full[S], done[S] | tile descriptor[S] | class table (one byte per tile)
+    // layout for S stages: stages | full[S], done[S] | tile descriptor[S] | mask values[S] | class table (one byte per tile)
     // tile descriptor, 32 bytes: {class, rows of the tile that exist, byte offset of its first output
     // row (64 bits)} {sequence, first row, -, -}
     __host__ __device__ static constexpr int off_bars(int S) { return S * kStageBytes; }
     __host__ __device__ static constexpr int off_flags(int S) { return off_bars(S) + 2 * S * 8; }
-    __host__ __device__ static constexpr int off_table(int S) { return off_flags(S) + S * 32; }
+    // mask values of a mixed tile's box rows, one float per row, written by the producer
+    static constexpr int kMaskBytes = ((kBoxRows + 31) / 32) * 32 * 4;
+    __host__ __device__ static constexpr int off_mvals(int S) { return off_flags(S) + S * 32; }
+    __host__ __device__ static constexpr int off_table(int S) { return off_mvals(S) + S * kMaskBytes; }
     __host__ __device__ static constexpr int smem_bytes(int S, int table_bytes) {
         return off_table(S) + table_bytes + 128 /* base alignment slack */;
     }
@@ -378,6 +384,7 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
     const int kStages = p.stages;  // ring depth of this launch
     const uint32_t bars = base + G::off_bars(kStages);    // full[s] at bars + 8 s, done[s] at bars + 8 (kStages + s)
     const uint32_t flags = base + G::off_flags(kStages);  // per stage: 32-byte tile descriptor
+    const uint32_t mvals = base + G::off_mvals(kStages);  // per stage: mask value of every box row (mixed tiles)
     const uint32_t table = base + G::off_table(kStages);  // class of each of this CTA's tiles (masked launches)
 
     const int warp = threadIdx.x >> 5;
@@ -487,8 +494,17 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
             return lds_u8(table + i);
         };
         // announce a tile in the next ring slot and start its copy
-        auto put_tile = [&](int b, int t0, int cls) {
+        auto fetch_mask = [&](int b, int t0, float (&mv)[NMK]) {
+#pragma unroll
+            for (int k = 0; k < NMK; ++k) mv[k] = tile_mask(p, (long long)b * p.smb, t0 - H + lane + 32 * k);
+        };
+        auto put_tile = [&](int b, int t0, int cls, const float (&mv)[NMK]) {
             const int s = s_ring;
+            if (cls == TILE_MIXED) {
+#pragma unroll
+                for (int k = 0; k < NMK; ++k) sts_f32(mvals + s * G::kMaskBytes + (lane + 32 * k) * 4, mv[k]);
+                __syncwarp();  // lane 0's arrive below publishes the whole warp's stores
+            }
             if (lane == 0) {
                 const long long yoff = (long long)b * p.syb + (long long)t0 * p.syt;
                 sts_desc(flags + 32 * s, cls, p.T - t0, yoff);
@@ -506,23 +522,31 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         };
         // One claim ahead: the next tile and its class are fetched while the current tile waits for
         // its ring slot.  (Claiming further ahead was measured slower: the tiles in flight spread out
-        // in memory and the tail of the launch gets longer.)
+        // in memory and the tail of the launch gets longer.)  The mask rows of a mixed tile are
+        // fetched at the same time and travel to the consumers with the tile.
         bool live = true;
         int rt = next_tile(), b = 0, t0 = 0, cls = TILE_FULL;
+        float mv[NMK], mv_now[NMK];
+#pragma unroll
+        for (int k = 0; k < NMK; ++k) mv[k] = 1.0f;
         if (rt >= 0) {
             locate(rt, b, t0);
             cls = tile_class(0, b, t0);
+            if (cls == TILE_MIXED) fetch_mask(b, t0, mv);
         }
         for (int i = 0; live && rt >= 0; ++i) {
             const int b_now = b, t0_now = t0, cls_now = cls;
+#pragma unroll
+            for (int k = 0; k < NMK; ++k) mv_now[k] = mv[k];
             rt = next_tile();
             if (rt >= 0) {
                 locate(rt, b, t0);
                 cls = tile_class(i + 1, b, t0);
+                if (cls == TILE_MIXED) fetch_mask(b, t0, mv);
             }
             live = claim();
             if (!live) break;
-            put_tile(b_now, t0_now, cls_now);
+            put_tile(b_now, t0_now, cls_now, mv_now);
             advance();
         }
         // Every tile of this CTA is on its way: a dependent launch of the stream may now take the slots
@@ -644,7 +668,7 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
                 float mkv = 1.0f;
                 if (mixed) {
                     const int j = lane & (GL - 1);
-                    if (j < R + H) mkv = tile_mask(p, (long long)b * p.smb, tfirst - H + j);
+                    if (j < R + H) mkv = lds_f32(mvals + s * G::kMaskBytes + (rbase + j) * 4);  // box row rbase + j
 #pragma unroll
                     for (int w = 0; w < H; ++w)
                         apply_mask<DT, VB>(hist[w], __shfl_sync(0xffffffffu, mkv, msrc + w), p.skip);
