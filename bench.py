@@ -267,6 +267,9 @@ def main():
         result_out = sys.stdout
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
+    # one process per GPU: keep this rank's pinned buffers and copy threads on the GPU's NUMA node
+    from viby_model_b200.host_io import bind_to_gpu_numa_node
+    numa_node = bind_to_gpu_numa_node(local_rank) if world > 1 else None
 
     def barrier():
         torch.cuda.synchronize(dev)
@@ -422,6 +425,7 @@ def main():
             "ms_per_step": e2e_ms,
             "steps": e2e_steps,
             "matches_device_result": e2e_ok,
+            "numa_node": numa_node,
             "note": "rows behind each sequence's last valid position are never read by the kernel and are not sent",
         },
         "e2e_all_rows_sent": {

@@ -20,6 +20,44 @@ import torch
 from .ops import causal_conv1d_fn
 
 
+def bind_to_gpu_numa_node(device_index: int) -> Optional[int]:
+    """Pin the calling process to the CPUs of the NUMA node the GPU hangs off, so that pinned host
+    buffers allocated afterwards (first touch) and the copy threads sit next to its PCIe root.
+    With one process per GPU on a multi-socket host this keeps host<->device copies off the
+    inter-socket link.  Returns the node, or None when the topology cannot be read (nothing is
+    changed then)."""
+    import os
+
+    try:
+        props = torch.cuda.get_device_properties(device_index)
+        if hasattr(props, "pci_bus_id"):
+            bus = f"{getattr(props, 'pci_domain_id', 0):04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        else:
+            import pynvml
+
+            pynvml.nvmlInit()
+            uuid = str(props.uuid)
+            h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+            bus = pynvml.nvmlDeviceGetPciInfo(h).busId
+            bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()[-12:]
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
 class HostPrefill:
     def __init__(self, batch: int, seqlen: int, dim: int, dtype: torch.dtype, device="cuda",
                  chunk_batch: int = 4, masked: bool = True, mask_dtype: torch.dtype = torch.int64,
