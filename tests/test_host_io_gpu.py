@@ -68,3 +68,19 @@ def test_host_prefill_pipelines_consecutive_batches():
     torch.cuda.synchronize()
     for (x, _, _, m), y in zip(batches, outs):
         assert torch.equal(y.to(DEV), direct(x, w, b, m))
+
+
+def test_host_prefill_sending_all_rows_gives_the_same_result():
+    B, T, D = 4, 256, 512
+    x, w, b, m = make(B, T, D, 4, torch.bfloat16, seed=9)
+    outs = []
+    for send_all in (False, True):
+        pipe = HostPrefill(B, T, D, torch.bfloat16, device=DEV, chunk_batch=2, mask_dtype=torch.bool,
+                           send_masked_rows=send_all)
+        y = torch.empty_like(x).pin_memory()
+        pipe.run(x, w, b, "silu", m, y)
+        torch.cuda.synchronize()
+        outs.append(y.clone())
+        assert pipe.h2d_bytes == ((B * T * D * 2 + B * T) if send_all else
+                                  (sum(HostPrefill.valid_prefix_lengths(m)) * D * 2 + B * T))
+    assert torch.equal(outs[0], outs[1])
