@@ -45,7 +45,8 @@ def prefill_bwd(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tens
                 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     dx, dw, db = ops.causal_conv1d_bwd(x, weight, bias, dy, _ACT[activation], attention_mask=mask,
                                        residual=residual_is_x)
-    return dx, dw, db if db is not None else x.new_empty(0, dtype=torch.float32)
+    # the eager op returns dweight and dbias as views of one buffer; outputs of a custom op must not alias
+    return dx, dw.clone(), db.clone() if db is not None else x.new_empty(0, dtype=torch.float32)
 
 
 @prefill_bwd.register_fake

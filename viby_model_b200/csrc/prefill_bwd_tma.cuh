@@ -143,6 +143,9 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES>::kThreads, BwdG
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // launched as a programmatic dependent of the tile-classification pre-pass when there is one:
+    // nothing above touched global memory
+    griddep_wait();
     __syncthreads();
 
     if (warp == G::kConsumerWarps) {
@@ -527,10 +530,19 @@ cudaError_t launch_bwd_kernel(const vc1d_prefill_bwd_args& a, const BwdParams& b
             p.gtable = tab;
         }
     }
-    const dim3 grid((unsigned)n_slab, (unsigned)g);
     note_launch("bwd_tma");
-    k_prefill_bwd_tma<DT, W, SLAB_BYTES, ACT><<<grid, G::kThreads, smem, s>>>(tmap_x, tmap_g, p);
-    return cudaGetLastError();
+    // after a pre-pass the main kernel is its programmatic dependent: its launch and prologue overlap it
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = (pdl_enabled() && p.gtable != nullptr) ? 1 : 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)n_slab, (unsigned)g);
+    cfg.blockDim = dim3(G::kThreads);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, k_prefill_bwd_tma<DT, W, SLAB_BYTES, ACT>, tmap_x, tmap_g, p);
 }
 
 template <int DT, int W>
