@@ -8,26 +8,33 @@ tokens x 3456 channels, bf16, width 4, bias, SiLU, right-padded with valid lengt
 [128, 1024] and the attention mask applied inside the kernel (synthetic, seeded).  With N > 1
 (launched by torch.distributed.run, one process per GPU) every rank runs its own 32 sequences
 -- weak scaling, sharded by sequence, no collective on the data path; NCCL is used only for
-the barrier around the timed region and the max-over-ranks of the device time.
+the barrier around the timed regions and the reductions of the device times.
 
 The single JSON line printed by rank 0 carries:
   value / ms_per_step   padded tokens per second over all ranks, inputs resident in HBM, timed
-                        with CUDA events on the launching stream;
+                        with CUDA events on the launching stream (K steps per round, several
+                        rounds back to back, the median round reported; max over ranks);
   e2e                   the same metric through HostPrefill: pinned host input, host-to-device
-                        copy, kernel, device-to-host copy of the result, every step;
+                        copy, kernel, device-to-host copy of the result, every step; with the
+                        plain copy rate of the same bytes over the same link beside it;
   roofline              algorithmic HBM bytes of one launch / its average duration, against the
                         measured copy bandwidth of this GPU pool;
+  ragged_sweep          the ragged large-batch configuration (512 sequences, up to 4096 tokens,
+                        lengths log-uniform) sharded over the N ranks -- strong scaling;
+  shapes                the Canon A/B/C/D shapes of the whole-model configuration and a dense batch;
+  backward, decode, model_decode_step
+                        gradient kernel of the step; the decode configuration as a CUDA graph,
+                        bandwidth-bound decode shapes; the 72 decode calls of one model step;
   cpu_baseline          the reference's CPU arithmetic for the same workload on the host cores;
-  decode                the decode configuration (batch 256, dim 960, state 3, 1024 steps) as a
-                        CUDA graph, and a decode shape large enough to be bandwidth-bound;
   clocks                SM clock and throttle reasons sampled while the timed regions ran.
 
---impl reference times only the CPU path (the reference has no CUDA kernel of its own for this
-operator and its Metal kernels cannot run here).
+--impl reference times only the CPU path, in a process that never loads the CUDA library (the
+reference has no CUDA kernel of its own for this operator and its Metal kernels cannot run here).
 """
 from __future__ import annotations
 
 import argparse
+import importlib.util
 import json
 import os
 import statistics
@@ -39,7 +46,6 @@ from pathlib import Path
 import torch
 
 ROOT = Path(__file__).resolve().parent
-sys.path.insert(0, str(ROOT))
 
 METRIC = "prefill_tokens_per_s"
 UNIT = "tokens/s"
@@ -47,6 +53,16 @@ UNIT = "tokens/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
 # capture summarised under profiles/ (None until a capture of the current kernel exists).
 NCU_TRAFFIC_BYTES = {"canon_d_prefill_bf16": 320_200_000}
+
+
+def load_workloads():
+    """The seeded input generators, loaded by file path: importing the package would load the CUDA
+    library, which the reference arm must not do."""
+    spec = importlib.util.spec_from_file_location("vc1d_workloads", ROOT / "viby_model_b200" / "workloads.py")
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["vc1d_workloads"] = mod  # dataclasses look their module up by name
+    spec.loader.exec_module(mod)
+    return mod
 
 
 def measured_peak_gbs():
@@ -143,46 +159,82 @@ def cpu_reference_step(x_btd, weight, bias, mask):
     return F.silu(y)
 
 
-def time_cpu_reference(cfg, rows, steps, warmup):
-    from viby_model_b200 import workloads as WL
+def find_reference_tree():
+    """A checkout of the reference, where one exists on this machine (never on the GPU boxes)."""
+    for cand in (os.environ.get("VIBY_REFERENCE"), "/root/reference", str(ROOT / "baseline" / "_ref")):
+        if cand and (Path(cand) / "model" / "model.py").exists():
+            return Path(cand)
+    return None
 
+
+def reference_canon_layer(tree: Path, cfg, weight, bias):
+    """The reference's own CanonLayer (model/model.py:201-675), imported unmodified with both optional
+    kernel packages made unimportable, so that its forward takes the PyTorch branch (:587-675)."""
+    sys.modules["causal_conv1d"] = None      # model/model.py:20-30 then sets HAS_CAUSAL_CONV1D_CUDA = False
+    sys.modules["causal_conv1d_mps"] = None  # model/model.py:12-18
+    sys.dont_write_bytecode = True
+    sys.path.insert(0, str(tree))
+    from model.model import CanonLayer, VibyConfig  # noqa: E402
+
+    conf = VibyConfig(canon_bias=bias is not None, canon_activation=cfg.activation is not None,
+                      canon_kernel=cfg.width)
+    layer = CanonLayer(cfg.dim, conf, "d").to(cfg.dtype)
+    with torch.no_grad():
+        layer.weight.copy_(weight.unsqueeze(1))
+        if bias is not None:
+            layer.bias_param.copy_(bias)
+    return layer.eval()
+
+
+def time_cpu_reference(WL, cfg, rows, steps, warmup, want_tree=True):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     x = WL.prefill_inputs(cfg, rows)
     m = WL.attention_mask(cfg, rows, dtype=torch.bool)
     w, b = WL.weights(cfg.cfg, cfg.dim, cfg.width, cfg.dtype)
+    kind, step = "port", (lambda: cpu_reference_step(x, w, b, m))
+    tree = find_reference_tree() if want_tree else None
+    if tree is not None:
+        try:
+            layer = reference_canon_layer(tree, cfg, w, b)
+            kind, step = "reference", (lambda: layer(x, attention_mask=m))
+        except Exception as e:  # an incomplete tree: fall back to the restated calls
+            print(f"reference tree at {tree} not usable ({type(e).__name__}: {e}); timing the port", file=sys.stderr)
     with torch.no_grad():
         for _ in range(warmup):
-            cpu_reference_step(x, w, b, m)
+            step()
         times = []
         for _ in range(steps):
             t0 = time.perf_counter()
-            cpu_reference_step(x, w, b, m)
+            step()
             times.append(time.perf_counter() - t0)
     tokens = len(rows) * cfg.seqlen
-    return tokens, times, cores
+    return tokens, times, cores, kind
 
 
 def run_reference_arm(args):
-    """--impl reference: the reference's own CPU arithmetic on the host cores; rank 0 only."""
-    from viby_model_b200 import workloads as WL
-
+    """--impl reference: the reference's own CPU code path on the host cores, one process (rank 0)
+    whatever N is.  Nothing of viby_model_b200 is imported, so no CUDA library is loaded."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    WL = load_workloads()
     cfg = WL.CANON_D_PREFILL
     rows = list(range(8))  # bounded sample: 8 of the 32 sequences per step
-    steps, warmup = max(1, args.steps), max(1, min(args.warmup, 3))
-    tokens, times, cores = time_cpu_reference(cfg, rows, min(steps, 10), warmup)
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    tokens, times, cores, kind = time_cpu_reference(WL, cfg, rows, steps, warmup)
     mean_s = sum(times) / len(times)
     value = tokens / mean_s
+    what = ("the reference's CanonLayer.forward, PyTorch branch (model/model.py:587-675), imported unmodified"
+            if kind == "reference" else
+            "the reference's CPU arithmetic restated in torch (model/model.py:590-620, 664-670): no reference tree on this machine")
     line = {
         "impl": "reference",
         "metric": METRIC,
         "value": value,
         "unit": UNIT,
         "n_gpus": args.gpus,
-        "steps": len(times),
+        "steps": steps,
         "warmup": warmup,
         "ms_per_step": mean_s * 1e3,
         "higher_is_better": True,
@@ -195,8 +247,11 @@ def run_reference_arm(args):
             "value": value,
             "unit": UNIT,
             "cores": cores,
-            "kind": "port",
-            "sample": f"{len(rows)} of {cfg.batch} sequences x {cfg.seqlen} tokens per step, mean of {len(times)} steps",
+            "kind": kind,
+            "what": what,
+            "processes": 1,
+            "sample": f"{len(rows)} of {cfg.batch} sequences x {cfg.seqlen} tokens per step, mean of {steps} steps; "
+                      f"one host process on rank 0 at every N",
         },
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -224,6 +279,57 @@ def workload_config(cfg, n_gpus):
 # --------------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------------
+class Ctx:
+    """What every section of the GPU arm needs: the device, the rank layout and the reductions."""
+
+    def __init__(self, V, WL, dev, rank, world):
+        import torch.distributed as dist
+
+        self.V, self.WL, self.dev, self.rank, self.world, self.dist = V, WL, dev, rank, world, dist
+        self.peak, self.peak_kind = measured_peak_gbs()
+
+    def barrier(self):
+        torch.cuda.synchronize(self.dev)
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize(self.dev)
+
+    def gather(self, v: float):
+        """The value of every rank, in rank order."""
+        if self.world == 1:
+            return [float(v)]
+        t = torch.tensor([float(v)], dtype=torch.float64, device=self.dev)
+        out = [torch.empty_like(t) for _ in range(self.world)]
+        self.dist.all_gather(out, t)
+        return [float(o.item()) for o in out]
+
+    def max_over_ranks(self, v: float) -> float:
+        return max(self.gather(v))
+
+    def sum_over_ranks(self, v: float) -> float:
+        return sum(self.gather(v))
+
+    def time_loop(self, fn, steps, warmup=3):
+        """steps calls of fn between two events on the current stream, barriers on both sides.
+        Returns (this rank's ms for all steps, host seconds the loop took to enqueue)."""
+        for _ in range(warmup):
+            fn()
+        self.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            fn()
+        host_s = time.perf_counter() - t0
+        e1.record()
+        self.barrier()
+        return e0.elapsed_time(e1), host_s
+
+
+def spread(values):
+    return {"min": min(values), "median": statistics.median(values), "max": max(values)}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -231,22 +337,29 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kernel", default=None, help="force a prefill kernel (channel_last | tma)")
+    ap.add_argument("--rounds", type=int, default=5, help="timed rounds of --steps steps each; the median is reported")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-backward", action="store_true")
-    ap.add_argument("--decode-saturating-only", action="store_true",
-                    help="run only the bandwidth-bound decode shape and print its figures (for profiling)")
+    ap.add_argument("--no-ragged", action="store_true")
+    ap.add_argument("--no-shapes", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--only", default=None, choices=["headline", "decode_saturating", "ragged", "backward"],
+                    help="run one section and print its figures (for profiling: few launches, small footprint)")
+    ap.add_argument("--state-len", type=int, default=3, help="state length of --only decode_saturating")
+    ap.add_argument("--circular", action="store_true", help="circular state for --only decode_saturating")
     args = ap.parse_args()
 
     if args.impl == "reference":
         run_reference_arm(args)
         return
 
+    sys.path.insert(0, str(ROOT))
     import torch.distributed as dist
 
     import viby_model_b200 as V
     from viby_model_b200 import workloads as WL
-    from viby_model_b200.host_io import HostPrefill
+    from viby_model_b200.host_io import NUMA_STATUS, HostPrefill, bind_to_gpu_numa_node
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -265,38 +378,25 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     else:
         result_out = sys.stdout
+    ctx = Ctx(V, WL, dev, rank, world)
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
     # one process per GPU: keep this rank's pinned buffers and copy threads on the GPU's NUMA node
-    from viby_model_b200.host_io import bind_to_gpu_numa_node
     numa_node = bind_to_gpu_numa_node(local_rank) if world > 1 else None
+    numa_note = NUMA_STATUS.get(local_rank, "one process: not bound")
 
-    def barrier():
-        torch.cuda.synchronize(dev)
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-
-    def max_over_ranks(v: float) -> float:
-        if world == 1:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    def sum_over_ranks(v: float) -> float:
-        if world == 1:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return float(t.item())
-
-    if args.decode_saturating_only:
-        res = bench_decode_saturating(V, WL, dev, world, barrier, max_over_ranks)
+    def emit(obj):
         if rank == 0:
-            print(json.dumps({"decode_saturating": res}), file=result_out, flush=True)
+            print(json.dumps(obj), file=result_out, flush=True)
         if world > 1:
             dist.destroy_process_group()
+
+    if args.only == "decode_saturating":
+        emit({"decode_saturating": bench_decode_saturating(ctx, args.state_len, circular=args.circular,
+                                                           steps=min(steps, 20))})
+        return
+    if args.only == "ragged":
+        emit({"ragged_sweep": bench_ragged(ctx, steps=min(steps, 10))})
         return
 
     # ---- workload: this rank's 32 sequences ---------------------------------------------------
@@ -317,68 +417,61 @@ def main():
     def step():
         V.causal_conv1d_fn(xv, w, b, activation=cfg.activation, attention_mask=m, out=yv, kernel=args.kernel)
 
-    sampler = ClockSampler(nvml_index_for_local_device(local_rank))
-    launches0 = V.launch_count()
+    if args.only == "backward":
+        emit({"backward": bench_backward(ctx, cfg, xv, w, b, m, valid_tokens, padded_tokens, steps=min(steps, 50))})
+        return
 
-    # ---- device-resident timing ------------------------------------------------------------------
+    sampler = ClockSampler(nvml_index_for_local_device(local_rank))
+
+    # ---- device-resident timing: R rounds of K steps back to back, each between its own events ----
+    rounds = 1 if args.only == "headline" else max(1, args.rounds)
     for _ in range(warmup):
         step()
-    barrier()
+    ctx.barrier()
     with sampler:
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(rounds + 1)]
         launches_before = V.launch_count()
-        e0.record()
-        for _ in range(steps):
-            step()
-        e1.record()
-        barrier()
-        timed_launches = V.launch_count() - launches_before
-        ms_total = max_over_ranks(e0.elapsed_time(e1))
+        host_t0 = time.perf_counter()
+        events[0].record()
+        for r in range(rounds):
+            for _ in range(steps):
+                step()
+            events[r + 1].record()
+        host_s = time.perf_counter() - host_t0
+        ctx.barrier()
+        timed_launches = (V.launch_count() - launches_before) // rounds
         kernel_name = V.last_kernel()
+        my_rounds = [events[r].elapsed_time(events[r + 1]) for r in range(rounds)]
+        # per round: every rank's time; the round counts with its slowest rank
+        per_round = [ctx.gather(t) for t in my_rounds]
+        round_ms = [max(v) for v in per_round]
+        order = sorted(range(rounds), key=lambda r: round_ms[r])
+        mid = order[(rounds - 1) // 2]
+        ms_total = round_ms[mid]
+        if args.only == "headline":
+            emit({"ms_per_step": ms_total / steps, "kernel": kernel_name, "launches_per_round": timed_launches})
+            return
 
         # ---- end to end: pinned host in, pinned host out, every step -------------------------
-        y_host = torch.empty_like(x_host).pin_memory()
-        e2e_steps = max(3, min(steps, 20))
+        e2e = None
+        if not args.no_e2e:
+            e2e = bench_e2e(ctx, HostPrefill, cfg, x_host, m_host, w, b, x, y, steps, padded_tokens)
+            e2e["main"]["numa_node"] = numa_node
+            e2e["main"]["numa_note"] = numa_note
 
-        def time_e2e(send_masked_rows):
-            pipe = HostPrefill(cfg.batch, cfg.seqlen, cfg.dim, cfg.dtype, device=dev, chunk_batch=4,
-                               mask_dtype=torch.bool, send_masked_rows=send_masked_rows)
-            for _ in range(3):
-                pipe.run(x_host, w, b, cfg.activation, m_host, y_host)
-            barrier()
-            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            f0.record()
-            for _ in range(e2e_steps):
-                # consecutive batches pipeline into each other; every one is copied in and read back
-                pipe.run(x_host, w, b, cfg.activation, m_host, y_host, join=False)
-            pipe.join()
-            f1.record()
-            barrier()
-            return pipe, max_over_ranks(f0.elapsed_time(f1))
-
-        _, e2e_full_ms_total = time_e2e(True)   # every input row crosses PCIe
-        pipe, e2e_ms_total = time_e2e(False)    # rows no kernel reads stay on the host
-
-        # ---- backward of the same workload (training step of the Canon-D layer) ------------------
-        backward = None
-        if not args.no_backward:
-            backward = bench_backward(V, cfg, xv, w, b, m, valid_tokens, padded_tokens, world, barrier,
-                                      max_over_ranks)
-
-        # ---- decode ---------------------------------------------------------------------------
-        decode = None
-        if not args.no_decode:
-            decode = bench_decode(V, WL, dev, rank, world, barrier, max_over_ranks)
-    e2e_ok = bool(torch.equal(y_host.to(dev), y))
+        backward = None if args.no_backward else bench_backward(ctx, cfg, xv, w, b, m, valid_tokens, padded_tokens)
+        decode = None if args.no_decode else bench_decode(ctx)
+        model_step = None if args.no_decode else bench_model_decode_step(ctx)
+        shapes = None if args.no_shapes else bench_shapes(ctx)
+        del x_host
+        ragged = None if args.no_ragged else bench_ragged(ctx, steps=10)
 
     ms_per_step = ms_total / steps
     value = world * padded_tokens / (ms_per_step * 1e-3)
-    valid_total = sum_over_ranks(float(valid_tokens))
-    e2e_ms = e2e_ms_total / e2e_steps
-    e2e_value = world * padded_tokens / (e2e_ms * 1e-3)
+    valid_total = ctx.sum_over_ranks(float(valid_tokens))
 
     # ---- roofline of the dominant kernel -------------------------------------------------------
-    peak, peak_kind = measured_peak_gbs()
+    peak, peak_kind = ctx.peak, ctx.peak_kind
     elem = 2
     mask_bytes = m.numel() * m.element_size()
     alg_bytes = WL.prefill_bytes(cfg.batch, cfg.dim, cfg.seqlen, cfg.width, elem, valid_tokens=valid_tokens,
@@ -401,7 +494,6 @@ def main():
         "traffic": NCU_TRAFFIC_BYTES.get(cfg.name),
     }
 
-    clocks = sampler.summary()
     line = {
         "metric": METRIC,
         "value": value,
@@ -417,88 +509,176 @@ def main():
         "data": "synthetic",
         "config": workload_config(cfg, world),
         "valid_tokens_per_s": valid_total / (ms_per_step * 1e-3),
-        "e2e": {
-            "value": e2e_value,
-            "unit": UNIT,
-            "h2d_bytes_per_step": pipe.h2d_bytes,
-            "d2h_bytes_per_step": pipe.d2h_bytes,
-            "ms_per_step": e2e_ms,
-            "steps": e2e_steps,
-            "matches_device_result": e2e_ok,
-            "numa_node": numa_node,
-            "note": "rows behind each sequence's last valid position are never read by the kernel and are not sent",
-        },
-        "e2e_all_rows_sent": {
-            "value": world * padded_tokens / (e2e_full_ms_total / e2e_steps * 1e-3),
-            "unit": UNIT,
-            "h2d_bytes_per_step": cfg.batch * cfg.seqlen * (cfg.dim * 2 + 1),
-            "d2h_bytes_per_step": pipe.d2h_bytes,
-            "ms_per_step": e2e_full_ms_total / e2e_steps,
-            "note": "the same pipeline copying all of x, masked rows included",
+        "timing": {
+            "rounds": rounds,
+            "steps_per_round": steps,
+            "reported": "median round (by its slowest rank)",
+            "ms_per_step_rounds": [t / steps for t in round_ms],
+            "ms_per_step_first_round": round_ms[0] / steps,
+            "per_rank_ms_per_step": spread([t / steps for t in per_round[mid]]),
+            "slowest_rank": max(range(world), key=lambda r: per_round[mid][r]),
+            "host_enqueue_us_per_step": host_s / (rounds * steps) * 1e6,
         },
         "gpu_launches": timed_launches,
         "roofline": roofline,
-        "clocks": clocks,
+        "clocks": sampler.summary(),
     }
+    if e2e is not None:
+        line["e2e"] = e2e["main"]
+        line["e2e_variants"] = e2e["variants"]
     if backward is not None:
         line["backward"] = backward
     if decode is not None:
         line["decode"] = decode
+    if model_step is not None:
+        line["model_decode_step"] = model_step
+    if shapes is not None:
+        line["shapes"] = shapes
+    if ragged is not None:
+        line["ragged_sweep"] = ragged
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         sample_rows = list(range(8))
-        tokens, times, cores = time_cpu_reference(cfg, sample_rows, 5, 1)
+        tokens, times, cores, kind = time_cpu_reference(WL, cfg, sample_rows, 5, 1, want_tree=False)
         best = min(times)
         line["cpu_baseline"] = {
             "value": tokens / best,
             "unit": UNIT,
             "cores": cores,
-            "kind": "port",
+            "kind": kind,
             "sample": f"{len(sample_rows)} of {cfg.batch} sequences x {cfg.seqlen} tokens, best of {len(times)} "
                       f"after 1 warm-up, reference arithmetic (bf16 F.conv1d + SiLU) in torch",
             "ms": best * 1e3,
         }
-    if rank == 0:
-        print(json.dumps(line), file=result_out, flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    emit(line)
 
 
-def bench_backward(V, cfg, xv, w, b, m, valid_tokens, padded_tokens, world, barrier, max_over_ranks):
+# --------------------------------------------------------------------------------------------------
+# sections
+# --------------------------------------------------------------------------------------------------
+def bench_e2e(ctx, HostPrefill, cfg, x_host, m_host, w, b, x_dev, y_dev, steps, padded_tokens):
+    """The step through HostPrefill, host buffers in and out, in three variants; and the plain copy
+    rate of the same byte counts over the same link (two streams, no kernel) for comparison."""
+    dev, world = ctx.dev, ctx.world
+    y_host = torch.empty_like(x_host).pin_memory()
+    e2e_steps = max(3, min(steps, 20))
+
+    def run(**kw):
+        pipe = HostPrefill(cfg.batch, cfg.seqlen, cfg.dim, cfg.dtype, device=dev, chunk_batch=4,
+                           mask_dtype=torch.bool, **kw)
+        y_host.fill_(0)
+        for _ in range(3):
+            pipe.run(x_host, w, b, cfg.activation, m_host, y_host)
+        ctx.barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(e2e_steps):
+            # consecutive batches pipeline into each other; every one is copied in and read back
+            pipe.run(x_host, w, b, cfg.activation, m_host, y_host, join=False)
+        pipe.join()
+        f1.record()
+        ctx.barrier()
+        per_rank = ctx.gather(f0.elapsed_time(f1) / e2e_steps)
+        ok = bool(torch.equal(y_host.to(dev), y_dev))
+        ms = max(per_rank)
+        return {
+            "value": world * padded_tokens / (ms * 1e-3),
+            "unit": UNIT,
+            "h2d_bytes_per_step": pipe.h2d_bytes,
+            "d2h_bytes_per_step": pipe.d2h_bytes,
+            "ms_per_step": ms,
+            "per_rank_ms_per_step": spread(per_rank),
+            "steps": e2e_steps,
+            "matches_device_result": ok,
+        }
+
+    full = run(send_masked_rows=True)
+    full["note"] = "every row of x sent, every row of y copied back"
+    lean_in = run()
+    lean_in["note"] = "rows behind each sequence's last valid position are never read by the kernel and are not sent"
+    lean = run(skip_constant_rows=True)
+    lean["note"] = ("as above, and output rows whose taps are all masked (the constant act(bias)) are not copied "
+                    "back: the host writes them into y_host from one [channels] vector inside the timed region")
+
+    # plain copies of the same byte counts: what the link gives with no kernel and no pipeline logic
+    def link(h2d_bytes, d2h_bytes):
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        xin = x_host.view(-1).view(torch.uint8)
+        xd = x_dev.view(-1).view(torch.uint8)
+        yd = y_dev.view(-1).view(torch.uint8)
+        yout = y_host.view(-1).view(torch.uint8)
+        n_in, n_out = min(h2d_bytes, xin.numel()), min(d2h_bytes, yout.numel())
+        scratch_dev = torch.empty(n_in, dtype=torch.uint8, device=dev)
+
+        def once():
+            with torch.cuda.stream(s_in):
+                scratch_dev.copy_(xin[:n_in], non_blocking=True)
+            with torch.cuda.stream(s_out):
+                yout[:n_out].copy_(yd[:n_out], non_blocking=True)
+
+        for _ in range(2):
+            once()
+        ctx.barrier()
+        main = torch.cuda.current_stream(dev)
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        s_in.wait_stream(main)
+        s_out.wait_stream(main)
+        reps = 5
+        for _ in range(reps):
+            once()
+        main.wait_stream(s_in)
+        main.wait_stream(s_out)
+        f1.record()
+        ctx.barrier()
+        del xd
+        per_rank = ctx.gather(f0.elapsed_time(f1) / reps)
+        ms = max(per_rank)
+        return {"ms": ms, "gbs_per_rank_both_directions": (n_in + n_out) / (ms * 1e-3) / 1e9,
+                "d2h_gbs_per_rank": n_out / (ms * 1e-3) / 1e9, "per_rank_ms": spread(per_rank)}
+
+    for v in (full, lean_in, lean):
+        lk = link(v["h2d_bytes_per_step"], v["d2h_bytes_per_step"])
+        v["link_ms_same_bytes"] = lk["ms"]
+        v["link_gbs"] = lk["gbs_per_rank_both_directions"]
+        v["frac_of_link"] = lk["ms"] / v["ms_per_step"]
+    # Headline: y_host holds the same bytes in all three; the leanest copy plan is the product's path.
+    main = dict(lean)
+    return {"main": main, "variants": {"all_rows_both_ways": full, "valid_rows_in_all_rows_out": lean_in}}
+
+
+def bench_backward(ctx, cfg, xv, w, b, m, valid_tokens, padded_tokens, steps=50):
     """Gradients (dx, dweight, dbias) of the bench workload: one causal_conv1d_bwd launch per step,
     device-resident.  Algorithmic bytes: x read where valid + dy read + dx written."""
+    V = ctx.V
     g = torch.Generator(device=xv.device).manual_seed(11)
     dy = torch.randn(xv.shape[0], xv.shape[2], xv.shape[1], generator=g, device=xv.device).to(cfg.dtype).transpose(1, 2)
+
     def step():
         return V.causal_conv1d_bwd(xv, w, b, dy, cfg.activation, attention_mask=m)
-    for _ in range(5):
-        step()
-    barrier()
-    n = 50
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(n):
-        step()
-    e1.record()
-    barrier()
-    ms = max_over_ranks(e0.elapsed_time(e1)) / n
+
+    n = steps
+    ms_rank, host_s = ctx.time_loop(step, n, warmup=min(5, max(3, steps)))
+    ms = ctx.max_over_ranks(ms_rank) / n
     elem = 2
     nbytes = (valid_tokens + 2 * padded_tokens) * cfg.dim * elem
-    peak, _ = measured_peak_gbs()
     gbs = nbytes / (ms * 1e-3) / 1e9
     return {
         "kernel": V.last_kernel(),
         "ms_per_step": ms,
-        "tokens_per_s": world * padded_tokens / (ms * 1e-3),
+        "tokens_per_s": ctx.world * padded_tokens / (ms * 1e-3),
         "algorithmic_bytes_per_launch": nbytes,
         "achieved_gbs": gbs,
-        "frac_of_measured_peak": gbs / peak,
-        "note": "includes the zeroing of the fp32 dweight/dbias accumulators and the tile-classification pre-pass",
+        "frac_of_measured_peak": gbs / ctx.peak,
+        "host_enqueue_us_per_step": host_s / n * 1e6,
+        "note": "one call = the tile-classification pre-pass (which also clears the fp32 dweight/dbias accumulators) "
+                "and the main kernel",
     }
 
 
-def bench_decode(V, WL, dev, rank, world, barrier, max_over_ranks):
+def bench_decode(ctx):
     """Decode configuration: 1024 successive causal_conv1d_update steps on a [256, 960, 3] state
-    seeded from a 512-token prefill, replayed as one CUDA graph; plus one bandwidth-bound shape."""
+    seeded from a 512-token prefill, replayed as one CUDA graph; plus bandwidth-bound shapes."""
+    V, WL, dev, rank, world = ctx.V, ctx.WL, ctx.dev, ctx.rank, ctx.world
     cfg = WL.DECODE_CANON_B
     rows = [rank * cfg.batch + i for i in range(cfg.batch)]
     w, b = WL.weights(cfg.cfg, cfg.dim, cfg.width, cfg.dtype, device=dev)
@@ -513,15 +693,8 @@ def bench_decode(V, WL, dev, rank, world, barrier, max_over_ranks):
         for s in range(cfg.steps):
             V.causal_conv1d_update(toks[s], state, w, b, out=ys[s])
 
-    # eager launches
-    eager()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    eager()
-    e1.record()
-    barrier()
-    eager_ms = max_over_ranks(e0.elapsed_time(e1))
+    eager_rank, _ = ctx.time_loop(eager, 1, warmup=1)
+    eager_ms = ctx.max_over_ranks(eager_rank)
 
     # the same 1024 launches captured once and replayed
     side = torch.cuda.Stream(dev)
@@ -533,60 +706,219 @@ def bench_decode(V, WL, dev, rank, world, barrier, max_over_ranks):
         with torch.cuda.graph(graph, stream=side):
             eager()
     torch.cuda.current_stream(dev).wait_stream(side)
-    for _ in range(3):
-        graph.replay()
-    barrier()
     reps = 5
-    e0.record()
-    for _ in range(reps):
-        graph.replay()
-    e1.record()
-    barrier()
-    graph_ms = max_over_ranks(e0.elapsed_time(e1)) / reps
+    graph_rank, _ = ctx.time_loop(graph.replay, reps, warmup=3)
+    graph_ms = ctx.max_over_ranks(graph_rank) / reps
     step_bytes = WL.decode_bytes(cfg.batch, cfg.dim, cfg.width, cfg.state_len, 2)
-
-    saturating = bench_decode_saturating(V, WL, dev, world, barrier, max_over_ranks)
     return {
         "config": {"workload": cfg.name, "batch_per_gpu": cfg.batch, "channels": cfg.dim, "state_len": cfg.state_len,
                    "width": cfg.width, "steps": cfg.steps, "prefill_len": cfg.prefill_len},
+        "bound": "launch",
+        "bound_note": "3.9 MB per step is under 1 us of HBM time and the 1.5 MB state stays in L2: a step costs its "
+                      "launch; bandwidth-bound decode figures are under 'saturating'",
         "tokens_per_s_graph": world * cfg.batch * cfg.steps / (graph_ms * 1e-3),
         "us_per_step_graph": graph_ms * 1e3 / cfg.steps,
         "tokens_per_s_eager": world * cfg.batch * cfg.steps / (eager_ms * 1e-3),
         "us_per_step_eager": eager_ms * 1e3 / cfg.steps,
         "bytes_per_step": step_bytes,
         "gbs_graph": step_bytes * cfg.steps / (graph_ms * 1e-3) / 1e9,
-        "saturating": saturating,
+        "saturating": bench_decode_saturating(ctx, cfg.state_len),
+        "saturating_state_len_4": bench_decode_saturating(ctx, 4),
+        "saturating_state_len_8": bench_decode_saturating(ctx, 8),
+        "saturating_circular_state_len_8": bench_decode_saturating(ctx, 8, circular=True),
     }
 
 
-def bench_decode_saturating(V, WL, dev, world, barrier, max_over_ranks):
+def bench_decode_saturating(ctx, state_len, circular=False, steps=20):
     """Bandwidth-bound decode shape: as many (sequence, channel) rows as one Canon-D prefill batch."""
+    V, WL, dev = ctx.V, ctx.WL, ctx.dev
     cfg = WL.DECODE_CANON_B
-    Bs, Ds, Ls = 32768, 3456, cfg.state_len
+    Bs, Ds, Ls = 32768, 3456, state_len
     ws, bs = WL.weights(cfg.cfg, Ds, cfg.width, cfg.dtype, device=dev)
     xs = torch.randn(Bs, Ds, device=dev).to(cfg.dtype)
     ss = torch.randn(Bs, Ds, Ls, device=dev).to(cfg.dtype)
     yo = torch.empty_like(xs)
-    for _ in range(5):
-        V.causal_conv1d_update(xs, ss, ws, bs, activation="silu", out=yo)
-    barrier()
-    n = 20
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(n):
-        V.causal_conv1d_update(xs, ss, ws, bs, activation="silu", out=yo)
-    e1.record()
-    barrier()
-    sat_ms = max_over_ranks(e0.elapsed_time(e1)) / n
-    sat_bytes = WL.decode_bytes(Bs, Ds, cfg.width, Ls, 2)
-    peak, _ = measured_peak_gbs()
+    seqlens = torch.arange(Bs, dtype=torch.int32, device=dev) if circular else None
+
+    def step():
+        V.causal_conv1d_update(xs, ss, ws, bs, "silu", seqlens, out=yo)
+
+    n = steps
+    ms_rank, _ = ctx.time_loop(step, n, warmup=min(5, max(3, steps)))
+    sat_ms = ctx.max_over_ranks(ms_rank) / n
+    kernel = V.last_kernel()
+    # x + y + the state row read + the state row written.  (The circular state keeps its columns in place
+    # and needs only width-1 of them, but a channel's whole row -- 16 bytes at state_len 8 -- is half a
+    # DRAM sector: it moves whole either way, so the row is counted whole.)
+    sat_bytes = WL.decode_bytes(Bs, Ds, cfg.width, Ls, 2) + (Bs * 4 if circular else 0)
     return {
-        "batch": Bs, "channels": Ds, "state_len": Ls, "activation": "silu",
+        "batch": Bs, "channels": Ds, "state_len": Ls, "activation": "silu", "circular": circular, "kernel": kernel,
         "ms_per_step": sat_ms, "bytes_per_step": sat_bytes,
         "achieved_gbs": sat_bytes / (sat_ms * 1e-3) / 1e9,
-        "frac_of_measured_peak": sat_bytes / (sat_ms * 1e-3) / 1e9 / peak,
-        "tokens_per_s": world * Bs / (sat_ms * 1e-3),
+        "frac_of_measured_peak": sat_bytes / (sat_ms * 1e-3) / 1e9 / ctx.peak,
+        "tokens_per_s": ctx.world * Bs / (sat_ms * 1e-3),
     }
+
+
+def bench_model_decode_step(ctx):
+    """The Canon work of ONE decode step of the whole-model configuration: 18 layers x (A 640, B 960,
+    C 640, D 3456 channels) = 72 causal_conv1d_update calls at batch 64 with the [B, D, 4] states the
+    reference's CUDA branch keeps (model/model.py:299-313), bf16, no bias, no activation (the
+    reference's defaults).  Eager with programmatic dependent launch on and off, and as one CUDA graph."""
+    V, dev = ctx.V, ctx.dev
+    B, L, W, layers = 64, 4, 4, 18
+    dims = (640, 960, 640, 3456)
+    g = torch.Generator(device=dev).manual_seed(3)
+    calls = []
+    for _ in range(layers):
+        for D in dims:
+            calls.append((torch.randn(B, D, generator=g, device=dev).bfloat16(),
+                          torch.randn(B, D, L, generator=g, device=dev).bfloat16(),
+                          (torch.rand(D, W, generator=g, device=dev) - 0.5).bfloat16(),
+                          torch.empty(B, D, device=dev, dtype=torch.bfloat16)))
+
+    def model_step():
+        for xt, st, wt, out in calls:
+            V.causal_conv1d_update(xt, st, wt, None, None, out=out)
+
+    nbytes = sum(B * D * 2 * (2 + 2 * L) + D * W * 2 for D in dims) * layers
+    res = {"calls_per_step": len(calls), "batch": B, "state_len": L, "channels": list(dims), "layers": layers,
+           "bytes_per_step": nbytes}
+    n = 20
+    for name, pdl in (("eager_pdl_on", True), ("eager_pdl_off", False)):
+        before = V.set_pdl(pdl)
+        ms_rank, host_s = ctx.time_loop(model_step, n, warmup=3)
+        V.set_pdl(None)
+        ms = ctx.max_over_ranks(ms_rank) / n
+        res[name] = {"us_per_step": ms * 1e3, "us_per_call": ms * 1e3 / len(calls), "gbs": nbytes / (ms * 1e-3) / 1e9,
+                     "host_enqueue_us_per_step": host_s / n * 1e6}
+        del before
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        model_step()
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            model_step()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    ms_rank, _ = ctx.time_loop(graph.replay, n, warmup=3)
+    ms = ctx.max_over_ranks(ms_rank) / n
+    res["graph"] = {"us_per_step": ms * 1e3, "us_per_call": ms * 1e3 / len(calls), "gbs": nbytes / (ms * 1e-3) / 1e9}
+    res["bound"] = "launch"
+    return res
+
+
+def bench_shapes(ctx):
+    """Device-resident prefill at the shapes of the whole-model configuration (batch 64 x 1024 tokens;
+    Canon A/C 640, B 960, D 3456 channels; bf16; no bias, no activation, no mask: what the reference's
+    layer passes by default) and one dense Canon-D batch of 128 sequences with bias and SiLU."""
+    V, WL, dev = ctx.V, ctx.WL, ctx.dev
+    out = {}
+    g = torch.Generator(device=dev).manual_seed(5)
+    specs = [("canon_a_c_b64", 64, 640, None, False), ("canon_b_b64", 64, 960, None, False),
+             ("canon_d_b64", 64, 3456, None, False), ("canon_d_dense_b128_silu", 128, 3456, "silu", True)]
+    for name, B, D, act, has_bias in specs:
+        T, W = 1024, 4
+        x = torch.randn(B, T, D, generator=g, device=dev).bfloat16()
+        y = torch.empty_like(x)
+        wt = (torch.rand(D, W, generator=g, device=dev) - 0.5).bfloat16()
+        bt = (torch.rand(D, generator=g, device=dev) - 0.5).bfloat16() if has_bias else None
+        xv, yv = x.transpose(1, 2), y.transpose(1, 2)
+
+        def step():
+            V.causal_conv1d_fn(xv, wt, bt, activation=act, out=yv)
+
+        n = 20
+        ms_rank, _ = ctx.time_loop(step, n, warmup=3)
+        ms = ctx.max_over_ranks(ms_rank) / n
+        nbytes = 2 * x.numel() * 2
+        out[name] = {"batch": B, "seq_len": T, "channels": D, "activation": act, "bias": has_bias,
+                     "kernel": V.last_kernel(), "us_per_launch": ms * 1e3, "bytes_per_launch": nbytes,
+                     "achieved_gbs": nbytes / (ms * 1e-3) / 1e9,
+                     "frac_of_measured_peak": nbytes / (ms * 1e-3) / 1e9 / ctx.peak,
+                     "tokens_per_s": ctx.world * B * T / (ms * 1e-3)}
+        del x, y
+    return out
+
+
+def bench_ragged(ctx, steps=10):
+    """The ragged large-batch configuration: 512 sequences x up to 4096 tokens x 3456 channels, bf16,
+    SiLU, lengths log-uniform in [16, 4096], right-padded and masked.  STRONG scaling: the 512
+    sequences are split over the N ranks, once by cost (longest-processing-time on the bytes a
+    sequence moves) and once as contiguous equal-count slices; no rank talks to another.  A third
+    figure runs the by-cost shards as packed rows (seq_idx), which neither read nor write padding."""
+    V, WL, dev, rank, world = ctx.V, ctx.WL, ctx.dev, ctx.rank, ctx.world
+    from viby_model_b200.dist_util import shard_by_cost, shard_range
+
+    cfg = WL.RAGGED_SWEEP
+    lens_all = WL.sequence_lengths(cfg).tolist()
+    w, b = WL.weights(cfg.cfg, cfg.dim, cfg.width, cfg.dtype, device=dev)
+    elem = 2
+    row_bytes = cfg.dim * elem
+
+    def run(rows, packed):
+        lens = [lens_all[i] for i in rows]
+        x = WL.prefill_inputs(cfg, rows, device=dev, generate_on="cuda")
+        if packed:
+            xp = torch.cat([x[i, :n] for i, n in enumerate(lens)], 0).unsqueeze(0)
+            del x
+            yp = torch.empty_like(xp)
+            ids = V.seq_idx_from_lengths(lens, device=dev)
+            xv, yv = xp.transpose(1, 2), yp.transpose(1, 2)
+
+            def step():
+                V.causal_conv1d_fn(xv, w, b, activation=cfg.activation, seq_idx=ids, out=yv)
+
+            my_bytes = 2 * sum(lens) * row_bytes
+        else:
+            m = WL.attention_mask(cfg, rows, device=dev, dtype=torch.bool)
+            y = torch.empty_like(x)
+            xv, yv = x.transpose(1, 2), y.transpose(1, 2)
+
+            def step():
+                V.causal_conv1d_fn(xv, w, b, activation=cfg.activation, attention_mask=m, out=yv)
+
+            my_bytes = (sum(lens) + len(rows) * cfg.seqlen) * row_bytes
+        ms_rank, _ = ctx.time_loop(step, steps, warmup=3)
+        kernel = V.last_kernel()
+        per_rank = [t / steps for t in ctx.gather(ms_rank)]
+        bytes_rank = ctx.gather(float(my_bytes))
+        ms = max(per_rank)
+        total_bytes = sum(bytes_rank)
+        gbs = total_bytes / (ms * 1e-3) / 1e9
+        return {
+            "kernel": kernel,
+            "ms_per_step": ms,
+            "per_rank_ms": spread(per_rank),
+            "imbalance_max_over_mean": ms / (sum(per_rank) / len(per_rank)),
+            "bytes_imbalance_max_over_mean": max(bytes_rank) / (total_bytes / len(bytes_rank)),
+            "padded_tokens_per_s": cfg.batch * cfg.seqlen / (ms * 1e-3),
+            "valid_tokens_per_s": sum(lens_all) / (ms * 1e-3),
+            "algorithmic_bytes": total_bytes,
+            "achieved_gbs_all_ranks": gbs,
+            "frac_of_measured_peak_per_gpu": gbs / world / ctx.peak,
+        }
+
+    costs = [n + cfg.seqlen for n in lens_all]  # rows read + rows written
+    by_cost = shard_by_cost(costs, world)[rank]
+    contiguous = list(shard_range(cfg.batch, rank, world))
+    res = {
+        "config": {"workload": cfg.name, "global_batch": cfg.batch, "max_seq_len": cfg.seqlen, "channels": cfg.dim,
+                   "lengths": "log-uniform in [16, 4096]", "valid_tokens": sum(lens_all),
+                   "padded_tokens": cfg.batch * cfg.seqlen},
+        "scaling": "strong",
+        "n_gpus": world,
+        "steps": steps,
+        "sharded_by_cost": run(by_cost, False),
+    }
+    torch.cuda.empty_cache()
+    res["sharded_contiguous"] = res["sharded_by_cost"] if world == 1 else run(contiguous, False)
+    torch.cuda.empty_cache()
+    packed_rows = shard_by_cost(lens_all, world)[rank]
+    res["packed_rows_by_cost"] = run(packed_rows, True)
+    torch.cuda.empty_cache()
+    return res
 
 
 if __name__ == "__main__":

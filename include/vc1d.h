@@ -129,6 +129,25 @@ typedef struct vc1d_prefill_args {
      * slabs = static tile assignment. */
     void* scratch;
     int64_t scratch_bytes;
+    /* Packed variable-length rows (the seq_idx argument of causal_conv1d_fn, signature at
+     * causal-conv1d-mps/causal_conv1d_mps/autograd.py:501-510): seq_idx[batch, seqlen] int32 names the
+     * sequence every time step belongs to; a tap contributes only when its step carries the same
+     * value as the output step, so sequences laid end to end in one row never see each other.
+     * NULL = absent.  Not combined with mask, initial_state or final_state (VC1D_E_SHAPE). */
+    const int32_t* seq_idx;
+    int64_t seq_stride_b, seq_stride_t;   /* in elements */
+    /* more tuning of the TMA-staged kernel: 0 = automatic */
+    int32_t tma_claim_chunk;     /* consecutive tiles a CTA takes per claim: 1, 2 or 4 */
+    int32_t tma_empty_store;     /* tiles whose taps are all masked: 1 = stored by the consumer warps,
+                                    2 = one bulk tensor store per tile from a constant tile in shared memory */
+    int32_t tma_classify;        /* tile classes of a masked launch: 1 = pre-pass kernel, 2 = by every CTA itself
+                                    while its first tile is in flight (small masks only) */
+    int32_t tma_pdl;             /* main kernel launched as a programmatic dependent of whatever precedes it in
+                                    the stream: 1 = only after a pre-pass, 2 = always */
+    int32_t tma_static_first;    /* tiles every CTA takes without a claim before it starts claiming: 1..8 */
+    int32_t tma_test_expire;     /* self-test of the bounded waits: 1 = every CTA withholds its first tile and
+                                    polls only 4096 times, so the waits for that tile expire, the kernel
+                                    returns normally with y incomplete and vc1d_tma_timeouts() has grown */
 } vc1d_prefill_args;
 
 VC1D_API int vc1d_prefill(const vc1d_prefill_args* args, void* stream);
@@ -138,11 +157,14 @@ VC1D_API int vc1d_prefill(const vc1d_prefill_args* args, void* stream);
  * (a serving loop whose memory plan is frozen, code running under another allocator's lock or
  * callback, a host language whose binding owns no device allocator).  No counterpart in the
  * reference.  Same arguments and results as vc1d_prefill with kernel = VC1D_KERNEL_TMA (so the
- * layout must be channel-last without initial_state, else VC1D_E_STRIDE); `scratch`,
- * `scratch_bytes` and `kernel` in *args are ignored.  The dynamic tile scheduler's scratch is a
- * fixed 64 KB array inside the library's device image, so the call never allocates or frees.
+ * layout must be channel-last, else VC1D_E_STRIDE; every fused option of vc1d_prefill, initial_state
+ * included, is accepted); `scratch`, `scratch_bytes` and `kernel` in *args are ignored.  The dynamic
+ * tile scheduler's scratch is a fixed 64 KB array inside the library's device image, so the call
+ * never allocates or frees.
  *  - Limit: batch * ceil(seqlen / 32) <= VC1D_NOALLOC_MAX_TILES, else VC1D_E_TOO_LARGE and nothing
- *    is launched.
+ *    is launched.  The limit is checked, and the array's counters are cleared on the caller's
+ *    stream, on every call -- also for launches that end up not using the array (no mask and few
+ *    tiles per CTA: static tile assignment).
  *  - The first call on each device looks the array up (with that device current) and may make
  *    the runtime load the device image: make it before any stream capture begins.
  *  - One array per device, shared by every call on that device and holding the last call's
@@ -164,8 +186,8 @@ VC1D_API int vc1d_prefill_noalloc(const vc1d_prefill_args* args, void* stream);
  *     dx[t]   = (residual ? dy[t] : 0) + mask[t] * sum_w weight[w] * g[t+(W-1-w)]
  *     dweight[d,w] += sum_{b,t} (x*mask)[t-(W-1-w)] * g[t];    dbias[d] += sum_{b,t} g[t]
  * x, dy, dx: logical [batch, dim, seqlen], element strides per tensor.  dweight [dim, width] and
- * dbias [dim] are fp32, contiguous, and ACCUMULATED into (the caller zeroes them), as the
- * reference accumulates in fp32 and casts afterwards (causal_conv1d_kernel.mm:553-557, 771-776).
+ * dbias [dim] are fp32, contiguous, and ACCUMULATED into (the caller zeroes them, or sets zero_grads),
+ * as the reference accumulates in fp32 and casts afterwards (causal_conv1d_kernel.mm:553-557, 771-776).
  * Sums over (batch, time) use atomic adds of per-CTA partial sums: their order is not fixed.
  */
 typedef struct vc1d_prefill_bwd_args {
@@ -192,7 +214,8 @@ typedef struct vc1d_prefill_bwd_args {
     int32_t kernel;         /* VC1D_KERNEL_AUTO | VC1D_KERNEL_GENERIC | VC1D_KERNEL_TMA */
     int32_t tma_stages;     /* tuning of the TMA-staged kernel: 0 = automatic */
     int32_t tma_ctas_per_sm;
-    int32_t reserved;
+    int32_t tma_variant;    /* thread geometry of the TMA-staged kernel: 0 = automatic, 1 = 8 bytes of channels per
+                               thread, 2 = 4 bytes (16-bit I/O), 3 = 4 bytes with twice the consumer warps */
     void* scratch;          /* as in vc1d_prefill_args */
     int64_t scratch_bytes;
     /* History of a chunked continuation (model/model.py:607-617), as in vc1d_prefill_args: the
@@ -202,7 +225,8 @@ typedef struct vc1d_prefill_bwd_args {
     const void* initial_state;  /* [batch, dim, init_len] contiguous, or NULL */
     void* dinitial_state;       /* [batch, dim, init_len] contiguous, or NULL */
     int32_t init_len;
-    int32_t reserved2;
+    int32_t zero_grads;         /* 1: the library clears dweight / dbias itself before accumulating (on the stream,
+                                   folded into the tile-classification pre-pass when the launch has one) */
 } vc1d_prefill_bwd_args;
 
 VC1D_API int vc1d_prefill_bwd(const vc1d_prefill_bwd_args* args, void* stream);
@@ -298,7 +322,7 @@ VC1D_API const char* vc1d_status_string(int status);
 VC1D_API uint64_t vc1d_launch_count(void);
 
 /* Name of the kernel the most recent launcher call on this thread selected ("channel_last",
- * "time_major", "generic", "tma", "update_vec", "update_generic", "bwd_tma", "bwd_generic",
+ * "time_major", "generic", "tma", "update_vec", "update_lane", "update_generic", "bwd_tma", "bwd_generic",
  * "update_bwd").  Per host thread: a backward pass run by an autograd worker thread does not show
  * up in the thread that called the forward. */
 VC1D_API const char* vc1d_last_kernel(void);
@@ -307,6 +331,14 @@ VC1D_API const char* vc1d_last_kernel(void);
  * started (0 in a healthy run; a CTA whose wait expires abandons its remaining tiles).  Reads a
  * device counter with a synchronising copy: call it after the stream has been synchronised. */
 VC1D_API unsigned int vc1d_tma_timeouts(void);
+
+/* Programmatic dependent launch between this library's kernels on one stream (a decode step's launch
+ * overlapping the previous step's tail; a masked prefill's main kernel overlapping its
+ * tile-classification pre-pass).  On by default unless the environment has VC1D_NO_PDL=1.
+ * enabled: 1 = on, 0 = off, negative = back to the environment's choice.  Returns the setting that was
+ * in effect before the call.  Process-wide; affects launches made after it returns.  (The reference
+ * has no counterpart: its kernels come from an external package, model/model.py:20-30.) */
+VC1D_API int vc1d_set_pdl(int enabled);
 
 #ifdef __cplusplus
 }

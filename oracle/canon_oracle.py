@@ -11,6 +11,8 @@ What each function follows (paths inside the reference project):
                             model/model.py:604-620, 664-670 (history or zero left-padding);
                             mask multiply model/model.py:454-457 / 590-602; state window
                             model/model.py:470-489 and 623-661; residual model/model.py:491.
+  causal_conv1d_packed_ref  the same operator on packed variable-length rows (seq_idx): every run of
+                            equal ids is one sequence of causal_conv1d_ref.
   causal_conv1d_update_ref  model/model.py:372-398 (roll left, insert, dot over the last W
                             columns, bias, SiLU), generalised to any state_len >= W-1 exactly as
                             the call at model/model.py:305-311 needs; circular variant
@@ -105,6 +107,27 @@ def causal_conv1d_ref(
         prev = torch.zeros(B, D, L, dtype=dt)
     state = torch.cat([prev, xm], dim=-1)[..., -L:].contiguous()
     return y, state
+
+
+def causal_conv1d_packed_ref(x: torch.Tensor, weight: torch.Tensor, bias=None, activation=None, *,
+                             seq_idx: torch.Tensor, return_fp32: bool = False) -> torch.Tensor:
+    """Oracle of causal_conv1d_fn with ``seq_idx`` (signature at
+    causal-conv1d-mps/causal_conv1d_mps/autograd.py:501-510; the reference itself passes None,
+    model/model.py:465).  x [B,D,T] holds, in every row, sequences laid end to end; seq_idx[B,T] names
+    the sequence of each step.  Each maximal run of equal ids is convolved on its own with
+    causal_conv1d_ref (zeros left of its first step), which is what a right-padded batch computes at
+    its valid positions (model/model.py:454-466)."""
+    B, D, T = x.shape
+    out = torch.empty((B, D, T), dtype=torch.float32 if return_fp32 else x.dtype)
+    ids = seq_idx.to(torch.int64)
+    for b in range(B):
+        row = ids[b]
+        cuts = [0] + (torch.nonzero(row[1:] != row[:-1]).flatten() + 1).tolist() + [T]
+        for t0, t1 in zip(cuts[:-1], cuts[1:]):
+            if t1 > t0:
+                out[b:b + 1, :, t0:t1] = causal_conv1d_ref(x[b:b + 1, :, t0:t1], weight, bias, activation,
+                                                          return_fp32=return_fp32)
+    return out
 
 
 def causal_conv1d_f64(x: torch.Tensor, weight: torch.Tensor, bias=None, activation=None) -> np.ndarray:

@@ -322,3 +322,49 @@ def test_gradients_of_a_chunked_continuation(W):
     # looks at chunk 2
     assert torch.allclose(wd.grad.cpu().double(), wr.grad, rtol=1e-4, atol=1e-4)
     assert torch.allclose(bd.grad.cpu().double(), br.grad, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("masked", [False, True])
+@pytest.mark.parametrize("T1,L", [(9, 3), (9, 6), (2, 5)])
+def test_gradient_flows_through_the_returned_final_state(T1, L, masked):
+    """Chunked training as the documentation describes it: ``y1, s = fn(x1, return_final_states=True)``
+    then ``y2 = fn(x2, initial_states=s)``.  The gradient the second chunk sends into its initial state
+    must reach the last inputs of the first chunk (and, when the first chunk is shorter than the state,
+    the first chunk's own initial state): compared with float64 autograd over the whole sequence."""
+    W = 4
+    g = torch.Generator().manual_seed(31 + T1 + L)
+    B, D, T0, T2 = 2, 16, 4, 11
+    x = torch.randn(B, T0 + T1 + T2, D, generator=g, dtype=torch.float64)
+    w = torch.randn(D, W, generator=g, dtype=torch.float64)
+    b = torch.randn(D, generator=g, dtype=torch.float64)
+    coef = torch.randn(B, T0 + T1 + T2, D, generator=g, dtype=torch.float64)
+    mask = torch.ones(B, T0 + T1 + T2, dtype=torch.float64)
+    if masked:
+        mask[0, T0 + T1 - 1] = 0  # the last step of chunk 1 of one sequence is padding
+        mask[1, T0 + 1] = 0
+    xr = x.clone().requires_grad_(True)
+    wr, br = w.clone().requires_grad_(True), b.clone().requires_grad_(True)
+    xm = xr * mask.unsqueeze(-1)
+    yr = torch.nn.functional.silu(torch.nn.functional.conv1d(
+        torch.nn.functional.pad(xm.transpose(1, 2), (W - 1, 0)), wr.unsqueeze(1), br, groups=D))
+    (yr[..., T0:].transpose(1, 2) * coef[:, T0:]).sum().backward()
+
+    dev = lambda t: t.float().to(DEV)  # noqa: E731
+    s0 = x[:, :T0].transpose(1, 2).contiguous().float().to(DEV).requires_grad_(True)  # history before chunk 1
+    x1 = dev(x[:, T0:T0 + T1]).requires_grad_(True)
+    x2 = dev(x[:, T0 + T1:]).requires_grad_(True)
+    wd, bd = dev(w).requires_grad_(True), dev(b).requires_grad_(True)
+    m1 = dev(mask[:, T0:T0 + T1]) if masked else None
+    m2 = dev(mask[:, T0 + T1:]) if masked else None
+    y1, s1 = V.causal_conv1d_fn(x1.transpose(1, 2), wd, bd, activation="silu", initial_states=s0, attention_mask=m1,
+                                return_final_states=True, state_len=L)
+    assert s1.requires_grad
+    y2 = V.causal_conv1d_fn(x2.transpose(1, 2), wd, bd, activation="silu", initial_states=s1, attention_mask=m2)
+    loss = (y1.transpose(1, 2) * dev(coef[:, T0:T0 + T1])).sum() + (y2.transpose(1, 2) * dev(coef[:, T0 + T1:])).sum()
+    loss.backward()
+    tol = dict(rtol=1e-4, atol=1e-4)
+    assert torch.allclose(x1.grad.cpu().double(), xr.grad[:, T0:T0 + T1], **tol)
+    assert torch.allclose(x2.grad.cpu().double(), xr.grad[:, T0 + T1:], **tol)
+    assert torch.allclose(s0.grad.cpu().double(), xr.grad[:, :T0].transpose(1, 2), **tol)
+    assert torch.allclose(wd.grad.cpu().double(), wr.grad, **tol)
+    assert torch.allclose(bd.grad.cpu().double(), br.grad, **tol)

@@ -84,3 +84,29 @@ def test_host_prefill_sending_all_rows_gives_the_same_result():
         assert pipe.h2d_bytes == ((B * T * D * 2 + B * T) if send_all else
                                   (sum(HostPrefill.valid_prefix_lengths(m)) * D * 2 + B * T))
     assert torch.equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("has_bias", [True, False])
+@pytest.mark.parametrize("act", ["silu", None])
+def test_host_prefill_filling_constant_rows_on_the_host_gives_the_same_bytes(act, has_bias):
+    """Rows width-1 or more steps behind a sequence's last valid position are act(bias) in every
+    sequence: with skip_constant_rows they are not copied back but written by the host, and y_host
+    must still equal the full copy bit for bit (pipelined batches included)."""
+    B, T, D, W = 7, 300, 1152, 4
+    x, w, b, m = make(B, T, D, W, torch.bfloat16, seed=21)
+    if not has_bias:
+        b = None
+    full = HostPrefill(B, T, D, torch.bfloat16, device=DEV, chunk_batch=2, mask_dtype=torch.bool)
+    lean = HostPrefill(B, T, D, torch.bfloat16, device=DEV, chunk_batch=2, mask_dtype=torch.bool,
+                       skip_constant_rows=True)
+    y_full = torch.empty_like(x).pin_memory()
+    y_lean = torch.full_like(x, float("nan")).pin_memory()
+    full.run(x, w, b, act, m, y_full)
+    for _ in range(3):
+        lean.run(x, w, b, act, m, y_lean, join=False)
+    lean.join()
+    torch.cuda.synchronize()
+    assert torch.equal(y_full.view(torch.int16), y_lean.view(torch.int16))
+    lens = HostPrefill.valid_prefix_lengths(m)
+    expect = sum(min(T, n + W - 1) for n in lens) * D * 2 + D * 2
+    assert lean.d2h_bytes == expect and expect < full.d2h_bytes

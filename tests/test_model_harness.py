@@ -7,9 +7,11 @@ model on a machine that has no copy of it.
 
 GPU part: the full-size Viby shape (18 layers, hidden 640, 4 query heads / 1 KV head, FFN 1728,
 vocab 25600, Canon A/C 640, B 960, D 3456 channels, width 4, bf16, N(0, 0.02) weights) with the
-Canon kernels swapped in: 72 kernel launches per forward, every Canon call checked against a torch
-fp32 reference on the same input, logits and greedy tokens compared with the same model run on
-torch ops, prefill followed by cached decode steps.
+Canon kernels swapped in: 72 kernel launches per forward, the conv term of every Canon call checked
+against a torch fp32 reference on the same input, once with the fused keywords and once with the
+reference's own call pattern (plain keyword calls through the drop-in module ``causal_conv1d``; both
+must agree bit for bit), logits and greedy tokens compared with the same model run on torch ops,
+prefill followed by cached decode steps.
 """
 import json
 import os
@@ -123,19 +125,36 @@ def test_config4_full_model_prefill_and_decode():
     assert V.launch_count() - before == 72
     assert V.last_kernel() == "tma"
     assert len(hk.canon_inputs) == 72
+    fused_calls = hk.canon_inputs
+    hk.canon_inputs = None
+
+    # --- the same prefill with the kernels called the way the reference calls them (plain keywords
+    # through the drop-in module, mask / state / residual in torch): 72 launches again, the conv term
+    # of EVERY Canon call within 1 ulp of a torch fp32 reference on the same input, and -- the fused
+    # residual being bit-equal to x + y -- the same bits as the fused run, call by call
+    hp = VibyHarness(FULL, params, canon="kernel_plain")
+    hp.canon_inputs = []
+    cp = hp.new_cache()
+    before = V.launch_count()
+    logits_p = hp.forward(ids, None, cp)
+    assert V.launch_count() - before == 72
+    assert len(hp.canon_inputs) == 72
     worst = 0
-    for name, layer, x, m, out in hk.canon_inputs[::5] + hk.canon_inputs[-4:]:
+    for (name, layer, x, m, out, conv_term), fused in zip(hp.canon_inputs, fused_calls):
         w = params[f"model.layers.{layer}.{name}.weight"].squeeze(1)
         b = params[f"model.layers.{layer}.{name}.bias_param"]
         conv = torch.nn.functional.conv1d(torch.nn.functional.pad(x.transpose(1, 2).float(), (3, 0)),
                                           w.float().unsqueeze(1), b.float(), groups=x.shape[-1])
-        ref = x + torch.nn.functional.silu(conv).to(x.dtype).transpose(1, 2)
-        ulp = ulp_distance(out.contiguous(), ref.contiguous())
-        bad = (ulp > 1) & ((out.float() - ref.float()).abs() > 1e-6)
-        # the residual sum can amplify a 1-ulp difference of the conv term where x and y cancel
-        assert float(bad.float().mean()) < 1e-4, (name, layer, int(ulp.max()))
+        ref = torch.nn.functional.silu(conv).to(x.dtype).transpose(1, 2)
+        ulp = ulp_distance(conv_term.contiguous(), ref.contiguous())
+        bad = (ulp > 1) & ((conv_term.float() - ref.float()).abs() > 1e-6)
+        assert not bool(bad.any()), (name, layer, int(bad.sum()), int(ulp.max()))
         worst = max(worst, int(ulp.max()))
-    hk.canon_inputs = None
+        assert torch.equal(x, fused[2]) and torch.equal(out, fused[4]), (name, layer)
+    hp.canon_inputs = None
+    assert torch.equal(logits_p, logits_k)
+    for key in ck["canon"]:
+        assert torch.equal(ck["canon"][key], cp["canon"][key]), key
     ct = ht.new_cache()
     logits_t = ht.forward(ids, None, ct)
     for key in ck["canon"]:
@@ -155,6 +174,15 @@ def test_config4_full_model_prefill_and_decode():
         before = V.launch_count()
         lk = hk.forward(tok, None, ck)
         assert V.launch_count() - before == 72
+        if s < 8:
+            # the reference's own call pattern (keywords through the drop-in module, residual in torch)
+            # in lockstep: 72 launches, the same logits and the same states bit for bit
+            before = V.launch_count()
+            lp = hp.forward(tok, None, cp)
+            assert V.launch_count() - before == 72
+            assert torch.equal(lp, lk), s
+            for key in ck["canon"]:
+                assert torch.equal(ck["canon"][key], cp["canon"][key]), (s, key)
         lt = ht.forward(tok, None, ct)
         agree_steps.append(float((lk.argmax(-1) == lt.argmax(-1)).float().mean()))
         tok = lk[:, -1].argmax(-1, keepdim=True)

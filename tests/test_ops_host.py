@@ -43,8 +43,11 @@ def test_activation_and_seq_idx():
     w = torch.randn(4, 4)
     with pytest.raises(NotImplementedError, match="activation must be None, silu, or swish"):
         V.causal_conv1d_fn(x, w, activation="gelu")
-    with pytest.raises(NotImplementedError, match="seq_idx"):
+    # seq_idx is an operand like any other: host tensors are refused, never computed on the CPU
+    with pytest.raises(ValueError, match="must be on a CUDA device"):
         V.causal_conv1d_fn(x, w, seq_idx=torch.zeros(2, 8, dtype=torch.int32))
+    with pytest.raises(NotImplementedError, match="forward-only"):
+        V.causal_conv1d_fn(x.requires_grad_(), w, seq_idx=torch.zeros(2, 8, dtype=torch.int32))
 
 
 def test_update_shape_checks():
@@ -87,7 +90,8 @@ def test_custom_ops_have_shape_functions():
         assert st.shape == (2, 64, 4)
         y2, st2 = torch.ops.vc1d.prefill(x, w, None, None, None, None, 0, False, True, 0)
         assert st2.numel() == 0
-        dx, dw, db = torch.ops.vc1d.prefill_bwd(x, w, b, y, None, 1, True)
+        dx, dw, db, dinit = torch.ops.vc1d.prefill_bwd(x, w, b, y, None, None, 1, True)
+        assert dinit.numel() == 0
         assert dx.stride() == x.stride() and dw.shape == (64, 4) and dw.dtype == torch.float32 and db.shape == (64,)
         s = torch.empty(2, 64, 4, device="cuda", dtype=torch.bfloat16)
         assert torch.ops.vc1d.update(x[..., 0], s, w, b, None, 1, False).shape == (2, 64)

@@ -140,3 +140,41 @@ def test_initial_states_continue_a_sequence():
     y2, s2 = O.causal_conv1d_ref(x[..., 17:], w, None, "silu", initial_states=s1, state_len=4)
     assert torch.allclose(torch.cat([y1, y2], -1), y_full, rtol=1e-6, atol=1e-6)
     assert torch.equal(s2, s_full)
+
+
+def _pack_valid(x_btd, m):
+    """Right-padded [B,T,D] + mask [B,T] -> packed [1, sum(len), D], seq_idx [1, sum(len)], lengths."""
+    lens = [int(v) for v in (m != 0).sum(1)]
+    rows = [x_btd[b, :n] for b, n in enumerate(lens)]
+    ids = torch.cat([torch.full((n,), b, dtype=torch.int32) for b, n in enumerate(lens)])
+    return torch.cat(rows, 0).unsqueeze(0), ids.unsqueeze(0), lens
+
+
+RIGHT_PADDED = [c for c in GOLDEN_CASES if c.has("mask") and c.mask == "right"]
+
+
+@pytest.mark.parametrize("c", RIGHT_PADDED, ids=[repr(c) for c in RIGHT_PADDED])
+def test_packed_oracle_reproduces_reference_on_valid_positions(c):
+    """Packing the valid prefixes of a right-padded batch end to end and convolving with seq_idx gives,
+    at every valid position, what the reference's CanonLayer gives for the padded batch."""
+    x, w, b, m = _inputs(c)
+    act = "silu" if c.activation else None
+    xp, ids, lens = _pack_valid(x, m)
+    if xp.shape[1] == 0:
+        pytest.skip("no valid position")
+    yp = O.causal_conv1d_packed_ref(xp.transpose(1, 2), w, b, act, seq_idx=ids).transpose(1, 2)
+    ref = c.get("prefill_out")
+    at = 0
+    for bi, n in enumerate(lens):
+        out = x[bi, :n] + yp[0, at:at + n]
+        if c.dtype == torch.float32:
+            assert torch.allclose(out, ref[bi, :n], rtol=1e-5, atol=1e-6)
+        else:
+            assert torch.allclose(out.float(), ref[bi, :n].float(), rtol=2 ** -6, atol=2 ** -6)
+        at += n
+    # and bit for bit what the padded oracle computes there
+    ypad = O.causal_conv1d_ref(x.transpose(1, 2), w, b, act, attention_mask=m).transpose(1, 2)
+    at = 0
+    for bi, n in enumerate(lens):
+        assert_close_to_oracle(yp[0, at:at + n], ypad[bi, :n], f"sequence {bi}")
+        at += n

@@ -439,11 +439,17 @@ def test_config5_ragged_shard_properties():
     w, b = WL.weights(cfg.cfg, cfg.dim, cfg.width, cfg.dtype, device=DEV)
     y = V.causal_conv1d_fn(x.transpose(1, 2), w, b, activation="silu", attention_mask=m)
     lens = WL.sequence_lengths(cfg, rows)
-    # (1) sampled sequences vs the oracle
-    for i in (0, 17, 63):
-        ref = O.causal_conv1d_ref(x[i:i + 1].cpu().transpose(1, 2), w.cpu(), b.cpu(), "silu",
-                                  attention_mask=m[i:i + 1].cpu())
-        assert_close_to_oracle(y[i:i + 1], ref, f"cfg5 row {rows[i]} len {int(lens[i])}")
+    # (1) against the oracle: every sequence of up to 256 valid steps and the 8 longest ones, over their
+    # valid steps plus the width-1 steps behind them (what follows is checked as a constant in (2))
+    order = sorted(range(len(rows)), key=lambda i: int(lens[i]))
+    check = [i for i in order if int(lens[i]) <= 256] + order[-8:]
+    assert len(check) >= 20
+    wc, bc = w.cpu(), b.cpu()
+    for i in check:
+        n = min(cfg.seqlen, int(lens[i]) + cfg.width - 1)
+        ref = O.causal_conv1d_ref(x[i:i + 1, :n].cpu().transpose(1, 2), wc, bc, "silu",
+                                  attention_mask=m[i:i + 1, :n].cpu())
+        assert_close_to_oracle(y[i:i + 1, :, :n], ref, f"cfg5 row {rows[i]} len {int(lens[i])}")
     # (2) beyond len+W-1 every output is act(bias): constant along time
     const = torch.nn.functional.silu(b.float()).to(cfg.dtype)
     for i in range(len(rows)):
@@ -524,3 +530,111 @@ def test_tma_chunked_continuation_with_masks(dtype):
         t0 += n
     torch.cuda.synchronize()
     assert V.tma_timeouts() == 0
+
+
+def _mask_of_kind(kind, B, T, seed):
+    g = torch.Generator().manual_seed(seed)
+    if kind == "right":
+        lens = torch.randint(1, T + 1, (B,), generator=g)
+        lens[0], lens[1] = T, 3
+        return torch.arange(T)[None, :] < lens[:, None]
+    if kind == "left":
+        lens = torch.randint(1, T + 1, (B,), generator=g)
+        return torch.arange(T)[None, :] >= (T - lens)[:, None]
+    if kind == "holes":
+        m = torch.rand(B, T, generator=g) > 0.02
+        m[2, 100:400] = False  # a stretch long enough to hold tiles without any live tap
+        return m
+    if kind == "zeros":
+        return torch.zeros(B, T, dtype=torch.bool)
+    return torch.ones(B, T, dtype=torch.bool)
+
+
+@pytest.mark.parametrize("tma", [dict(empty_store=1), dict(empty_store=2), dict(classify=2), dict(static_first=3),
+                                 dict(claim_chunk=2), dict(claim_chunk=4, empty_store=1),
+                                 dict(classify=2, static_first=2, pdl=2), dict(rows_per_thread=4, empty_store=2)],
+                         ids=lambda d: ",".join(f"{k}={v}" for k, v in d.items()))
+@pytest.mark.parametrize("mask_kind", ["right", "left", "holes", "zeros", "ones"])
+@pytest.mark.parametrize("mask_dtype", [torch.bool, torch.int64])
+def test_tma_scheduling_variants_agree(mask_dtype, mask_kind, tma):
+    """Every way the TMA-staged kernel can hand out, classify and store its tiles gives the bits of the
+    register-window kernel: bulk-stored or consumer-stored constant tiles, tile classes from the
+    pre-pass or worked out inside the kernel, chunked claims, unclaimed first tiles.  The shape has a
+    last time tile that is not full and a last channel slab that is half outside the tensor."""
+    B, T, D, W = 20, 1008, 1160, 4
+    x = O.seeded((B, T, D), 77, "normal", torch.bfloat16)
+    w = O.seeded((D, W), 78, "uniform", torch.bfloat16)
+    b = O.seeded((D,), 79, "uniform", torch.bfloat16)
+    m = _mask_of_kind(mask_kind, B, T, 80).to(mask_dtype)
+    xd, wd, bd, md = dev(x).transpose(1, 2), dev(w), dev(b), dev(m)
+    ref = V.causal_conv1d_fn(xd, wd, bd, activation="silu", attention_mask=md, kernel="channel_last")
+    before = V.launch_count()
+    y = V.causal_conv1d_fn(xd, wd, bd, activation="silu", attention_mask=md, kernel="tma", tma=tma,
+                           dynamic_schedule=True)
+    assert V.last_kernel() == "tma"
+    if tma.get("classify") == 2 and mask_dtype == torch.bool:
+        assert V.launch_count() - before == 1, "the kernel classifies its tiles itself: no pre-pass launch"
+    assert torch.equal(y, ref)
+    # twice more on the same stream: the scratch counters were left zeroed
+    for _ in range(2):
+        y2 = V.causal_conv1d_fn(xd, wd, bd, activation="silu", attention_mask=md, kernel="tma", tma=tma,
+                                dynamic_schedule=True)
+        assert torch.equal(y2, ref)
+    torch.cuda.synchronize()
+    assert V.tma_timeouts() == 0
+
+
+def test_tma_class_table_of_a_very_long_batch():
+    """More tiles than the byte-per-tile class table a CTA keeps in shared memory (16384): the table
+    is kept at two bits per tile.  19200 tiles here; against the register-window kernel."""
+    B, T, D = 300, 4096, 256
+    g = torch.Generator(device=DEV).manual_seed(3)
+    x = torch.randn(B, T, D, generator=g, device=DEV).bfloat16()
+    w = dev(O.seeded((D, 4), 5, "uniform", torch.bfloat16))
+    b = dev(O.seeded((D,), 6, "uniform", torch.bfloat16))
+    lens = torch.randint(1, T + 1, (B,), generator=torch.Generator().manual_seed(4))
+    m = (torch.arange(T)[None, :] < lens[:, None]).to(DEV)
+    m[5, 50:700] = False
+    ref = V.causal_conv1d_fn(x.transpose(1, 2), w, b, activation="silu", attention_mask=m, kernel="channel_last")
+    before = V.launch_count()
+    y = V.causal_conv1d_fn(x.transpose(1, 2), w, b, activation="silu", attention_mask=m, kernel="tma")
+    assert V.launch_count() - before == 2 and V.last_kernel() == "tma"
+    assert torch.equal(y, ref)
+    torch.cuda.synchronize()
+    assert V.tma_timeouts() == 0
+
+
+def test_bounded_waits_expire_and_report():
+    """Failure detection of the TMA-staged kernel, provoked without faulting anything: with the
+    self-test switch every producer warp withholds its first tile and every wait polls only 4096 times,
+    so the consumers' wait for that tile (and then the producer's wait for the slot) runs out.  The
+    kernel must come back normally, the device counter read by tma_timeouts() must have grown, and
+    the next ordinary launch must be clean and correct.  Runs in a child process: the counter is
+    cumulative, and every other test asserts that it is still zero."""
+    import subprocess
+    import sys
+
+    code = r'''
+import torch
+import viby_model_b200 as V
+dev = "cuda"
+g = torch.Generator().manual_seed(1)
+x = torch.randn(8, 512, 1152, generator=g).bfloat16().to(dev)
+w = (torch.rand(1152, 4, generator=g) - 0.5).bfloat16().to(dev)
+m = (torch.arange(512)[None, :] < torch.randint(1, 513, (8,), generator=g)[:, None]).to(dev)
+ref = V.causal_conv1d_fn(x.transpose(1, 2), w, None, activation="silu", attention_mask=m, kernel="channel_last")
+assert V.tma_timeouts() == 0
+V.causal_conv1d_fn(x.transpose(1, 2), w, None, activation="silu", attention_mask=m, kernel="tma", tma=dict(test_expire=1))
+torch.cuda.synchronize()          # the launch returns: nothing hangs, nothing traps
+expired = V.tma_timeouts()
+assert expired > 0, "the expired waits were not reported"
+y = V.causal_conv1d_fn(x.transpose(1, 2), w, None, activation="silu", attention_mask=m, kernel="tma")
+torch.cuda.synchronize()
+assert V.tma_timeouts() == expired, "an ordinary launch after the self-test reported expired waits"
+assert torch.equal(y, ref)
+print("EXPIRED", expired)
+'''
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300,
+                       cwd=str(__import__("conftest").ROOT))
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "EXPIRED" in r.stdout

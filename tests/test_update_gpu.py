@@ -18,6 +18,19 @@ def bits(t):
     return t.view(torch.int32 if t.dtype == torch.float32 else torch.int16)
 
 
+def expected_kernel(dtype, L, kernel=None, circular=False):
+    """State rows of 16 or 32 bytes (and every such circular state) take the one-channel-per-lane
+    kernel, other short shifting states the 8-channels-per-thread kernel, the rest the scalar one."""
+    if kernel == "generic":
+        return "update_generic"
+    row_bytes = L * (4 if dtype == torch.float32 else 2)
+    if row_bytes in (16, 32) and not (dtype == torch.float32 and L == 4 and not circular):
+        return "update_lane"
+    if circular or L not in (1, 2, 3, 4, 8):
+        return "update_generic"
+    return "update_vec"
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("W", [2, 3, 4])
 @pytest.mark.parametrize("L", [1, 2, 3, 4, 5, 8, 11])
@@ -40,8 +53,7 @@ def test_update_steps(dtype, W, L, kernel):
         ref = O.causal_conv1d_update_ref(xt, state, w, b, "silu")
         assert_close_to_oracle(y, ref, f"step {step}")
         assert torch.equal(bits(sd.cpu()), bits(state)), f"state after step {step}"
-    expect = "update_generic" if (kernel == "generic" or L not in (1, 2, 3, 4, 8)) else "update_vec"
-    assert V.last_kernel() == expect
+    assert V.last_kernel() == expected_kernel(dtype, L, kernel)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -53,7 +65,9 @@ def test_update_odd_dim_and_no_bias_no_activation(dtype):
     sd = state.to(DEV)
     xt = torch.randn(B, D, generator=g).to(dtype)
     y = V.causal_conv1d_update(xt.to(DEV), sd, w.to(DEV))
-    assert V.last_kernel() == "update_generic"
+    # 21 channels are no multiple of a 128-bit vector: fp32 rows of 16 bytes still take the
+    # one-channel-per-lane kernel, bf16 rows of 8 bytes the scalar one
+    assert V.last_kernel() == ("update_lane" if dtype == torch.float32 else "update_generic")
     assert_close_to_oracle(y, O.causal_conv1d_update_ref(xt, state, w))
     assert torch.equal(bits(sd.cpu()), bits(state))
 
@@ -92,22 +106,23 @@ def test_update_accepts_trailing_singleton_and_strided_x():
     assert torch.equal(bits(sd.cpu()), bits(state))
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_circular_state_update(dtype):
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("W,L,D", [(4, 8, 32), (4, 8, 1001), (3, 8, 64), (2, 16, 40), (4, 4, 48), (4, 5, 32), (3, 2, 32)])
+def test_circular_state_update(dtype, W, L, D):
     """cache_seqlens mode (causal_conv1d.metal:586-664), per-sequence write positions."""
-    B, D, W, L = 4, 32, 4, 8
+    B = 5
     g = torch.Generator().manual_seed(17)
     w = (torch.rand(D, W, generator=g) - 0.5).to(dtype)
     b = (torch.rand(D, generator=g) - 0.5).to(dtype)
     state = torch.randn(B, D, L, generator=g).to(dtype)
-    seqlens = torch.tensor([0, 3, 7, 12], dtype=torch.int32)
+    seqlens = torch.tensor([0, 3, 7, 12, 1000003], dtype=torch.int32)
     sd = state.to(DEV)
     for step in range(10):
         xt = torch.randn(B, D, generator=g).to(dtype)
         y = V.causal_conv1d_update(xt.to(DEV), sd, w.to(DEV), b.to(DEV), activation="silu",
                                    cache_seqlens=seqlens.to(DEV), residual=True)
         ref = O.causal_conv1d_update_ref(xt, state, w, b, "silu", cache_seqlens=seqlens, residual=True)
-        assert V.last_kernel() == "update_generic"
+        assert V.last_kernel() == expected_kernel(dtype, L, circular=True)
         assert_close_to_oracle(y, ref, f"circular step {step}")
         assert torch.equal(bits(sd.cpu()), bits(state))
         seqlens = seqlens + 1
@@ -158,7 +173,7 @@ def test_config3_decode_1024_steps(L):
     for s in range(cfg.steps):
         V.causal_conv1d_update(toks_d[s], st, wd, bd, out=ys[s])
     assert V.launch_count() == before + cfg.steps
-    assert V.last_kernel() == "update_vec"
+    assert V.last_kernel() == expected_kernel(cfg.dtype, L)
     ys = ys.cpu()
     for s in range(cfg.steps):
         ref = O.causal_conv1d_update_ref(toks[s], ref_state, w, b)

@@ -50,8 +50,15 @@ def make(B, T, D, W, dtype, seed):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("masked", [True, False])
 def test_noalloc_matches_prefill_twice_in_a_row(dtype, masked):
+    from oracle import canon_oracle as O
+    from parity import assert_close_to_oracle
+
     stream = torch.cuda.current_stream(DEV).cuda_stream
-    shapes = [(6, 777, 1152, 4), (3, 2048, 256, 3)]  # different slab counts share the one array
+    # Shapes that give every CTA of the kernel several tiles, so that it claims them from the counters
+    # in the library's array (and, with a mask, reads the class bytes a pre-pass kernel wrote there):
+    # different slab counts share the one array.  The last shape is too small for that and runs with
+    # static assignment, the array untouched.
+    shapes = [(32, 1024, 3456, 4), (16, 2048, 1152, 3), (6, 777, 1152, 4)]
     for rep in range(2):
         for i, (B, T, D, W) in enumerate(shapes):
             x, w, b, mask = make(B, T, D, W, dtype, seed=17 * rep + i)
@@ -65,7 +72,12 @@ def test_noalloc_matches_prefill_twice_in_a_row(dtype, masked):
             torch.cuda.synchronize()
             free_before, _ = torch.cuda.mem_get_info(DEV)
             # two calls in a row: the second finds the array as the first left it
+            launches = _cabi.launch_count()
             assert _cabi.lib.vc1d_prefill_noalloc(C.byref(a_new), stream) == 0
+            if i < 2:
+                # the tile-classification pre-pass ran before the main kernel: its class bytes, and the claim
+                # counters beside them, live in the library's array
+                assert _cabi.launch_count() - launches == (2 if masked else 1)
             y_first = y_new.clone()
             y_new.fill_(float("nan"))
             assert _cabi.lib.vc1d_prefill_noalloc(C.byref(a_new), stream) == 0
@@ -73,6 +85,11 @@ def test_noalloc_matches_prefill_twice_in_a_row(dtype, masked):
             assert torch.equal(y_first, y_ref)
             assert torch.equal(y_new, y_ref)
             assert not torch.isnan(y_ref).any()
+            if rep == 0:
+                # and against the CPU oracle directly, on the first two sequences
+                ref = O.causal_conv1d_ref(x[:2].cpu().transpose(1, 2), w.cpu(), b.cpu(), "silu",
+                                          attention_mask=None if m is None else m[:2].cpu())
+                assert_close_to_oracle(y_new[:2].transpose(1, 2), ref, f"noalloc {B}x{T}x{D}")
             if rep == 1:
                 # set-up happened in the first round; y_first's clone is the only allocation since
                 free_after, _ = torch.cuda.mem_get_info(DEV)

@@ -14,6 +14,10 @@ Canon modes:
   "torch"     the reference's CUDA-branch semantics (unmasked prefill residual, masked decode
               residual, kernel_size-column state) with torch ops on the tensor's own device
   "kernel"    the same semantics through viby_model_b200 (fused mask / residual / final state)
+  "kernel_plain"  the kernels called exactly as the reference's CUDA branch calls them
+              (model/model.py:454-491 and 299-313): through the drop-in module ``causal_conv1d``, keyword
+              arguments ``x=, weight=, bias=, activation=, seq_idx=None`` / ``x=, conv_state=, ...``, with
+              the mask multiply, the state seeding and the residual left to torch ops around the call
 """
 from __future__ import annotations
 
@@ -47,7 +51,8 @@ class VibyHarness:
         self.hd = cfg["hidden_size"] // cfg["num_attention_heads"]
         dev = params["model.embed_tokens.weight"].device
         self.cos, self.sin = rope_tables(self.hd, cfg.get("max_positions", 4096), cfg["rope_theta"], dev)
-        self.canon_inputs = None  # set to a list to record (name, layer, x, mask, y) of every prefill Canon call
+        # set to a list to record (name, layer, x, mask, out, conv term or None) of every prefill Canon call
+        self.canon_inputs = None
 
     # ---- Canon layer ------------------------------------------------------------------------------
     def _canon(self, x, name, layer, mask, cache):
@@ -79,6 +84,11 @@ class VibyHarness:
                 import viby_model_b200 as V
 
                 y = V.causal_conv1d_update(xt, state, w, b, activation="silu" if act else None)
+            elif self.canon == "kernel_plain":
+                import causal_conv1d as CC
+
+                y = CC.causal_conv1d_update(x=xt, conv_state=state, weight=w, bias=b,
+                                            activation="silu" if act else None)  # model/model.py:305-311
             else:
                 cat = torch.cat([state, xt.unsqueeze(-1)], -1)
                 y = (cat[..., -K:].float() * w.float()).sum(-1)
@@ -103,6 +113,22 @@ class VibyHarness:
             else:
                 y = res
             out = y.transpose(1, 2)
+        elif self.canon == "kernel_plain":
+            import causal_conv1d as CC
+
+            xm = x * m.unsqueeze(-1).to(x.dtype) if m is not None else x            # model/model.py:454-457
+            y = CC.causal_conv1d_fn(x=xm.transpose(1, 2), weight=w, bias=b, activation="silu" if act else None,
+                                    seq_idx=None)                                    # :460-466
+            conv_term = y.transpose(1, 2)
+            out = x + conv_term                                                       # :491
+            if cache is not None:                                                     # :470-489
+                st = torch.zeros(B, D, K, dtype=x.dtype, device=x.device)
+                n = min(T, K)
+                st[..., K - n:] = xm.transpose(1, 2)[..., T - n:]
+                cache["canon"][key] = st
+            if self.canon_inputs is not None:
+                self.canon_inputs.append((name, layer, x, m, out, conv_term))
+            return out
         else:
             xm = x * m.unsqueeze(-1).to(x.dtype) if m is not None else x
             conv = F.conv1d(F.pad(xm.transpose(1, 2).float(), (K - 1, 0)), w.float().unsqueeze(1),
@@ -116,7 +142,7 @@ class VibyHarness:
                 st[..., K - n:] = xm.transpose(1, 2)[..., T - n:]
                 cache["canon"][key] = st
         if self.canon_inputs is not None:
-            self.canon_inputs.append((name, layer, x, m, out))
+            self.canon_inputs.append((name, layer, x, m, out, None))
         return out
 
     # ---- attention ----------------------------------------------------------------------------------

@@ -14,9 +14,9 @@ The operators call hand-written CUDA kernels through the C ABI of include/vc1d.h
 (libvc1d.so, built by ``python viby_model_b200/build.py``).  Importing the package without
 that library raises ImportError: there is no CPU or PyTorch fallback.
 """
-from ._cabi import last_kernel, launch_count, library_path, tma_timeouts
+from ._cabi import last_kernel, launch_count, library_path, set_pdl, tma_timeouts
 from .ops import (causal_conv1d_bwd, causal_conv1d_fn, causal_conv1d_fn_multi, causal_conv1d_update,
-                  causal_conv1d_update_bwd)
+                  causal_conv1d_update_bwd, seq_idx_from_lengths)
 from .short_conv import causal_conv1d_fwd, short_conv_fused, short_conv_update
 from . import compile_ops  # noqa: F401  (registers torch.ops.vc1d.* for torch.compile)
 
@@ -25,6 +25,7 @@ __all__ = [
     "causal_conv1d_update",
     "causal_conv1d_bwd",
     "causal_conv1d_fn_multi",
+    "seq_idx_from_lengths",
     "causal_conv1d_update_bwd",
     "causal_conv1d_fwd",
     "short_conv_fused",
@@ -33,5 +34,6 @@ __all__ = [
     "last_kernel",
     "library_path",
     "tma_timeouts",
+    "set_pdl",
 ]
 __version__ = "0.1.0"

@@ -79,6 +79,15 @@ class PrefillArgs(C.Structure):
         ("tma_rows_per_thread", C.c_int32),
         ("scratch", C.c_void_p),
         ("scratch_bytes", C.c_int64),
+        ("seq_idx", C.c_void_p),
+        ("seq_stride_b", C.c_int64),
+        ("seq_stride_t", C.c_int64),
+        ("tma_claim_chunk", C.c_int32),
+        ("tma_empty_store", C.c_int32),
+        ("tma_classify", C.c_int32),
+        ("tma_pdl", C.c_int32),
+        ("tma_static_first", C.c_int32),
+        ("tma_test_expire", C.c_int32),
     ]
 
 
@@ -120,13 +129,13 @@ class PrefillBwdArgs(C.Structure):
         ("kernel", C.c_int32),
         ("tma_stages", C.c_int32),
         ("tma_ctas_per_sm", C.c_int32),
-        ("reserved", C.c_int32),
+        ("tma_variant", C.c_int32),
         ("scratch", C.c_void_p),
         ("scratch_bytes", C.c_int64),
         ("initial_state", C.c_void_p),
         ("dinitial_state", C.c_void_p),
         ("init_len", C.c_int32),
-        ("reserved2", C.c_int32),
+        ("zero_grads", C.c_int32),
     ]
 
 
@@ -218,6 +227,7 @@ EXPORTS = {
     "vc1d_launch_count": (C.c_uint64, []),
     "vc1d_last_kernel": (C.c_char_p, []),
     "vc1d_tma_timeouts": (C.c_uint, []),
+    "vc1d_set_pdl": (C.c_int, [C.c_int]),
 }
 
 
@@ -269,6 +279,12 @@ def launch_count() -> int:
 
 def last_kernel() -> str:
     return lib.vc1d_last_kernel().decode()
+
+
+def set_pdl(enabled) -> bool:
+    """Programmatic dependent launch between the library's kernels: True / False, or None to follow the
+    environment (VC1D_NO_PDL).  Returns the previous setting."""
+    return bool(lib.vc1d_set_pdl(-1 if enabled is None else int(bool(enabled))))
 
 
 def tma_timeouts() -> int:

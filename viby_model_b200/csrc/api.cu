@@ -24,12 +24,17 @@ int sm_count() {
     return n;
 }
 
+namespace {
+std::atomic<int> g_pdl_override{-1};  // -1: follow the environment; 0 / 1: set by vc1d_set_pdl
+}
+
 bool pdl_enabled() {
-    static const bool on = [] {
+    static const bool env_on = [] {
         const char* v = std::getenv("VC1D_NO_PDL");
         return !(v != nullptr && v[0] == '1');
     }();
-    return on;
+    const int o = g_pdl_override.load(std::memory_order_relaxed);
+    return o < 0 ? env_on : (o != 0);
 }
 
 void note_launch(const char* kernel_name) {
@@ -80,6 +85,8 @@ int check_prefill(const vc1d_prefill_args* a) {
     if (a->initial_state != nullptr && a->init_len < a->width - 1) return VC1D_E_SHAPE;
     if (a->final_state != nullptr && a->state_len < 1) return VC1D_E_SHAPE;
     if (a->kernel < VC1D_KERNEL_AUTO || a->kernel > VC1D_KERNEL_TMA) return VC1D_E_SHAPE;
+    if (a->seq_idx != nullptr && (a->mask != nullptr || a->initial_state != nullptr || a->final_state != nullptr))
+        return VC1D_E_SHAPE;
     const long long n = (long long)a->batch * a->dim * a->seqlen;
     if (n == 0) return VC1D_OK;
     if (a->x == nullptr || a->y == nullptr || a->weight == nullptr) return VC1D_E_NULL;
@@ -186,6 +193,18 @@ bool update_vec_ok(const vc1d_update_args* a) {
     return true;
 }
 
+// one channel per lane: state rows of 16 or 32 bytes; takes the circular state and the 8-column states
+bool update_lane_ok(const vc1d_update_args* a) {
+    const int eb = elem_bytes(a->dtype);
+    if (!update_lane_supports(a->dtype, a->state_len, a->width)) return false;
+    if (a->x_stride_d != 1 || a->y_stride_d != 1) return false;
+    if (a->s_stride_l != 1 || a->s_stride_d != a->state_len) return false;
+    if (!aligned16(a->conv_state) || (a->s_stride_b * eb) % 16 != 0) return false;
+    // the 128-bit-per-8-channels kernel keeps the short shifting states
+    if (a->cache_seqlens == nullptr && a->state_len * eb == 16 && eb == 4 && update_vec_ok(a)) return false;
+    return true;
+}
+
 }  // namespace
 }  // namespace vc1d
 
@@ -200,6 +219,18 @@ VC1D_API int vc1d_prefill(const vc1d_prefill_args* a, void* stream) {
     const bool cl = channel_last_ok(a);
     const bool tm = time_major_ok(a);
     cudaError_t err;
+    if (a->seq_idx != nullptr) {
+        // packed rows: the TMA-staged kernel when it applies, else the scalar kernel
+        if (a->kernel == VC1D_KERNEL_CHANNEL_LAST || a->kernel == VC1D_KERNEL_TIME_MAJOR) return VC1D_E_STRIDE;
+        if (a->kernel == VC1D_KERNEL_TMA && (!cl || !tma_available())) return VC1D_E_STRIDE;
+        const long long elems = (long long)a->batch * a->dim * a->seqlen;
+        err = cudaErrorNotSupported;
+        if (a->kernel != VC1D_KERNEL_GENERIC && cl && tma_available() &&
+            (a->kernel == VC1D_KERNEL_TMA || (a->seqlen >= 16 && elems >= (1LL << 20))))
+            err = launch_prefill_tma(*a, s);
+        if (err == cudaErrorNotSupported && a->kernel != VC1D_KERNEL_TMA) err = launch_prefill_generic(*a, s);
+        return (int)err;
+    }
     switch (a->kernel) {
         case VC1D_KERNEL_CHANNEL_LAST:
             if (!cl) return VC1D_E_STRIDE;
@@ -240,8 +271,18 @@ VC1D_API int vc1d_prefill_bwd(const vc1d_prefill_bwd_args* a, void* stream) {
     using namespace vc1d;
     const int st = check_prefill_bwd(a);
     if (st != VC1D_OK) return st;
-    if ((long long)a->batch * a->dim * a->seqlen == 0) return VC1D_OK;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if ((long long)a->batch * a->dim * a->seqlen == 0) {
+        // nothing to sum: the gradients of the parameters are zero
+        if (a->zero_grads && a->dim > 0) {
+            cudaError_t e = a->dweight != nullptr
+                                ? cudaMemsetAsync(a->dweight, 0, sizeof(float) * (size_t)a->dim * a->width, s)
+                                : cudaSuccess;
+            if (e == cudaSuccess && a->dbias != nullptr) e = cudaMemsetAsync(a->dbias, 0, sizeof(float) * (size_t)a->dim, s);
+            return (int)e;
+        }
+        return VC1D_OK;
+    }
     const bool cl = bwd_channel_last_ok(a);
     cudaError_t err;
     switch (a->kernel) {
@@ -273,7 +314,9 @@ VC1D_API int vc1d_update(const vc1d_update_args* a, void* stream) {
     if ((long long)a->batch * a->dim == 0) return VC1D_OK;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     cudaError_t err;
-    if (a->kernel == VC1D_KERNEL_AUTO && update_vec_ok(a))
+    if (a->kernel == VC1D_KERNEL_AUTO && update_lane_ok(a))
+        err = launch_update_lane(*a, s);
+    else if (a->kernel == VC1D_KERNEL_AUTO && update_vec_ok(a))
         err = launch_update_vec(*a, s);
     else
         err = launch_update_generic(*a, s);
@@ -324,5 +367,11 @@ VC1D_API uint64_t vc1d_launch_count(void) { return vc1d::g_launches.load(std::me
 VC1D_API const char* vc1d_last_kernel(void) { return vc1d::t_last_kernel; }
 
 VC1D_API unsigned int vc1d_tma_timeouts(void) { return vc1d::tma_timeouts(); }
+
+VC1D_API int vc1d_set_pdl(int enabled) {
+    const int before = vc1d::pdl_enabled() ? 1 : 0;
+    vc1d::g_pdl_override.store(enabled < 0 ? -1 : (enabled != 0 ? 1 : 0), std::memory_order_relaxed);
+    return before;
+}
 
 }  // extern "C"

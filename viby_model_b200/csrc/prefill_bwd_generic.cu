@@ -181,6 +181,12 @@ cudaError_t launch_prefill_bwd_generic(const vc1d_prefill_bwd_args& a, cudaStrea
     const long long n_items = (long long)a.batch * p.n_chunks;
     const dim3 block(128);
     const dim3 grid((unsigned)((a.dim + 127) / 128), (unsigned)(n_items < 65535 ? n_items : 65535));
+    if (a.zero_grads) {
+        cudaError_t e = a.dweight != nullptr ? cudaMemsetAsync(a.dweight, 0, sizeof(float) * (size_t)a.dim * a.width, s)
+                                             : cudaSuccess;
+        if (e == cudaSuccess && a.dbias != nullptr) e = cudaMemsetAsync(a.dbias, 0, sizeof(float) * (size_t)a.dim, s);
+        if (e != cudaSuccess) return e;
+    }
     note_launch("bwd_generic");
     switch (a.dtype) {
         case VC1D_F32: k_prefill_bwd_generic<VC1D_F32><<<grid, block, 0, s>>>(p); break;

@@ -45,11 +45,16 @@ struct BwdParams {
     int stages;
 };
 
-template <int DT, int W, int SLAB_BYTES>
+// VARIANT 0: a thread owns 8 bytes of channels and 8 consecutive rows.  VARIANT 1 (16-bit I/O): 4
+// bytes of channels (one pair) and 8 rows, so a tile is half as tall and a third CTA fits an SM.
+// VARIANT 2 (16-bit I/O): 4 bytes of channels and 16 rows: tiles as tall as variant 0, three CTAs per
+// SM with a two-stage ring, and the W-1 rows of g below a thread's own rows, which it has to work
+// out a second time, are spread over 16 rows instead of 8.
+template <int DT, int W, int SLAB_BYTES, int VARIANT = 0>
 struct BwdGeometry {
-    static constexpr int kVB = 8;
+    static constexpr int kVB = (VARIANT == 0) ? 8 : 4;
     static constexpr int kH = W - 1;
-    static constexpr int kRows = 8;
+    static constexpr int kRows = (VARIANT == 2) ? 16 : 8;
     static constexpr int kLanesPerRow = SLAB_BYTES / kVB;
     static constexpr int kConsumerWarps = 8;
     static constexpr int kConsumerThreads = kConsumerWarps * 32;
@@ -65,8 +70,8 @@ struct BwdGeometry {
     static constexpr int kStageBytes = kXBytes + kGBytes;  // rows are 128 or 256 bytes: stays 128-byte aligned
     // fp32 I/O (one channel pair per thread) fits 72 registers: 3 CTAs per SM with a 2-stage ring.  16-bit I/O
     // (two pairs) needs 96: 2 CTAs per SM with 3 stages; squeezed to 72 it spills and runs at half the speed.
-    static constexpr int kCtasPerSm = (DT == VC1D_F32) ? 3 : 2;
-    static constexpr int kDefaultStages = (DT == VC1D_F32) ? 2 : 3;
+    static constexpr int kCtasPerSm = (DT == VC1D_F32 || VARIANT != 0) ? 3 : 2;
+    static constexpr int kDefaultStages = ((DT == VC1D_F32 && VARIANT == 0) || VARIANT == 2) ? 2 : 3;
     // layout for S stages: stages | full[S], done[S] | tile descriptor[S]
     __host__ __device__ static constexpr int off_bars(int S) { return S * kStageBytes; }
     __host__ __device__ static constexpr int off_flags(int S) { return off_bars(S) + 2 * S * 8; }
@@ -104,12 +109,13 @@ __device__ __forceinline__ void named_barrier_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-template <int DT, int W, int SLAB_BYTES, bool ACT>
-__global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES>::kThreads, BwdGeometry<DT, W, SLAB_BYTES>::kCtasPerSm)
+template <int DT, int W, int SLAB_BYTES, bool ACT, int VARIANT = 0>
+__global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES, VARIANT>::kThreads,
+                                  BwdGeometry<DT, W, SLAB_BYTES, VARIANT>::kCtasPerSm)
     k_prefill_bwd_tma(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_g,
                       const BwdParams p) {
     using E = Elem<DT>;
-    using G = BwdGeometry<DT, W, SLAB_BYTES>;
+    using G = BwdGeometry<DT, W, SLAB_BYTES, VARIANT>;
     constexpr int VB = G::kVB;
     using S = Slice<DT, VB>;
     constexpr int NE = S::kElems;
@@ -239,7 +245,7 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES>::kThreads, BwdG
     float2 wp[W][NP];
     float2 bp[NP];
     {
-        TmaParams wparams;  // load_weights reads these fields only
+        TmaParams wparams = {};  // load_weights reads these fields only
         wparams.weight = p.weight;
         wparams.bias = p.bias;
         wparams.wsd = p.wsd;
@@ -292,7 +298,7 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES>::kThreads, BwdG
         if (cls == TILE_MIXED) {  // only mixed tiles look at their mask rows
             const int b = lds_s32(flags + 32 * s + 16);
             const int tfirst = lds_s32(flags + 32 * s + 20) + rbase;
-            TmaParams mp;
+            TmaParams mp = {};
             mp.mask = p.mask;
             mp.smt = p.smt;
             mp.mask_dtype = p.mask_dtype;
@@ -442,9 +448,9 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES>::kThreads, BwdG
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-template <int DT, int W, int SLAB_BYTES, bool ACT>
+template <int DT, int W, int SLAB_BYTES, bool ACT, int VARIANT = 0>
 cudaError_t launch_bwd_kernel(const vc1d_prefill_bwd_args& a, const BwdParams& base, cudaStream_t s) {
-    using G = BwdGeometry<DT, W, SLAB_BYTES>;
+    using G = BwdGeometry<DT, W, SLAB_BYTES, VARIANT>;
     const int eb = Elem<DT>::kBytes;
     BwdParams p = base;
     const int slab_ch = G::kSlabElems;
@@ -497,7 +503,7 @@ cudaError_t launch_bwd_kernel(const vc1d_prefill_bwd_args& a, const BwdParams& b
         int dev = 0;
         cudaGetDevice(&dev);
         if (dev < 0 || dev >= 64 || granted[dev].load(std::memory_order_acquire) < smem) {
-            const cudaError_t e = cudaFuncSetAttribute(k_prefill_bwd_tma<DT, W, SLAB_BYTES, ACT>,
+            const cudaError_t e = cudaFuncSetAttribute(k_prefill_bwd_tma<DT, W, SLAB_BYTES, ACT, VARIANT>,
                                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
             if (e != cudaSuccess) return e == cudaErrorInvalidValue ? cudaErrorNotSupported : e;
             if (dev >= 0 && dev < 64) granted[dev].store(smem, std::memory_order_release);
@@ -505,11 +511,16 @@ cudaError_t launch_bwd_kernel(const vc1d_prefill_bwd_args& a, const BwdParams& b
     }
     p.sched = nullptr;
     p.gtable = nullptr;
+    // gradient accumulators the caller asked the library to clear: by the pre-pass when there is one
+    // (no extra launch), else by memsets on the stream
+    bool zero_pending = a.zero_grads != 0;
+    const int n_dw = a.dweight != nullptr ? a.dim * a.width : 0;
+    const int n_db = a.dbias != nullptr ? a.dim : 0;
     if (use_sched) {
         p.sched = reinterpret_cast<unsigned int*>(a.scratch);
         if (a.mask != nullptr && a.scratch_bytes >= kSchedCounterBytes + n_rowtiles) {
             // class of every tile from its R + 2H mask rows (pre-pass shared with the forward kernel)
-            TmaParams cp;
+            TmaParams cp = {};
             cp.mask = a.mask;
             cp.smb = a.mask_stride_b;
             cp.smt = a.mask_stride_t;
@@ -522,13 +533,20 @@ cudaError_t launch_bwd_kernel(const vc1d_prefill_bwd_args& a, const BwdParams& b
             cp.init = nullptr;
             unsigned char* tab = reinterpret_cast<unsigned char*>(a.scratch) + kSchedCounterBytes;
             const long long threads = n_rowtiles * 32;
-            k_classify_tiles<<<(unsigned)((threads + 255) / 256), 256, 0, s>>>(cp, tab, (int)G::kTileRows, (int)G::kH,
-                                                                             (int)G::kXRows);
+            k_classify_tiles<<<(unsigned)((threads + 255) / 256), 256, 0, s>>>(
+                cp, tab, (int)G::kTileRows, (int)G::kH, (int)G::kXRows, zero_pending ? a.dweight : nullptr,
+                zero_pending ? n_dw : 0, zero_pending ? a.dbias : nullptr, zero_pending ? n_db : 0);
             const cudaError_t e = cudaGetLastError();
             if (e != cudaSuccess) return e;
+            zero_pending = false;
             note_launch("classify");
             p.gtable = tab;
         }
+    }
+    if (zero_pending) {
+        cudaError_t e = n_dw > 0 ? cudaMemsetAsync(a.dweight, 0, sizeof(float) * (size_t)n_dw, s) : cudaSuccess;
+        if (e == cudaSuccess && n_db > 0) e = cudaMemsetAsync(a.dbias, 0, sizeof(float) * (size_t)n_db, s);
+        if (e != cudaSuccess) return e;
     }
     note_launch("bwd_tma");
     // after a pre-pass the main kernel is its programmatic dependent: its launch and prologue overlap it
@@ -542,7 +560,7 @@ cudaError_t launch_bwd_kernel(const vc1d_prefill_bwd_args& a, const BwdParams& b
     cfg.stream = s;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, k_prefill_bwd_tma<DT, W, SLAB_BYTES, ACT>, tmap_x, tmap_g, p);
+    return cudaLaunchKernelEx(&cfg, k_prefill_bwd_tma<DT, W, SLAB_BYTES, ACT, VARIANT>, tmap_x, tmap_g, p);
 }
 
 template <int DT, int W>
@@ -551,6 +569,16 @@ cudaError_t launch_bwd_w(const vc1d_prefill_bwd_args& a, const BwdParams& p, cud
     const int wide = 256 / eb, narrow = 128 / eb;
     const bool use_wide = (a.dim % wide == 0) || (a.dim % narrow != 0);
     const bool act = a.activation == VC1D_ACT_SILU;
+    if constexpr (DT != VC1D_F32) {
+        // 16-bit I/O, full-width slabs: one channel pair per thread (see BwdGeometry).  With SiLU the
+        // kernel is bound by instruction issue and 16 rows per thread save the most work; without it 8
+        // rows per thread measured fastest.
+        const int variant = a.tma_variant != 0 ? a.tma_variant : (act ? 3 : 2);
+        if (use_wide && variant == 2)
+            return act ? launch_bwd_kernel<DT, W, 256, true, 1>(a, p, s) : launch_bwd_kernel<DT, W, 256, false, 1>(a, p, s);
+        if (use_wide && variant == 3)
+            return act ? launch_bwd_kernel<DT, W, 256, true, 2>(a, p, s) : launch_bwd_kernel<DT, W, 256, false, 2>(a, p, s);
+    }
     if (use_wide)
         return act ? launch_bwd_kernel<DT, W, 256, true>(a, p, s) : launch_bwd_kernel<DT, W, 256, false>(a, p, s);
     return act ? launch_bwd_kernel<DT, W, 128, true>(a, p, s) : launch_bwd_kernel<DT, W, 128, false>(a, p, s);

@@ -16,7 +16,9 @@ struct GParams {
     const void* bias;
     const void* mask;
     const void* init;
+    const int* seq;  // sequence id of every time step (packed variable-length rows), or NULL
     void* fstate;
+    long long ssb, sst;
     long long sxb, sxd, sxt;  // elements
     long long syb, syd, syt;
     long long srb, srd, srt;
@@ -85,7 +87,11 @@ __global__ void __launch_bounds__(256) k_prefill_generic(const GParams p) {
         const long long widx = (long long)d * p.wsd + (long long)w * p.wsw;
         const float wv = (p.wdtype == VC1D_F32) ? reinterpret_cast<const float*>(p.weight)[widx]
                                                 : E::to_float(reinterpret_cast<const T*>(p.weight)[widx]);
-        acc = fmaf(wv, masked_input<DT>(p, x, b, d, t - (p.W - 1 - w)), acc);
+        const int tt = t - (p.W - 1 - w);
+        // a tap from another sequence of the same packed row does not count
+        if (p.seq != nullptr && tt >= 0 && p.seq[b * p.ssb + (long long)tt * p.sst] != p.seq[b * p.ssb + (long long)t * p.sst])
+            continue;
+        acc = fmaf(wv, masked_input<DT>(p, x, b, d, tt), acc);
     }
     if (p.act) acc = silu1<E::kPreciseSilu>(acc);
     if (p.res != nullptr) {
@@ -131,6 +137,9 @@ cudaError_t launch_prefill_generic(const vc1d_prefill_args& a, cudaStream_t s) {
     p.bias = a.bias;
     p.mask = a.mask;
     p.init = a.initial_state;
+    p.seq = a.seq_idx;
+    p.ssb = a.seq_stride_b;
+    p.sst = a.seq_stride_t;
     p.fstate = a.final_state;
     p.sxb = a.x_stride_b;
     p.sxd = a.x_stride_d;

@@ -54,7 +54,7 @@ unsigned int tma_timeouts() {
 
 cudaError_t launch_prefill_tma(const vc1d_prefill_args& a, cudaStream_t s) {
     const int eb = elem_bytes(a.dtype);
-    tma::TmaParams p;
+    tma::TmaParams p = {};
     p.y = reinterpret_cast<char*>(a.y);
     p.syb = a.y_stride_b * eb;
     p.syt = a.y_stride_t * eb;
@@ -90,6 +90,19 @@ cudaError_t launch_prefill_tma(const vc1d_prefill_args& a, cudaStream_t s) {
                      : 0;
     p.state_len = a.state_len;
     p.stages = 0;
+    p.seg_mode = 0;
+    p.chunk = 1;
+    p.empty_tma = 0;
+    if (a.seq_idx != nullptr) {
+        // sequence ids travel the mask's path: per-row values fetched by the producer, tile classes
+        // from the pre-pass; a row whose value is not one starts a new sequence
+        p.mask = a.seq_idx;
+        p.mask_dtype = VC1D_I32;
+        p.smb = a.seq_stride_b;
+        p.smt = a.seq_stride_t;
+        p.skip = 0;
+        p.seg_mode = 1;
+    }
     switch (a.dtype) {
         case VC1D_F32: return tma::launch_dt<VC1D_F32>(a, p, s);
         case VC1D_BF16: return tma::launch_dt<VC1D_BF16>(a, p, s);

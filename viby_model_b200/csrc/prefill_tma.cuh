@@ -80,9 +80,17 @@ struct TmaParams {
     int skip;
     int init_len;
     int res_is_x;
-    int table_in_smem;  // the pre-pass class table fits in shared memory and every CTA copies it there
+    int table_in_smem;  // every CTA copies the pre-pass class table to shared memory: 1 = a byte per tile, 2 = two bits
     int state_len;
     int stages;      // ring depth (2..kMaxStages)
+    int seg_mode;    // mask holds int32 sequence ids (packed variable-length rows), not multipliers
+    int chunk;       // consecutive tiles per dynamic claim
+    int empty_tma;   // tiles without any live tap are written by one bulk tensor store each
+    int inline_cls;  // every CTA classifies all tiles itself (consumer warps, while the first tile is in flight)
+    int mask_vec;    // mask rows are contiguous and 16-byte aligned: whole tiles are classified with 128-bit loads
+    int static_first;  // tiles a CTA takes without a claim (j0, j0 + G, ...) before the counter hands out the rest
+    unsigned spin_limit;  // polls after which a wait gives up
+    int test_withhold;    // self-test of the bounded waits: every producer keeps its first tile to itself
 };
 
 // ---- raw PTX wrappers -----------------------------------------------------------------------
@@ -110,8 +118,8 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait.  Returns false when the limit expired.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (unsigned i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned limit = kSpinLimit) {
+    for (unsigned i = 0; i < limit; ++i) {
         if (mbar_test(bar, parity)) return true;
         if (i > 64) __nanosleep(64);
     }
@@ -124,6 +132,17 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
         : "memory");
 }
+// One bulk tensor store of a whole tile from shared memory; rows and channels outside the tensor
+// are clipped by the tensor map.  Completion is tracked by the issuing thread's bulk groups.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int c0, int c1, int c2, uint32_t src) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(map), "r"(c0),
+                 "r"(c1), "r"(c2), "r"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// makes this thread's earlier shared-memory writes visible to bulk copies issued afterwards
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ float lds_f32(uint32_t a) {
     float v;
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a));
@@ -174,17 +193,25 @@ struct Geometry {
     static constexpr int kRowBytes = SLAB_BYTES;
     static constexpr int kSlabElems = SLAB_BYTES / Elem<DT>::kBytes;
     static constexpr int kStageBytes = ((kBoxRows * kRowBytes + 127) / 128) * 128;
-    // layout for S stages: stages | full[S], done[S] | tile descriptor[S] | mask values[S] | class table (one byte per tile)
+    // kConstRows rows of act(bias), the source of the bulk stores of tiles without a live tap (a tile is
+    // written by kTileRows / kConstRows stores: the rows are all alike, and shared memory is better spent
+    // on the ring and the class table)
+    static constexpr int kConstRows = 16;
+    static constexpr int kConstBytes = kConstRows * kRowBytes;
+    static_assert(kTileRows % kConstRows == 0 && kConstRows % RPT == 0, "whole row groups fill the constant rows");
+    // layout for S stages (C = 1 with the constant tile): stages | constant tile | full[S], done[S],
+    // constant-tile-ready | tile descriptor[S] | mask values[S] | class table (one byte per tile)
     // tile descriptor, 32 bytes: {class, rows of the tile that exist, byte offset of its first output
     // row (64 bits)} {sequence, first row, -, -}
-    __host__ __device__ static constexpr int off_bars(int S) { return S * kStageBytes; }
-    __host__ __device__ static constexpr int off_flags(int S) { return off_bars(S) + 2 * S * 8; }
+    __host__ __device__ static constexpr int off_const(int S) { return S * kStageBytes; }
+    __host__ __device__ static constexpr int off_bars(int S, int C) { return off_const(S) + C * kConstBytes; }
+    __host__ __device__ static constexpr int off_flags(int S, int C) { return off_bars(S, C) + (2 * S + 2) * 8; }
     // mask values of a mixed tile's box rows, one float per row, written by the producer
     static constexpr int kMaskBytes = ((kBoxRows + 31) / 32) * 32 * 4;
-    __host__ __device__ static constexpr int off_mvals(int S) { return off_flags(S) + S * 32; }
-    __host__ __device__ static constexpr int off_table(int S) { return off_mvals(S) + S * kMaskBytes; }
-    __host__ __device__ static constexpr int smem_bytes(int S, int table_bytes) {
-        return off_table(S) + table_bytes + 128 /* base alignment slack */;
+    __host__ __device__ static constexpr int off_mvals(int S, int C) { return off_flags(S, C) + S * 32; }
+    __host__ __device__ static constexpr int off_table(int S, int C) { return off_mvals(S, C) + S * kMaskBytes; }
+    __host__ __device__ static constexpr int smem_bytes(int S, int C, int table_bytes) {
+        return off_table(S, C) + table_bytes + 128 /* base alignment slack */;
     }
 };
 
@@ -247,8 +274,16 @@ __device__ __forceinline__ void apply_mask(float2 (&f)[Slice<DT, VB>::kPairs], f
 
 // Mask multiplier of time row t of the sequence whose mask row starts at element mrow.  Rows before
 // t = 0 hold zero-filled data (any multiplier works); rows past the end are never stored.
+// With sequence ids instead of a mask the value is kSegStart where a new sequence begins (the taps
+// of that row and of the rows after it must not reach above it) and one elsewhere.
+constexpr float kSegStart = 2.0f;
 __device__ __forceinline__ float tile_mask(const TmaParams& p, long long mrow, int t) {
     if (t < 0 || t >= p.T) return 1.0f;
+    if (p.seg_mode) {
+        if (t == 0) return 1.0f;  // rows above the tensor arrive as zeros anyway
+        const int* ids = reinterpret_cast<const int*>(p.mask) + mrow + (long long)t * p.smt;
+        return __ldg(ids) != __ldg(ids - p.smt) ? kSegStart : 1.0f;
+    }
     return load_mask(p.mask, mrow + (long long)t * p.smt, p.mask_dtype);
 }
 
@@ -286,7 +321,19 @@ __device__ __forceinline__ void process_rows(uint32_t trow, float mkv, int msrc,
         float2 cur[NP];
         S::unpack(raw, cur);
         if constexpr (GENERAL) {
-            if (mixed) apply_mask<DT, VB>(cur, __shfl_sync(0xffffffffu, mkv, msrc + H + k), p.skip);
+            if (mixed) {
+                const float mk = __shfl_sync(0xffffffffu, mkv, msrc + H + k);
+                if (p.seg_mode) {
+                    if (mk != 1.0f) {  // a sequence begins at this row: nothing above it is a tap
+#pragma unroll
+                        for (int w = 0; w < H; ++w)
+#pragma unroll
+                            for (int q = 0; q < NP; ++q) hist[w][q] = make_float2(0.f, 0.f);
+                    }
+                } else {
+                    apply_mask<DT, VB>(cur, mk, p.skip);
+                }
+            }
         }
         float2 acc[NP];
 #pragma unroll
@@ -330,6 +377,14 @@ __device__ __forceinline__ void process_rows(uint32_t trow, float mkv, int msrc,
 
 // Class of one tile from its mask rows: all valid, mixed, or nothing to read.  One warp per tile.
 __device__ __forceinline__ int classify_tile(const TmaParams& p, int b, int t0, int H, int box_rows, int lane) {
+    if (p.seg_mode) {
+        // a sequence starting at box row 1 or later cuts taps of this tile's rows; one starting at
+        // box row 0 does not (no output of the tile reads above it)
+        bool cut = false;
+        for (int jrow = 1 + lane; jrow < box_rows; jrow += 32)
+            cut |= tile_mask(p, (long long)b * p.smb, t0 - H + jrow) != 1.0f;
+        return __any_sync(0xffffffffu, cut) ? TILE_MIXED : TILE_FULL;
+    }
     bool any = false, all_one = true;
     for (int jrow = lane; jrow < box_rows; jrow += 32) {
         const int t = t0 - H + jrow;
@@ -346,16 +401,70 @@ __device__ __forceinline__ int classify_tile(const TmaParams& p, int b, int t0, 
     return all_one ? TILE_FULL : ((any || !p.skip || p.res != nullptr || history) ? TILE_MIXED : TILE_EMPTY);
 }
 
+// The same classification by ONE thread (every CTA classifying all tiles of a small launch itself).
+// With contiguous, aligned mask rows a whole tile's mask is read with 128-bit loads and compared as
+// raw bits: FULL only if every element is exactly one, EMPTY only if every bit is zero (a negative
+// zero makes the tile MIXED, where the values themselves are looked at).
+__device__ __forceinline__ int classify_tile_thread(const TmaParams& p, int b, int t0, int H, int tile_rows) {
+    bool any = false, all_one = true;
+    const long long mrow = (long long)b * p.smb;
+    for (int j = 0; j < H; ++j) {
+        const int t = t0 - H + j;
+        if (t >= 0 && t < p.T) {
+            const float mk = load_mask(p.mask, mrow + (long long)t * p.smt, p.mask_dtype);
+            any |= (mk != 0.0f);
+            all_one &= (mk == 1.0f);
+        }
+    }
+    const int rows = min(tile_rows, p.T - t0);
+    if (p.mask_vec && rows == tile_rows) {
+        int es = 1;
+        unsigned pat0 = 0x01010101u, pat1 = 0x01010101u;
+        switch (p.mask_dtype) {
+            case VC1D_I32: es = 4; pat0 = pat1 = 1u; break;
+            case VC1D_I64: es = 8; pat0 = 1u; pat1 = 0u; break;
+            case VC1D_F32: es = 4; pat0 = pat1 = 0x3f800000u; break;
+            case VC1D_BF16: es = 2; pat0 = pat1 = 0x3f803f80u; break;
+            case VC1D_F16: es = 2; pat0 = pat1 = 0x3c003c00u; break;
+            default: break;
+        }
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.mask) + (mrow + t0) * es);
+        const int n16 = tile_rows * es / 16;
+#pragma unroll 4
+        for (int i = 0; i < n16; ++i) {
+            const uint4 v = __ldg(src + i);
+            any |= (v.x | v.y | v.z | v.w) != 0u;
+            all_one &= (v.x == pat0) & (v.y == pat1) & (v.z == pat0) & (v.w == pat1);
+        }
+    } else {
+        for (int j = 0; j < rows; ++j) {
+            const float mk = load_mask(p.mask, mrow + (long long)(t0 + j) * p.smt, p.mask_dtype);
+            any |= (mk != 0.0f);
+            all_one &= (mk == 1.0f);
+        }
+    }
+    const bool history = p.init != nullptr && t0 == 0;
+    return all_one ? TILE_FULL : ((any || !p.skip || p.res != nullptr || history) ? TILE_MIXED : TILE_EMPTY);
+}
+
 // Pre-pass of masked launches that schedule dynamically: the class of every (sequence, time tile),
 // one byte each, into scratch memory.  The mask is the same for every channel slab.  A tile's class
 // looks at box_rows mask rows starting H rows above the tile.
 constexpr int kSchedCounterBytes = 4096;
 constexpr int kSmemTableCap = 16384;  // largest pre-pass class table a CTA copies into shared memory
 
+// (For the backward pass it can also clear the fp32 gradient accumulators, which saves a launch.)
 static __global__ void __launch_bounds__(256) k_classify_tiles(const TmaParams p, unsigned char* table, int tile_rows, int H,
-                                                               int box_rows) {
+                                                               int box_rows, float* zero_a = nullptr, int n_a = 0,
+                                                               float* zero_b = nullptr, int n_b = 0) {
     griddep_wait();  // the table may still be read by the previous launch on this stream
     griddep_launch_dependents();
+    {
+        const int stride = gridDim.x * blockDim.x;
+        const int first = blockIdx.x * blockDim.x + threadIdx.x;
+        for (int i = first; i < n_a; i += stride) zero_a[i] = 0.f;
+        for (int i = first; i < n_b; i += stride) zero_b[i] = 0.f;
+    }
     const int lane = threadIdx.x & 31;
     const long long tile = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (tile >= (long long)p.B * p.n_ttile) return;
@@ -367,7 +476,8 @@ static __global__ void __launch_bounds__(256) k_classify_tiles(const TmaParams p
 
 template <int DT, int W, int SLAB_BYTES, int VB, int RPT, bool ACT>
 __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads)
-    k_prefill_tma(const __grid_constant__ CUtensorMap tmap_x, const TmaParams p) {
+    k_prefill_tma(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
+                  const TmaParams p) {
     using E = Elem<DT>;
     using S = Slice<DT, VB>;
     using G = Geometry<DT, W, SLAB_BYTES, VB, RPT>;
@@ -382,10 +492,14 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
     extern __shared__ __align__(128) unsigned char smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
     const int kStages = p.stages;  // ring depth of this launch
-    const uint32_t bars = base + G::off_bars(kStages);    // full[s] at bars + 8 s, done[s] at bars + 8 (kStages + s)
-    const uint32_t flags = base + G::off_flags(kStages);  // per stage: 32-byte tile descriptor
-    const uint32_t mvals = base + G::off_mvals(kStages);  // per stage: mask value of every box row (mixed tiles)
-    const uint32_t table = base + G::off_table(kStages);  // class of each of this CTA's tiles (masked launches)
+    const int kC = p.empty_tma;    // 1: the constant tile exists
+    const uint32_t ctile = base + G::off_const(kStages);      // constant tile: act(bias) in every row
+    const uint32_t bars = base + G::off_bars(kStages, kC);    // full[s] at bars + 8 s, done[s] at bars + 8 (kStages + s)
+    const uint32_t cbar = bars + 8 * (2 * kStages);           // constant tile written (one arrive per consumer warp)
+    const uint32_t tbar = cbar + 8;                           // class table written (one arrive per consumer warp)
+    const uint32_t flags = base + G::off_flags(kStages, kC);  // per stage: 32-byte tile descriptor
+    const uint32_t mvals = base + G::off_mvals(kStages, kC);  // per stage: mask value of every box row (mixed tiles)
+    const uint32_t table = base + G::off_table(kStages, kC);  // class of each of this CTA's tiles (masked launches)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -400,6 +514,8 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
             mbar_init(bars + 8 * s, 1);                              // full: the producer's arrive (+ tx bytes)
             mbar_init(bars + 8 * (kStages + s), G::kConsumerWarps);  // done: one arrive per consumer warp
         }
+        mbar_init(cbar, G::kConsumerWarps);
+        mbar_init(tbar, G::kConsumerWarps);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
 
@@ -419,17 +535,29 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
     // Launched with programmatic stream serialization, this grid may start while its predecessor in
     // the stream is still running: nothing above touched global memory, everything below may.
     griddep_wait();
-    if (p.gtable != nullptr && p.table_in_smem) {
+    if (p.gtable != nullptr && p.table_in_smem == 2) {
+        // large launches: two bits per tile, sixteen tiles to a word (the scratch table is padded to 16)
+        const int n16 = (p.n_rowtiles + 15) >> 4;
+        const uint4* src = reinterpret_cast<const uint4*>(p.gtable);
+        for (int i = threadIdx.x; i < n16; i += G::kThreads) {
+            const uint4 v = __ldcg(src + i);
+            const unsigned wv[4] = {v.x, v.y, v.z, v.w};
+            unsigned packed = 0u;
+#pragma unroll
+            for (int k = 0; k < 16; ++k) packed |= ((wv[k >> 2] >> (8 * (k & 3))) & 3u) << (2 * k);
+            sts_s32(table + 4 * i, (int)packed);
+        }
+    } else if (p.gtable != nullptr && p.table_in_smem) {
         const int n16 = p.n_rowtiles >> 4;
         const uint4* src = reinterpret_cast<const uint4*>(p.gtable);
         for (int i = threadIdx.x; i < n16; i += G::kThreads) {
-            const uint4 v = __ldg(src + i);
+            const uint4 v = __ldcg(src + i);  // written by the pre-pass while this grid was already resident: no read-only path
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(table + 16 * i), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                          : "memory");
         }
-        for (int i = (n16 << 4) + threadIdx.x; i < p.n_rowtiles; i += G::kThreads) sts_u8(table + i, __ldg(p.gtable + i));
+        for (int i = (n16 << 4) + threadIdx.x; i < p.n_rowtiles; i += G::kThreads) sts_u8(table + i, __ldcg(p.gtable + i));
     }
-    if (p.mask != nullptr && p.gtable == nullptr) {
+    if (p.mask != nullptr && p.gtable == nullptr && !p.inline_cls) {
         for (int i = warp; i < n_my; i += G::kThreads / 32) {
             int b, t0;
             locate(j0 + i * stride, b, t0);
@@ -450,12 +578,13 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         // claim the next slot: wait until its previous tile has been consumed
         auto claim = [&]() -> bool {
             if (n_ring >= kStages) {
-                const bool ok = mbar_wait(bars + 8 * (kStages + s_ring), ph_ring ^ 1);
+                const bool ok = mbar_wait(bars + 8 * (kStages + s_ring), ph_ring ^ 1, p.spin_limit);
                 if (!ok && lane == 0) atomicAdd(p.timeouts, 1u);
                 if (!ok) return false;
             }
             return true;
         };
+        unsigned loads_issued = 0u, loads_parity = 0u;  // per stage: a copy was started, and in which ring phase
         auto advance = [&]() {
             ++n_ring;
             if (++s_ring == kStages) {
@@ -466,17 +595,29 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         // Which tile comes next.  Static: this CTA's tiles are j0, j0 + G, j0 + 2G, ...  Dynamic
         // (a zeroed counter per slab in caller-provided scratch memory): the next unclaimed tile of
         // the slab, so that a CTA that met cheap (masked) tiles or runs on a faster SM takes more.
-        const bool dynamic = p.sched != nullptr && (p.mask == nullptr || p.gtable != nullptr);
+        const bool dynamic = p.sched != nullptr && (p.mask == nullptr || p.gtable != nullptr || p.inline_cls);
         int n_issued = 0;
+        const unsigned chunk = (unsigned)p.chunk;  // consecutive tiles per claim
+        unsigned c_next = 0u, c_left = 0u;
         auto next_tile = [&]() -> int {
             unsigned raw;
-            if (dynamic && n_issued > 0) {
-                // the counter hands out the tiles behind the first one of every CTA of the slab
+            if (dynamic && c_left > 0u) {
+                raw = c_next++;  // rest of the chunk claimed last
+                --c_left;
+            } else if (dynamic && chunk == 1u && n_issued < p.static_first) {
+                // the first tiles of a CTA need no claim: their copies start back to back
+                raw = (unsigned)(j0 + n_issued * stride);
+            } else if (dynamic && n_issued > 0) {
+                // the counter hands out the chunks behind the unclaimed first ones of every CTA of the slab
                 raw = 0u;
-                if (lane == 0) raw = atomicAdd(p.sched + slab, 1u);
-                raw = __shfl_sync(0xffffffffu, raw, 0) + (unsigned)stride;
+                if (lane == 0) raw = atomicAdd(p.sched + slab, chunk);
+                raw = __shfl_sync(0xffffffffu, raw, 0) + (unsigned)stride * (chunk == 1u ? (unsigned)p.static_first : chunk);
+                c_next = raw + 1u;
+                c_left = chunk - 1u;
             } else if (dynamic) {
-                raw = (unsigned)j0;  // a CTA's first tile needs no claim: the copy starts a round trip earlier
+                raw = (unsigned)j0 * chunk;  // a CTA's first chunk needs no claim: the copy starts a round trip earlier
+                c_next = raw + 1u;
+                c_left = chunk - 1u;
             } else {
                 raw = n_issued < n_my ? (unsigned)(j0 + n_issued * stride) : 0xffffffffu;
             }
@@ -487,9 +628,12 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         // CTA's own table, or no mask at all
         auto tile_class = [&](int i, int b, int t0) -> int {
             if (p.mask == nullptr) return TILE_FULL;
+            if (p.inline_cls) return lds_u8(table + (uint32_t)(b * p.n_ttile + t0 / G::kTileRows));
             if (p.gtable != nullptr) {
                 const long long idx = (long long)b * p.n_ttile + t0 / G::kTileRows;
-                return p.table_in_smem ? lds_u8(table + (uint32_t)idx) : (int)__ldg(p.gtable + idx);
+                if (p.table_in_smem == 2)
+                    return (lds_s32(table + 4u * (uint32_t)(idx >> 4)) >> (2 * (int)(idx & 15))) & 3;
+                return p.table_in_smem ? lds_u8(table + (uint32_t)idx) : (int)__ldcg(p.gtable + idx);
             }
             return lds_u8(table + i);
         };
@@ -500,6 +644,13 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         };
         auto put_tile = [&](int b, int t0, int cls, const float (&mv)[NMK]) {
             const int s = s_ring;
+            if (p.test_withhold && n_ring == 0) return;  // self-test: the consumers' wait for this slot must expire
+            // (the slot's previous tile has been consumed: claim() saw to that)
+            loads_issued &= ~(1u << s);
+            if (cls != TILE_EMPTY) {
+                loads_issued |= 1u << s;
+                loads_parity = (loads_parity & ~(1u << s)) | (ph_ring << s);
+            }
             if (cls == TILE_MIXED) {
 #pragma unroll
                 for (int k = 0; k < NMK; ++k) sts_f32(mvals + s * G::kMaskBytes + (lane + 32 * k) * 4, mv[k]);
@@ -531,18 +682,57 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         for (int k = 0; k < NMK; ++k) mv[k] = 1.0f;
         if (rt >= 0) {
             locate(rt, b, t0);
-            cls = tile_class(0, b, t0);
+            // (classifying in the kernel: the consumer warps are still filling the table, so the
+            // producer works out the class of its first tile by itself)
+            cls = p.inline_cls ? classify_tile(p, b, t0, H, G::kBoxRows, lane) : tile_class(0, b, t0);
             if (cls == TILE_MIXED) fetch_mask(b, t0, mv);
         }
+        bool const_ready = false;  // the consumers have written the constant tile
+        bool table_ready = !p.inline_cls;  // the consumers have classified every tile
         for (int i = 0; live && rt >= 0; ++i) {
             const int b_now = b, t0_now = t0, cls_now = cls;
 #pragma unroll
             for (int k = 0; k < NMK; ++k) mv_now[k] = mv[k];
+            bool put_done = false;
+            if (!table_ready && !(cls_now == TILE_EMPTY && kC)) {
+                // first tile of a CTA that classifies in the kernel: start its copy before waiting for
+                // the table the next claim needs
+                put_tile(b_now, t0_now, cls_now, mv_now);
+                advance();
+                put_done = true;
+            }
             rt = next_tile();
             if (rt >= 0) {
                 locate(rt, b, t0);
+                if (!table_ready) {
+                    table_ready = mbar_wait(tbar, 0, p.spin_limit);
+                    if (!table_ready) {
+                        if (lane == 0) atomicAdd(p.timeouts, 1u);
+                        live = false;
+                        break;
+                    }
+                }
                 cls = tile_class(i + 1, b, t0);
                 if (cls == TILE_MIXED) fetch_mask(b, t0, mv);
+            }
+            if (put_done) continue;
+            if (cls_now == TILE_EMPTY && kC) {
+                // no tap of the tile is live: every row is act(bias).  One bulk store from the
+                // constant tile writes it; it takes no ring slot and no consumer sees it.
+                if (!const_ready) {
+                    const_ready = mbar_wait(cbar, 0, p.spin_limit);
+                    if (!const_ready && lane == 0) atomicAdd(p.timeouts, 1u);
+                    live = const_ready;
+                    if (!live) break;
+                }
+                if (lane == 0) {
+                    // (a store is never started past the last row; rows past it inside a box are clipped)
+                    for (int r = 0; r < G::kTileRows && t0_now + r < p.T; r += G::kConstRows)
+                        tma_store_3d(&tmap_y, slab_ch0, t0_now + r, b_now, ctile);
+                    bulk_commit();
+                }
+                __syncwarp();
+                continue;
             }
             live = claim();
             if (!live) break;
@@ -555,6 +745,7 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         griddep_launch_dependents();
         // END marker: the consumers leave when they meet it
         if (live && claim()) {
+            loads_issued &= ~(1u << s_ring);
             if (lane == 0) {
                 sts_desc(flags + 32 * s_ring, TILE_END, 0, 0);
                 mbar_arrive(bars + 8 * s_ring);
@@ -572,6 +763,13 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
                 __threadfence();
             }
         }
+        // the bulk stores read the constant tile: shared memory must outlive them
+        if (kC && lane == 0) bulk_wait_all();
+        // No copy of this CTA may still be in flight when it ends.  Normally the consumers, who wait for
+        // every copy, outlive this warp; if their waits expired they are gone already, so the copies
+        // started here are waited for here as well (bounded like every wait).
+        for (int s = 0; s < kStages; ++s)
+            if ((loads_issued >> s) & 1u) mbar_wait(bars + 8 * s, (loads_parity >> s) & 1u, p.spin_limit);
     } else {
         // ================================ consumer warps =================================
         const int grp = threadIdx.x / LPR;  // row group inside the tile
@@ -591,6 +789,27 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
             for (int q = 0; q < NP; ++q) c[q] = ACT ? silu2<E::kPreciseSilu>(bp[q]) : bp[q];
             S::pack(c, const_row);
         }
+        if (kC) {
+            // the constant rows (the first row groups write them); the producer's bulk stores read them
+            if (rbase < G::kConstRows) {
+#pragma unroll
+                for (int k = 0; k < R; ++k) S::sts(ctile + (rbase + k) * G::kRowBytes + cl * VB, const_row);
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(cbar);
+        }
+        if (p.inline_cls) {
+            // class of every tile of the launch, one thread per tile; the producer meanwhile has its
+            // first tile in flight and waits for this table before its second claim
+            for (int tile = threadIdx.x; tile < p.n_rowtiles; tile += G::kConsumerThreads) {
+                const int bb = tile / p.n_ttile;
+                const int tt = tile - bb * p.n_ttile;
+                sts_u8(table + tile, classify_tile_thread(p, bb, tt * G::kTileRows, H, G::kTileRows));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tbar);
+        }
         const bool general_kernel = (p.mask != nullptr) || (p.res != nullptr);
         const unsigned pitch = (unsigned)p.syt;  // output row pitch in bytes; the launcher keeps 8 rows within 32 bits
 
@@ -609,7 +828,7 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
                 ph ^= 1;
                 trow = tbase;
             }
-            if (!mbar_wait(bars + 8 * s, ph)) {
+            if (!mbar_wait(bars + 8 * s, ph, p.spin_limit)) {
                 if (lane == 0) atomicAdd(p.timeouts, 1u);
                 break;  // no barrier is shared with the other warps: each leaves on its own
             }
@@ -670,8 +889,22 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
                     const int j = lane & (GL - 1);
                     if (j < R + H) mkv = lds_f32(mvals + s * G::kMaskBytes + (rbase + j) * 4);  // box row rbase + j
 #pragma unroll
-                    for (int w = 0; w < H; ++w)
-                        apply_mask<DT, VB>(hist[w], __shfl_sync(0xffffffffu, mkv, msrc + w), p.skip);
+                    for (int w = 0; w < H; ++w) {
+                        const float mk = __shfl_sync(0xffffffffu, mkv, msrc + w);
+                        if (p.seg_mode) {
+                            if (mk != 1.0f) {  // a sequence begins at box row w: the rows above it are no taps
+#pragma unroll
+                                for (int v = 0; v < H; ++v) {
+                                    if (v < w) {
+#pragma unroll
+                                        for (int q = 0; q < NP; ++q) hist[v][q] = make_float2(0.f, 0.f);
+                                    }
+                                }
+                            }
+                        } else {
+                            apply_mask<DT, VB>(hist[w], mk, p.skip);
+                        }
+                    }
                 }
                 const char* rb = nullptr;
                 if (p.res != nullptr && !p.res_is_x && ch_ok)
@@ -759,6 +992,27 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return cudaErrorNotSupported;  // the caller falls back to the direct kernel
     }
+    // Output map for the bulk stores of tiles without a live tap (same box as a tile, no halo).  Only
+    // launches that can have such tiles carry the constant tile; when y cannot be described by a
+    // tensor map the consumer warps store those tiles instead.
+    CUtensorMap tmap_y = tmap_x;
+    p.empty_tma = 0;
+    if (p.mask != nullptr && p.skip && a.residual == nullptr && !p.seg_mode && a.tma_empty_store != 1) {
+        const cuuint64_t dims[3] = {(cuuint64_t)a.dim, (cuuint64_t)a.seqlen, (cuuint64_t)a.batch};
+        const cuuint32_t estr[3] = {1u, 1u, 1u};
+        cuuint64_t st[2] = {(cuuint64_t)a.y_stride_t * eb, (cuuint64_t)a.y_stride_b * eb};
+        if (a.seqlen == 1) st[0] = (cuuint64_t)a.dim * eb;
+        if (a.batch == 1) st[1] = st[0] * (cuuint64_t)a.seqlen;
+        const bool addressable = a.y_stride_t > 0 && a.y_stride_b >= 0 && st[0] % 16 == 0 && st[1] % 16 == 0 &&
+                                 (reinterpret_cast<uintptr_t>(a.y) & 15u) == 0;
+        if (addressable) {
+            const cuuint32_t box[3] = {(cuuint32_t)slab_ch, (cuuint32_t)G::kConstRows, 1u};
+            const CUresult r = enc(&tmap_y, dt, 3, a.y, dims, st, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r == CUDA_SUCCESS) p.empty_tma = 1;
+        }
+    }
     int stages = a.tma_stages > 0 ? a.tma_stages : 3;
     if (stages < 2) stages = 2;
     if (stages > kMaxStages) stages = kMaxStages;
@@ -768,7 +1022,7 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     // byte per tile in shared memory, so the grid grows before a CTA would own more than 8192 tiles
     long long g = ((long long)sm_count() * per_sm) / n_slab;
     if (g < 1) g = 1;
-    if (a.mask != nullptr && n_rowtiles > g * 8192) g = (n_rowtiles + 8191) / 8192;  // only matters without scratch
+    if (p.mask != nullptr && n_rowtiles > g * 8192) g = (n_rowtiles + 8191) / 8192;  // only matters without scratch
     if (g > n_rowtiles) g = n_rowtiles;
     if (g > 65535) g = 65535;
     p.ctas_per_slab = (int)g;
@@ -780,29 +1034,57 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     p.sched = nullptr;
     p.gtable = nullptr;
     p.table_in_smem = 0;
-    const long long table_need = a.mask != nullptr ? n_rowtiles : 0;
+    const long long table_need = p.mask != nullptr ? n_rowtiles : 0;
     // dynamic claims pay off once a CTA has several tiles; with two or three the claim round trips
     // (and, with a mask, the pre-pass) cost more than the balance gains
+    p.spin_limit = a.tma_test_expire ? (1u << 12) : kSpinLimit;
+    p.test_withhold = a.tma_test_expire ? 1 : 0;
+    p.chunk = (a.tma_claim_chunk == 2 || a.tma_claim_chunk == 4) ? a.tma_claim_chunk : 1;
+    if (tiles_per_cta < 4LL * p.chunk) p.chunk = 1;
+    // two unclaimed tiles per CTA: both copies start back to back at the top of the kernel
+    p.static_first = (a.tma_static_first >= 1 && a.tma_static_first <= 8) ? a.tma_static_first : 2;
+    if (tiles_per_cta < 2LL * p.static_first) p.static_first = 1;
     const bool use_scratch = tiles_per_cta >= 4 && a.scratch != nullptr && 4LL * (n_slab + 1) <= kSchedCounterBytes &&
                              a.scratch_bytes >= kSchedCounterBytes + table_need &&
                              (reinterpret_cast<uintptr_t>(a.scratch) & 15u) == 0;
     unsigned char* tab = nullptr;
     int table_bytes = 0;  // class bytes in shared memory
+    // Tile classes of a masked launch with dynamic claims.  A small mask whose rows can be read with
+    // 128-bit loads is classified by every CTA itself (its consumer warps do it while the first tile
+    // is in flight: no pre-pass launch, nothing on the critical path); otherwise a pre-pass kernel
+    // writes the classes to scratch memory once for all CTAs.
+    p.inline_cls = 0;
+    p.mask_vec = 0;
+    if (p.mask != nullptr && !p.seg_mode) {
+        const int es = elem_bytes(p.mask_dtype);
+        const bool vec = es > 0 && p.smt == 1 && (p.smb * es) % 16 == 0 &&
+                         (reinterpret_cast<uintptr_t>(p.mask) & 15u) == 0;
+        p.mask_vec = vec ? 1 : 0;
+        const long long loads = n_rowtiles * G::kTileRows * es / 16;  // 128-bit loads for the whole mask
+        if (use_scratch && vec && n_rowtiles <= kSmemTableCap && loads <= 32LL * G::kConsumerThreads &&
+            a.tma_classify == 2)
+            p.inline_cls = 1;
+    }
     if (use_scratch) {
         p.sched = reinterpret_cast<unsigned int*>(a.scratch);
-        if (a.mask != nullptr) {
+        if (p.inline_cls) {
+            table_bytes = (int)((n_rowtiles + 15) / 16 * 16);
+        } else if (p.mask != nullptr) {
             tab = reinterpret_cast<unsigned char*>(a.scratch) + kSchedCounterBytes;
             if (n_rowtiles <= kSmemTableCap) {
                 p.table_in_smem = 1;
                 table_bytes = (int)((n_rowtiles + 15) / 16 * 16);
+            } else if (n_rowtiles <= 4LL * kSmemTableCap && a.scratch_bytes >= kSchedCounterBytes + (n_rowtiles + 15) / 16 * 16) {
+                p.table_in_smem = 2;
+                table_bytes = (int)((n_rowtiles + 15) / 16 * 4);
             }
         }
-    } else if (a.mask != nullptr) {
+    } else if (p.mask != nullptr) {
         // static assignment: every CTA classifies its own tiles into shared memory
         if (tiles_per_cta > 8192) return cudaErrorNotSupported;  // the direct kernel takes it
         table_bytes = (int)((tiles_per_cta + 15) / 16 * 16);
     }
-    const int smem = G::smem_bytes(stages, table_bytes);
+    const int smem = G::smem_bytes(stages, p.empty_tma, table_bytes);
     {
         // opt in to > 48 KB of dynamic shared memory; the attribute is per device and sticky, so
         // remember the largest value set so far
@@ -822,7 +1104,8 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     // a pre-pass are serialized normally: letting dense launches overlap brought nothing.
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = (pdl_enabled() && tab != nullptr) ? 1 : 0;
+    attr[0].val.programmaticStreamSerializationAllowed =
+        (pdl_enabled() && (tab != nullptr || a.tma_pdl == 2)) ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
     cfg.stream = s;
     cfg.attrs = attr;
@@ -832,7 +1115,8 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
         cfg.gridDim = dim3((unsigned)((threads + 255) / 256));
         cfg.blockDim = dim3(256);
         cfg.dynamicSmemBytes = 0;
-        const cudaError_t e = cudaLaunchKernelEx(&cfg, k_classify_tiles, p, tab, (int)G::kTileRows, (int)G::kH, (int)G::kBoxRows);
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, k_classify_tiles, p, tab, (int)G::kTileRows, (int)G::kH,
+                                                 (int)G::kBoxRows, (float*)nullptr, 0, (float*)nullptr, 0);
         if (e != cudaSuccess) return e;
         note_launch("classify");
         p.gtable = tab;
@@ -841,7 +1125,7 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     cfg.blockDim = dim3(G::kThreads);
     cfg.dynamicSmemBytes = (size_t)smem;
     note_launch("tma");
-    return cudaLaunchKernelEx(&cfg, k_prefill_tma<DT, W, SLAB_BYTES, VB, RPT, ACT>, tmap_x, p);
+    return cudaLaunchKernelEx(&cfg, k_prefill_tma<DT, W, SLAB_BYTES, VB, RPT, ACT>, tmap_x, tmap_y, p);
 }
 
 template <int DT, int W, int SLAB_BYTES>

@@ -152,6 +152,149 @@ __global__ void __launch_bounds__(256, 2) k_update_vec(const UParams p) {
     }
 }
 
+// One channel per lane, for states whose state_len columns of one channel are one or two 128-bit
+// vectors (state_len 8 in bf16 / fp16, 4 or 8 in fp32: what the reference's PyTorch and Metal
+// branches keep, model/model.py:286 and 541).  Consecutive lanes own consecutive channels, so the
+// state of a warp's 32 channels is 512 (or 1024) contiguous bytes: every state access is one fully
+// coalesced 128-bit load or store per lane, x and y are one element per lane.  The window moves as
+// raw bits.  Shifting state: the vector is shifted by one element and x appended.  Circular state
+// (cache_seqlens, causal_conv1d.metal:586-664): the history columns are picked out of the vector by
+// position, x replaces the column at cache_seqlens[b] % state_len, and the vector is written back
+// whole (the partial sector a 2-byte store would dirty costs the same write-back).
+template <int EB, int NWORDS>
+__device__ __forceinline__ uint32_t state_elem(const uint32_t (&wd)[NWORDS], int idx) {
+    // element idx of the window, as raw bits in the low EB bytes
+    const int wi = (EB == 4) ? idx : (idx >> 1);
+    uint32_t r = wd[0];
+#pragma unroll
+    for (int k = 1; k < NWORDS; ++k) r = (wi == k) ? wd[k] : r;
+    if (EB == 2) r = (idx & 1) ? (r >> 16) : (r & 0xffffu);
+    return r;
+}
+template <int EB, int NWORDS>
+__device__ __forceinline__ void state_put(uint32_t (&wd)[NWORDS], int idx, uint32_t bits) {
+    const int wi = (EB == 4) ? idx : (idx >> 1);
+#pragma unroll
+    for (int k = 0; k < NWORDS; ++k) {
+        uint32_t nv = bits;
+        if (EB == 2) nv = (idx & 1) ? ((wd[k] & 0xffffu) | (bits << 16)) : ((wd[k] & 0xffff0000u) | bits);
+        wd[k] = (wi == k) ? nv : wd[k];
+    }
+}
+template <int DT>
+__device__ __forceinline__ float bits_to_float(uint32_t bits) {
+    if constexpr (DT == VC1D_F32) return __uint_as_float(bits);
+    if constexpr (DT == VC1D_BF16) return __uint_as_float(bits << 16);
+    if constexpr (DT == VC1D_F16) return __half2float(__ushort_as_half((unsigned short)bits));
+    return 0.f;
+}
+template <int DT>
+__device__ __forceinline__ uint32_t float_to_bits(float v) {
+    if constexpr (DT == VC1D_F32) return __float_as_uint(v);
+    if constexpr (DT == VC1D_BF16) return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(v));
+    if constexpr (DT == VC1D_F16) return (uint32_t)__half_as_ushort(__float2half_rn(v));
+    return 0u;
+}
+
+template <int DT, int W, int NV>
+__global__ void __launch_bounds__(256) k_update_lane(const UParams p) {
+    using E = Elem<DT>;
+    using T = typename E::type;
+    constexpr int EB = E::kBytes;
+    constexpr int NWORDS = 4 * NV;
+    constexpr int L = NV * 16 / EB;
+    constexpr int UB = 2;  // sequences in flight per thread
+    griddep_wait();
+    griddep_launch_dependents();
+    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= p.total) return;
+    const int d = (int)(g % p.D);
+    const long long grp = g / p.D;
+
+    float wf[W];
+    float bf = 0.f;
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+        const long long idx = (long long)d * p.wsd + (long long)w * p.wsw;
+        wf[w] = (p.wdtype == VC1D_F32) ? __ldg(reinterpret_cast<const float*>(p.weight) + idx)
+                                       : E::to_float(__ldg(reinterpret_cast<const T*>(p.weight) + idx));
+    }
+    if (p.bias != nullptr)
+        bf = (p.wdtype == VC1D_F32) ? __ldg(reinterpret_cast<const float*>(p.bias) + d)
+                                    : E::to_float(__ldg(reinterpret_cast<const T*>(p.bias) + d));
+
+    const bool circular = p.seqlens != nullptr;
+    const long long b0 = grp * p.nb;
+    const long long b1 = (b0 + p.nb < p.B) ? b0 + p.nb : p.B;
+    for (long long bb = b0; bb < b1; bb += UB) {
+        uint32_t wd[UB][NWORDS];
+        uint32_t xb[UB];
+        int pos[UB];
+#pragma unroll
+        for (int u = 0; u < UB; ++u) {
+            xb[u] = 0u;
+            pos[u] = 0;
+            if (bb + u < b1) {
+                const uint4* sp = reinterpret_cast<const uint4*>(p.state + ((bb + u) * p.ssb + (long long)d * L) * EB);
+#pragma unroll
+                for (int j = 0; j < NV; ++j) {
+                    const uint4 v = sp[j];
+                    wd[u][4 * j] = v.x;
+                    wd[u][4 * j + 1] = v.y;
+                    wd[u][4 * j + 2] = v.z;
+                    wd[u][4 * j + 3] = v.w;
+                }
+                const T xe = __ldg(reinterpret_cast<const T*>(p.x) + (bb + u) * p.sxb + d);
+                if constexpr (EB == 4) xb[u] = __float_as_uint(xe);
+                else xb[u] = (uint32_t)(*reinterpret_cast<const unsigned short*>(&xe));
+                if (circular) {
+                    int q = __ldg(p.seqlens + bb + u) % L;
+                    pos[u] = q < 0 ? q + L : q;
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UB; ++u) {
+            if (bb + u < b1) {
+                const float xf = bits_to_float<DT>(xb[u]);
+                float acc = bf;
+                if (!circular) {
+#pragma unroll
+                    for (int w = 0; w < W - 1; ++w)
+                        acc = fmaf(wf[w], bits_to_float<DT>(state_elem<EB, NWORDS>(wd[u], L + 1 - W + w)), acc);
+                    acc = fmaf(wf[W - 1], xf, acc);
+                    // shift the window left by one element, append x
+                    if constexpr (EB == 4) {
+#pragma unroll
+                        for (int k = 0; k + 1 < NWORDS; ++k) wd[u][k] = wd[u][k + 1];
+                        wd[u][NWORDS - 1] = xb[u];
+                    } else {
+#pragma unroll
+                        for (int k = 0; k + 1 < NWORDS; ++k) wd[u][k] = __funnelshift_r(wd[u][k], wd[u][k + 1], 16);
+                        wd[u][NWORDS - 1] = (wd[u][NWORDS - 1] >> 16) | (xb[u] << 16);
+                    }
+                } else {
+#pragma unroll
+                    for (int w = 0; w < W - 1; ++w) {
+                        int h = pos[u] - (W - 1 - w);
+                        h = h < 0 ? h + L : h;
+                        acc = fmaf(wf[w], bits_to_float<DT>(state_elem<EB, NWORDS>(wd[u], h)), acc);
+                    }
+                    acc = fmaf(wf[W - 1], xf, acc);
+                    state_put<EB, NWORDS>(wd[u], pos[u], xb[u]);
+                }
+                if (p.act) acc = silu1<E::kPreciseSilu>(acc);
+                if (p.residual) acc = E::to_float(E::from_float(acc)) + xf;
+                uint4* spw = reinterpret_cast<uint4*>(p.state + ((bb + u) * p.ssb + (long long)d * L) * EB);
+#pragma unroll
+                for (int j = 0; j < NV; ++j)
+                    spw[j] = make_uint4(wd[u][4 * j], wd[u][4 * j + 1], wd[u][4 * j + 2], wd[u][4 * j + 3]);
+                reinterpret_cast<T*>(p.y)[(bb + u) * p.syb + d] = E::from_float(acc);
+            }
+        }
+    }
+}
+
 // Scalar kernel: any strides, any state_len >= width-1, shifting or circular state.
 template <int DT>
 __global__ void __launch_bounds__(256) k_update_generic(const UParams p) {
@@ -315,6 +458,48 @@ cudaError_t launch_update_vec(const vc1d_update_args& a, cudaStream_t s) {
         case VC1D_BF16: return launch_vec_w<VC1D_BF16>(p, grid, block, s);
         default: return launch_vec_w<VC1D_F16>(p, grid, block, s);
     }
+}
+
+bool update_lane_supports(int dtype, int state_len, int width) {
+    const int bytes = state_len * elem_bytes(dtype);
+    return state_len >= width - 1 && state_len >= 1 && (bytes == 16 || bytes == 32);
+}
+
+cudaError_t launch_update_lane(const vc1d_update_args& a, cudaStream_t s) {
+    UParams p = make_params(a);
+    // a thread keeps its channel's weights in registers and walks nb sequences
+    const long long threads1 = (long long)a.batch * a.dim;
+    long long nb = threads1 / ((long long)sm_count() * 2048 * 4);
+    if (nb < 2) nb = 2;
+    if (nb > 16) nb = 16;
+    if (a.batch < nb) nb = a.batch;
+    if (a.reserved > 0) nb = a.reserved;  // tuning override
+    p.nb = (int)nb;
+    const long long ngroups = (a.batch + nb - 1) / nb;
+    p.total = ngroups * a.dim;
+    int block = a.block_threads > 0 ? a.block_threads : 256;
+    if (block > 256) block = 256;
+    block = (block + 31) / 32 * 32;
+    const long long blocks = (p.total + block - 1) / block;
+    if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    note_launch("update_lane");
+    const dim3 grid((unsigned)blocks);
+    const int nv = a.state_len * elem_bytes(a.dtype) / 16;
+#define VC1D_LANE(DT)                                                                          \
+    switch (a.width) {                                                                         \
+        case 2: return nv == 1 ? launch_pdl(k_update_lane<DT, 2, 1>, p, grid, block, s)        \
+                               : launch_pdl(k_update_lane<DT, 2, 2>, p, grid, block, s);       \
+        case 3: return nv == 1 ? launch_pdl(k_update_lane<DT, 3, 1>, p, grid, block, s)        \
+                               : launch_pdl(k_update_lane<DT, 3, 2>, p, grid, block, s);       \
+        default: return nv == 1 ? launch_pdl(k_update_lane<DT, 4, 1>, p, grid, block, s)       \
+                                : launch_pdl(k_update_lane<DT, 4, 2>, p, grid, block, s);      \
+    }
+    switch (a.dtype) {
+        case VC1D_F32: VC1D_LANE(VC1D_F32)
+        case VC1D_BF16: VC1D_LANE(VC1D_BF16)
+        default: VC1D_LANE(VC1D_F16)
+    }
+#undef VC1D_LANE
 }
 
 cudaError_t launch_update_generic(const vc1d_update_args& a, cudaStream_t s) {

@@ -269,32 +269,40 @@ struct Slice {
             asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
                          : "=r"(r[0]), "=r"(r[1]), "=r"(r[kWords > 2 ? 2 : 0]), "=r"(r[kWords > 3 ? 3 : 0])
                          : "r"(a));
+        else if constexpr (VB == 8)
+            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[kWords > 1 ? 1 : 0]) : "r"(a));
         else
-            asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+            asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r[0]) : "r"(a));
     }
     __device__ __forceinline__ static void sts(uint32_t a, const uint32_t (&r)[kWords]) {
         if constexpr (VB == 16)
             asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(r[0]), "r"(r[1]),
                          "r"(r[kWords > 2 ? 2 : 0]), "r"(r[kWords > 3 ? 3 : 0])
                          : "memory");
+        else if constexpr (VB == 8)
+            asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(r[0]), "r"(r[kWords > 1 ? 1 : 0]) : "memory");
         else
-            asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(r[0]), "r"(r[1]) : "memory");
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(r[0]) : "memory");
     }
     __device__ __forceinline__ static void ldg(const void* g, uint32_t (&r)[kWords]) {
         if constexpr (VB == 16)
             asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
                          : "=r"(r[0]), "=r"(r[1]), "=r"(r[kWords > 2 ? 2 : 0]), "=r"(r[kWords > 3 ? 3 : 0])
                          : "l"(g));
+        else if constexpr (VB == 8)
+            asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[kWords > 1 ? 1 : 0]) : "l"(g));
         else
-            asm volatile("ld.global.nc.v2.u32 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "l"(g));
+            asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r[0]) : "l"(g));
     }
     __device__ __forceinline__ static void stg(void* g, const uint32_t (&r)[kWords]) {
         if constexpr (VB == 16)
             asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(g), "r"(r[0]), "r"(r[1]),
                          "r"(r[kWords > 2 ? 2 : 0]), "r"(r[kWords > 3 ? 3 : 0])
                          : "memory");
+        else if constexpr (VB == 8)
+            asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(g), "r"(r[0]), "r"(r[kWords > 1 ? 1 : 0]) : "memory");
         else
-            asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(g), "r"(r[0]), "r"(r[1]) : "memory");
+            asm volatile("st.global.cs.u32 [%0], %1;" ::"l"(g), "r"(r[0]) : "memory");
     }
     // Streaming store of row K of a thread's rows, predicated on K < rows_ok inside the instruction
     // (a guarded store written in C++ around inline assembly becomes a branch per row instead).
@@ -305,9 +313,13 @@ struct Slice {
                 "{\n .reg .pred p;\n setp.gt.s32 p, %5, %6;\n @p st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};\n}" ::"l"(g),
                 "r"(r[0]), "r"(r[1]), "r"(r[kWords > 2 ? 2 : 0]), "r"(r[kWords > 3 ? 3 : 0]), "r"(rows_ok), "n"(K)
                 : "memory");
-        else
+        else if constexpr (VB == 8)
             asm volatile("{\n .reg .pred p;\n setp.gt.s32 p, %3, %4;\n @p st.global.cs.v2.u32 [%0], {%1,%2};\n}" ::"l"(g),
-                         "r"(r[0]), "r"(r[1]), "r"(rows_ok), "n"(K)
+                         "r"(r[0]), "r"(r[kWords > 1 ? 1 : 0]), "r"(rows_ok), "n"(K)
+                         : "memory");
+        else
+            asm volatile("{\n .reg .pred p;\n setp.gt.s32 p, %2, %3;\n @p st.global.cs.u32 [%0], %1;\n}" ::"l"(g),
+                         "r"(r[0]), "r"(rows_ok), "n"(K)
                          : "memory");
     }
     __device__ __forceinline__ static void unpack(const uint32_t (&r)[kWords], float2 (&f)[kPairs]) {

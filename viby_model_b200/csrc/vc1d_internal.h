@@ -49,6 +49,11 @@ cudaError_t launch_prefill_bwd_tma(const vc1d_prefill_bwd_args& a, cudaStream_t 
 cudaError_t launch_update_vec(const vc1d_update_args& a, cudaStream_t s);
 bool update_vec_supports(int state_len, int width);
 
+// One channel per lane: x/y channel stride 1, conv_state strides (.., state_len, 1) and 16-byte
+// aligned rows, state_len * elem_size 16 or 32 bytes; shifting or circular (cache_seqlens) state.
+cudaError_t launch_update_lane(const vc1d_update_args& a, cudaStream_t s);
+bool update_lane_supports(int dtype, int state_len, int width);
+
 // Any strides, shifting or circular state.
 cudaError_t launch_update_generic(const vc1d_update_args& a, cudaStream_t s);
 

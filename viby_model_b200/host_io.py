@@ -9,7 +9,11 @@ Two things keep the PCIe link, which bounds this path, busy with useful bytes on
   * rows behind a sequence's last valid position are never read by the kernels (masked loads are
     skipped), so they are not sent: only ``x[b, :last_valid_b]`` crosses the link;
   * with ``join=False`` consecutive ``run`` calls pipeline into each other (the copy-in of the next
-    batch overlaps the copy-out of the previous one); buffer reuse is ordered by events per chunk.
+    batch overlaps the copy-out of the previous one); buffer reuse is ordered by events per chunk;
+  * with ``skip_constant_rows`` output rows that lie ``width - 1`` or more steps behind a sequence's last
+    valid position are not copied back either: every tap of such a row is masked, so the row is the
+    per-channel constant ``act(bias)``, which the host writes into ``y_host`` itself from one ``[dim]``
+    vector while the copies run.
 """
 from __future__ import annotations
 
@@ -20,12 +24,44 @@ import torch
 from .ops import causal_conv1d_fn
 
 
+NUMA_STATUS = {}  # device index -> why bind_to_gpu_numa_node returned what it did
+
+
 def bind_to_gpu_numa_node(device_index: int) -> Optional[int]:
     """Pin the calling process to the CPUs of the NUMA node the GPU hangs off, so that pinned host
     buffers allocated afterwards (first touch) and the copy threads sit next to its PCIe root.
     With one process per GPU on a multi-socket host this keeps host<->device copies off the
     inter-socket link.  Returns the node, or None when the topology cannot be read (nothing is
-    changed then)."""
+    changed then); ``NUMA_STATUS[device_index]`` says which."""
+    node = _bind_to_gpu_numa_node(device_index)
+    NUMA_STATUS.setdefault(device_index, f"bound to node {node}")
+    return node
+
+
+def _nvml_cpu_set(device_index: int):
+    """CPUs NVML considers local to the GPU (its NUMA node), or None.  Works where sysfs does not
+    expose the PCI device's node, as inside some containers."""
+    try:
+        import os
+
+        import pynvml
+
+        pynvml.nvmlInit()
+        props = torch.cuda.get_device_properties(device_index)
+        uuid = str(props.uuid)
+        h = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid) if not uuid.startswith("GPU-") else uuid)
+        words = (max(os.sched_getaffinity(0)) // 64) + 1
+        try:
+            mask = pynvml.nvmlDeviceGetCpuAffinityWithinScope(h, words, pynvml.NVML_AFFINITY_SCOPE_NODE)
+        except Exception:
+            mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {64 * i + bit for i, word in enumerate(mask) for bit in range(64) if (int(word) >> bit) & 1}
+        return cpus or None
+    except Exception:
+        return None
+
+
+def _bind_to_gpu_numa_node(device_index: int) -> Optional[int]:
     import os
 
     try:
@@ -43,6 +79,15 @@ def bind_to_gpu_numa_node(device_index: int) -> Optional[int]:
         with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
             node = int(f.read().strip())
         if node < 0:
+            cpus = _nvml_cpu_set(device_index)
+            allowed = (cpus or set()) & os.sched_getaffinity(0)
+            if allowed and len(allowed) < len(os.sched_getaffinity(0)):
+                os.sched_setaffinity(0, allowed)
+                NUMA_STATUS[device_index] = (f"sysfs reports numa_node = {node}; bound to the {len(allowed)} CPUs NVML "
+                                             f"lists as local to the GPU")
+                return -1
+            NUMA_STATUS[device_index] = (f"/sys/bus/pci/devices/{bus}/numa_node = {node} and NVML names no smaller "
+                                         f"CPU set: the host exposes no NUMA topology")
             return None
         with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
             cpus = set()
@@ -51,21 +96,29 @@ def bind_to_gpu_numa_node(device_index: int) -> Optional[int]:
                 cpus.update(range(int(lo), int(hi or lo) + 1))
         allowed = cpus & os.sched_getaffinity(0)
         if not allowed:
+            NUMA_STATUS[device_index] = f"node {node}: none of its CPUs is in this process's affinity mask"
             return None
         os.sched_setaffinity(0, allowed)
         return node
-    except Exception:
+    except Exception as e:
+        NUMA_STATUS[device_index] = f"topology not readable: {type(e).__name__}: {e}"
         return None
 
 
 class HostPrefill:
     def __init__(self, batch: int, seqlen: int, dim: int, dtype: torch.dtype, device="cuda",
                  chunk_batch: int = 4, masked: bool = True, mask_dtype: torch.dtype = torch.int64,
-                 send_masked_rows: bool = False):
+                 send_masked_rows: bool = False, skip_constant_rows: bool = False):
         self.device = torch.device(device)
         self.batch, self.seqlen, self.dim, self.dtype = batch, seqlen, dim, dtype
         self.chunk = max(1, min(chunk_batch, batch))
         self.send_masked_rows = send_masked_rows  # True: copy all of x, also the rows no kernel reads
+        self.skip_constant_rows = skip_constant_rows and masked  # True: act(bias) rows are written by the host
+        self.const_dev = torch.empty(1, 1, dim, dtype=dtype, device=self.device)
+        self.const_host = torch.empty(1, 1, dim, dtype=dtype).pin_memory()
+        self.zero_in = torch.zeros(1, 1, dim, dtype=dtype, device=self.device)
+        self.zero_mask = torch.zeros(1, 1, dtype=mask_dtype, device=self.device) if masked else None
+        self.last_d2h_bytes = 0
         self.x_dev = torch.empty(batch, seqlen, dim, dtype=dtype, device=self.device)
         self.y_dev = torch.empty_like(self.x_dev)
         self.m_dev = torch.empty(batch, seqlen, dtype=mask_dtype, device=self.device) if masked else None
@@ -90,6 +143,9 @@ class HostPrefill:
 
     @property
     def d2h_bytes(self) -> int:
+        """Bytes the most recent run() copied back to the host (all of y before any run)."""
+        if self.last_d2h_bytes:
+            return self.last_d2h_bytes
         return self.y_dev.numel() * self.y_dev.element_size()
 
     @staticmethod
@@ -113,6 +169,21 @@ class HostPrefill:
             lens = [self.seqlen] * self.batch
         row_bytes = self.dim * self.x_dev.element_size()
         sent = 0
+        received = 0
+        out_rows = None
+        if self.skip_constant_rows and masked:
+            # rows from out_rows[b] on have every tap masked: they equal act(bias) in every sequence.
+            # One masked single-step launch computes that row; the host fills it in while the copies run.
+            width = weight.shape[1]
+            out_rows = [min(self.seqlen, n + width - 1) for n in self.valid_prefix_lengths(mask_host)]
+            with torch.cuda.stream(self.s_run):
+                self.s_run.wait_stream(main)
+                causal_conv1d_fn(self.zero_in.transpose(1, 2), weight, bias, activation=activation,
+                                 attention_mask=self.zero_mask, out=self.const_dev.transpose(1, 2))
+                self.const_host.copy_(self.const_dev, non_blocking=True)
+                const_ready = torch.cuda.Event()
+                const_ready.record(self.s_run)
+            received += row_bytes
         for i, b0 in enumerate(range(0, self.batch, self.chunk)):
             b1 = min(b0 + self.chunk, self.batch)
             with torch.cuda.stream(self.s_h2d):
@@ -139,9 +210,22 @@ class HostPrefill:
                 self.ev_run[i].record(self.s_run)
             with torch.cuda.stream(self.s_d2h):
                 self.s_d2h.wait_event(self.ev_run[i])
-                y_host[b0:b1].copy_(self.y_dev[b0:b1], non_blocking=True)
+                if out_rows is None:
+                    y_host[b0:b1].copy_(self.y_dev[b0:b1], non_blocking=True)
+                    received += (b1 - b0) * self.seqlen * row_bytes
+                else:
+                    for b in range(b0, b1):
+                        if out_rows[b] > 0:
+                            y_host[b, : out_rows[b]].copy_(self.y_dev[b, : out_rows[b]], non_blocking=True)
+                            received += out_rows[b] * row_bytes
                 self.ev_out[i].record(self.s_d2h)
+        if out_rows is not None:
+            const_ready.synchronize()  # a [dim] vector: arrives long before the first chunk is back
+            for b in range(self.batch):
+                if out_rows[b] < self.seqlen:
+                    y_host[b, out_rows[b]:] = self.const_host[0]
         self.last_h2d_bytes = sent
+        self.last_d2h_bytes = received
         if join:
             self.join()
         return y_host

@@ -31,7 +31,7 @@ _MASK_DTYPES = {
 }
 
 
-_TMA_TUNING = {"stages", "ctas_per_sm", "slab_bytes", "rows_per_thread"}
+_TMA_TUNING = {"stages", "ctas_per_sm", "slab_bytes", "rows_per_thread", "claim_chunk", "empty_store", "classify", "pdl", "static_first", "test_expire"}
 
 
 def _activation_code(activation) -> int:
@@ -92,9 +92,26 @@ def _stream_handle(device: torch.device) -> int:
 # launches that can overlap on the GPU must not share it.  The kernel leaves it zeroed.
 _DYNAMIC_DEFAULT = True
 _SCRATCH = {}
+_TLS = threading.local()  # per host thread: prepared argument structs, and the fresh-scratch switch
+
+
+class fresh_scratch:
+    """Within this context the launch wrappers allocate their scheduler scratch per call instead of
+    keeping one buffer per stream (used by the torch.compile custom ops)."""
+
+    def __enter__(self):
+        _TLS.fresh_scratch = getattr(_TLS, "fresh_scratch", 0) + 1
+
+    def __exit__(self, *exc):
+        _TLS.fresh_scratch -= 1
 
 
 def _scheduler_scratch(device: torch.device, stream: int, nbytes: int) -> torch.Tensor:
+    if getattr(_TLS, "fresh_scratch", 0) or torch.cuda.is_current_stream_capturing():
+        # Memory allocated while a CUDA graph is being captured, or inside a compiled region (whose
+        # allocations may go to a graph's private pool also while it warms up), belongs to that graph: it
+        # must not be kept for later launches.  A buffer of its own, zeroed by a memset on the stream.
+        return torch.zeros(max(16384, (nbytes + 3) // 4), dtype=torch.int32, device=device)
     key = (device.index, stream)
     buf = _SCRATCH.get(key)
     if buf is None or buf.numel() * 4 < nbytes:
@@ -135,7 +152,11 @@ def causal_conv1d_fn(
 
     Reference arguments (model/model.py:460-466; autograd.py:501-510):
       weight ``[dim, width]`` (width 2..4), bias ``[dim]`` or None, activation None|"silu"|"swish",
-      ``seq_idx`` must be None (the reference never passes anything else),
+      ``seq_idx[batch, seqlen]`` (int32): packed variable-length rows.  Each time step names the
+        sequence it belongs to and a tap only counts when it carries the same value as the output
+        step, so sequences laid end to end in one row (``seq_idx_from_lengths``) give exactly the
+        results of a right-padded batch at the valid positions, without reading or writing padding.
+        The reference passes None (model/model.py:465); not combined with a mask or states,
       ``initial_states[batch, dim, >=width-1]``: history used instead of zeros (its last width-1 columns),
       ``return_final_states`` / ``final_states_out``: also return the last ``state_len`` inputs as
       ``[batch, dim, state_len]`` (default state_len = width-1), right-aligned like
@@ -186,11 +207,21 @@ def causal_conv1d_fn(
                                 activation, **kw)
     if out is not None:
         raise ValueError("out= cannot be used when a gradient is required")
+    if seq_idx is not None:
+        raise NotImplementedError("seq_idx (packed rows) is forward-only")
     res_tensor = residual if isinstance(residual, torch.Tensor) else None
     result = _CausalConv1dFunction.apply(x, weight, bias, res_tensor, activation, attention_mask,
                                          residual is True, return_final_states, final_states_out, kw,
                                          initial_states)
     return result if (return_final_states or final_states_out is not None) else result[0]
+
+
+def seq_idx_from_lengths(lengths, device=None) -> torch.Tensor:
+    """``seq_idx[1, sum(lengths)]`` (int32) for sequences of the given lengths packed end to end in one
+    row: 0 for every step of the first sequence, 1 for the second, and so on."""
+    lengths = torch.as_tensor(lengths, dtype=torch.int64, device="cpu")
+    ids = torch.repeat_interleave(torch.arange(lengths.numel(), dtype=torch.int32), lengths)
+    return ids.unsqueeze(0).to(device) if device is not None else ids.unsqueeze(0)
 
 
 def causal_conv1d_fn_multi(xs, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, activation=None, **kwargs):
@@ -280,11 +311,17 @@ def _prefill_forward(
     width = _check_weight_shapes(weight, bias, dim)
     if x.dtype not in _IO_DTYPES:
         raise ValueError(f"unsupported dtype {x.dtype}: expected float32, bfloat16 or float16")
-    if seq_idx is not None:
-        raise NotImplementedError("seq_idx is not supported")
     act = _activation_code(activation)
     _require_cuda(x, "Input")
     weight, bias = _align_weights(x, weight, bias)
+    if seq_idx is not None:
+        _require_cuda(seq_idx, "seq_idx")
+        if tuple(seq_idx.shape) != (batch, seqlen):
+            raise ValueError(f"seq_idx shape {tuple(seq_idx.shape)} does not match input shape ({batch}, {seqlen})")
+        if attention_mask is not None or initial_states is not None or return_final_states or final_states_out is not None:
+            raise ValueError("seq_idx cannot be combined with attention_mask, initial_states or final states")
+        if seq_idx.dtype != torch.int32:
+            seq_idx = seq_idx.to(torch.int32)
 
     if out is None:
         out = torch.empty_like(x)
@@ -304,6 +341,10 @@ def _prefill_forward(
     a.x_stride_b, a.x_stride_d, a.x_stride_t = x.stride()
     a.y_stride_b, a.y_stride_d, a.y_stride_t = out.stride()
     a.w_stride_d, a.w_stride_w = weight.stride()
+
+    if seq_idx is not None:
+        a.seq_idx = seq_idx.data_ptr()
+        a.seq_stride_b, a.seq_stride_t = seq_idx.stride()
 
     if attention_mask is not None:
         m = attention_mask
@@ -411,6 +452,7 @@ def causal_conv1d_bwd(
     need_dbias: bool = True,
     kernel: Optional[str] = None,
     dynamic_schedule: Optional[bool] = None,
+    tma: Optional[dict] = None,
 ):
     """Gradients of ``causal_conv1d_fn`` (with its fused mask / residual) for ``x[batch, dim, seqlen]``
     and the upstream gradient ``dy`` of the same shape: returns ``(dx, dweight, dbias)``.
@@ -420,7 +462,8 @@ def causal_conv1d_bwd(
     (causal-conv1d-mps/causal_conv1d_mps/causal_conv1d_kernel.mm:553-557, 771-776).
     ``residual=True`` means the forward added ``x`` to its output.  Formulas: include/vc1d.h.
     With ``initial_states[batch, dim, >=width-1]`` (the history of a chunked continuation) a fourth
-    result is returned: the gradient with respect to it.
+    result is returned: the gradient with respect to it.  ``tma``: tuning overrides of the TMA-staged
+    kernel (stages, ctas_per_sm, variant).
     """
     if x.dim() != 3:
         raise ValueError(f"Expected 3D input tensor (batch, dim, seqlen), got {x.dim()}D")
@@ -439,9 +482,9 @@ def causal_conv1d_bwd(
     dx = torch.empty_like(x)
     if dx.stride() != x.stride():
         dx = torch.empty_strided(x.shape, x.stride(), dtype=x.dtype, device=x.device)
-    # both fp32 accumulators in one zeroed allocation: one memset launch instead of two
+    # both fp32 accumulators in one allocation; the library clears it (inside its pre-pass when it has one)
     want_db = need_dbias and bias is not None
-    acc = torch.zeros(dim * (width + 1), dtype=torch.float32, device=x.device) if (need_dweight or want_db) else None
+    acc = torch.empty(dim * (width + 1), dtype=torch.float32, device=x.device) if (need_dweight or want_db) else None
     dweight = acc[: dim * width].view(dim, width) if need_dweight else None
     dbias = acc[dim * width:] if want_db else None
 
@@ -473,6 +516,7 @@ def causal_conv1d_bwd(
     a.residual = 1 if residual else 0
     a.dweight = dweight.data_ptr() if dweight is not None else None
     a.dbias = dbias.data_ptr() if dbias is not None else None
+    a.zero_grads = 1
     dinit = None
     if initial_states is not None:
         s0 = initial_states
@@ -491,6 +535,11 @@ def causal_conv1d_bwd(
     if kernel not in (None, "auto", "generic", "tma"):
         raise ValueError(f"unknown backward kernel {kernel!r}")
     a.kernel = _cabi.KERNEL_BY_NAME[kernel]
+    if tma:
+        for key, value in tma.items():
+            if key not in ("stages", "ctas_per_sm", "variant"):
+                raise ValueError(f"unknown TMA tuning key {key!r}; expected stages, ctas_per_sm or variant")
+            setattr(a, "tma_" + key, int(value))
     stream = _stream_handle(x.device)
     if dynamic_schedule or (dynamic_schedule is None and _DYNAMIC_DEFAULT):
         sc = _scheduler_scratch(x.device, stream, 4096 + batch * ((seqlen + 31) // 32))
@@ -505,6 +554,39 @@ def causal_conv1d_bwd(
     if initial_states is not None:
         return dx, dweight, dbias, dinit
     return dx, dweight, dbias
+
+
+def add_state_gradient(dx, dinit, dstate, mask):
+    """Gradient arriving through the final state returned by causal_conv1d_fn.  Column j of the state
+    ``[batch, dim, L]`` is the masked input of step ``T - L + j`` (model/model.py:470-489), or, left of step
+    0, a column of the initial state: add ``dstate`` there.  Returns (dx, dinit)."""
+    L, T = dstate.shape[2], dx.shape[2]
+    n = min(L, T)
+    g = dstate[..., L - n:]
+    if mask is not None:
+        g = g * mask[:, None, T - n:].to(g.dtype)
+    dx[..., T - n:] += g.to(dx.dtype)
+    if T < L and dinit is not None:
+        k = min(L - T, dinit.shape[2])
+        dinit[..., dinit.shape[2] - k:] += dstate[..., L - T - k: L - T].to(dinit.dtype)
+    return dx, dinit
+
+
+def add_updated_state_gradient(dx, dstate, dstate_after, seqlens):
+    """Gradient arriving through the state a decode step left behind: the step moved the old columns
+    (or kept them in place, circular state) and stored x in one column.  Returns (dx, dstate)."""
+    L = dstate_after.shape[2]
+    if seqlens is not None:
+        pos = (seqlens.long() % L).view(-1, 1, 1).expand(-1, dstate_after.shape[1], 1)
+        dx = dx + dstate_after.gather(2, pos).squeeze(-1)
+        if dstate is not None:
+            dstate = dstate + dstate_after.scatter(2, pos, 0.0)
+    else:
+        dx = dx + dstate_after[..., L - 1]
+        if dstate is not None and L > 1:
+            dstate = dstate.clone()
+            dstate[..., 1:] += dstate_after[..., : L - 1]
+    return dx, dstate
 
 
 class _CausalConv1dFunction(torch.autograd.Function):
@@ -528,13 +610,14 @@ class _CausalConv1dFunction(torch.autograd.Function):
         ctx.activation = activation
         ctx.residual_is_x = residual_is_x
         ctx.has_res_tensor = res_tensor is not None
+        ctx.has_state = state is not None
         if state is None:
             state = x.new_empty(0)
-        ctx.mark_non_differentiable(state)
+            ctx.mark_non_differentiable(state)
         return y, state
 
     @staticmethod
-    def backward(ctx, dy, _dstate):
+    def backward(ctx, dy, dstate):
         x, weight, bias, mask, init = ctx.saved_tensors
         need_x, need_w, need_b = ctx.needs_input_grad[0], ctx.needs_input_grad[1], ctx.needs_input_grad[2]
         grads = causal_conv1d_bwd(
@@ -545,6 +628,10 @@ class _CausalConv1dFunction(torch.autograd.Function):
         )
         dx, dw, db = grads[0], grads[1], grads[2]
         dinit = grads[3] if ctx.has_init else None
+        if ctx.has_state and dstate is not None:
+            # the returned final state is part of the graph (chunked training feeds it to the next
+            # chunk as initial_states): its gradient lands on the last inputs of this chunk
+            dx, dinit = add_state_gradient(dx, dinit, dstate, mask if ctx.has_mask else None)
         return (
             dx if need_x else None,
             dw.to(weight.dtype) if (need_w and dw is not None) else None,
@@ -576,8 +663,20 @@ def causal_conv1d_update(
         if out is not None:
             raise ValueError("out= cannot be used under torch.compile")
         squeeze = x.dim() == 3
-        y = torch.ops.vc1d.update(x.squeeze(-1) if squeeze else x, conv_state, weight, bias, cache_seqlens,
-                                  _activation_code(activation), bool(residual))
+        x2 = x.squeeze(-1) if squeeze else x
+        wants_grad = torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad or conv_state.requires_grad
+                                                  or (bias is not None and bias.requires_grad))
+        if wants_grad:
+            # differentiable form: the step as a function of the old state; the caller's tensor then takes
+            # the new values, detached (inside a compiled graph the updated state carries no gradient)
+            # (a copy goes in: the backward formula needs the state the step started from, and the caller's
+            # tensor is overwritten below)
+            y, new_state = torch.ops.vc1d.update_fn(x2, conv_state.clone(), weight, bias, cache_seqlens,
+                                                    _activation_code(activation), bool(residual))
+            conv_state.detach().copy_(new_state.detach())
+        else:
+            y = torch.ops.vc1d.update(x2, conv_state, weight, bias, cache_seqlens, _activation_code(activation),
+                                      bool(residual))
         return y.unsqueeze(-1) if squeeze else y
     needs_grad = torch.is_grad_enabled() and (
         x.requires_grad or weight.requires_grad or conv_state.requires_grad
@@ -686,19 +785,7 @@ class _CausalConv1dUpdateFunction(torch.autograd.Function):
             seqlens if ctx.has_seqlens else None, residual=ctx.residual, need_dstate=ctx.needs_input_grad[1],
         )
         if dstate_after is not None:
-            # gradient arriving through the updated state: the step moved the old columns (or kept
-            # them, circular) and stored x in one column
-            L = before.shape[2]
-            if ctx.has_seqlens:
-                pos = (seqlens.long() % L).view(-1, 1, 1).expand(-1, before.shape[1], 1)
-                dx = dx + dstate_after.gather(2, pos).squeeze(-1)
-                if dstate is not None:
-                    dstate = dstate + dstate_after.scatter(2, pos, 0.0)
-            else:
-                dx = dx + dstate_after[..., L - 1]
-                if dstate is not None and L > 1:
-                    dstate = dstate.clone()
-                    dstate[..., 1:] += dstate_after[..., : L - 1]
+            dx, dstate = add_updated_state_gradient(dx, dstate, dstate_after, seqlens if ctx.has_seqlens else None)
         if ctx.squeeze:
             dx = dx.unsqueeze(-1)
         return (
@@ -713,7 +800,7 @@ class _CausalConv1dUpdateFunction(torch.autograd.Function):
 # Prepared vc1d_update_args per call signature (shapes, strides, dtypes, options): a decode step is
 # launch-bound, so a repeated call only refreshes the five pointers instead of re-validating and
 # re-filling the whole struct.
-_TLS = threading.local()  # per host thread: the library call releases the GIL while it reads the struct
+# (_TLS, per host thread: the library call releases the GIL while it reads the struct)
 
 
 def _update_fast(x, conv_state, weight, bias, activation, cache_seqlens, residual, out, kernel, block_threads):
