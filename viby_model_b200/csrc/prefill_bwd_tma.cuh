@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES, VARIANT>::kThre
             const int t0 = (rt - b * p.n_ttile) * G::kTileRows;
             // a tile whose x rows are all masked out needs no x: only its dy box is copied
             // class from the pre-pass: all mask rows one, mixed, or every x row masked out (no x box)
-            const int cls_now = p.gtable != nullptr ? (int)__ldg(p.gtable + rt)
+            const int cls_now = p.gtable != nullptr ? (int)__ldcg(p.gtable + rt)  // written by the pre-pass while this grid was resident: no read-only path
                                                     : (p.mask != nullptr ? (int)TILE_MIXED : (int)TILE_FULL);
             const bool need_x = cls_now != TILE_EMPTY;
             rt = next_tile();  // fetched while this tile waits for its slot

@@ -108,7 +108,7 @@ def _bind_to_gpu_numa_node(device_index: int) -> Optional[int]:
 class HostPrefill:
     def __init__(self, batch: int, seqlen: int, dim: int, dtype: torch.dtype, device="cuda",
                  chunk_batch: int = 4, masked: bool = True, mask_dtype: torch.dtype = torch.int64,
-                 send_masked_rows: bool = False, skip_constant_rows: bool = False):
+                 send_masked_rows: bool = False, skip_constant_rows: bool = False, copy_streams: int = 1):
         self.device = torch.device(device)
         self.batch, self.seqlen, self.dim, self.dtype = batch, seqlen, dim, dtype
         self.chunk = max(1, min(chunk_batch, batch))
@@ -122,9 +122,12 @@ class HostPrefill:
         self.x_dev = torch.empty(batch, seqlen, dim, dtype=dtype, device=self.device)
         self.y_dev = torch.empty_like(self.x_dev)
         self.m_dev = torch.empty(batch, seqlen, dtype=mask_dtype, device=self.device) if masked else None
-        self.s_h2d = torch.cuda.Stream(self.device)
+        # copies of consecutive chunks can alternate between copy_streams streams per direction (measured on
+        # one B200: 1 to 4 streams and chunks of 2 to 8 sequences all give the same rate, the link's)
+        k = max(1, int(copy_streams))
+        self.s_h2d_all = [torch.cuda.Stream(self.device) for _ in range(k)]
+        self.s_d2h_all = [torch.cuda.Stream(self.device) for _ in range(k)]
         self.s_run = torch.cuda.Stream(self.device)
-        self.s_d2h = torch.cuda.Stream(self.device)
         n = (batch + self.chunk - 1) // self.chunk
         self.ev_in = [torch.cuda.Event() for _ in range(n)]
         self.ev_run = [torch.cuda.Event() for _ in range(n)]
@@ -162,7 +165,8 @@ class HostPrefill:
         Returns y_host.  With ``join=True`` all work has been ordered into the caller's current stream on
         return; with ``join=False`` call ``join()`` (or wait on ``ev_out[-1]``) before reading y_host."""
         main = torch.cuda.current_stream(self.device)
-        self.s_h2d.wait_stream(main)  # the inputs may come from work queued on the caller's stream
+        for s in self.s_h2d_all:
+            s.wait_stream(main)  # the inputs may come from work queued on the caller's stream
         masked = self.m_dev is not None and mask_host is not None
         lens = self.valid_prefix_lengths(mask_host) if masked else None
         if self.send_masked_rows and lens is not None:
@@ -186,8 +190,10 @@ class HostPrefill:
             received += row_bytes
         for i, b0 in enumerate(range(0, self.batch, self.chunk)):
             b1 = min(b0 + self.chunk, self.batch)
-            with torch.cuda.stream(self.s_h2d):
-                self.s_h2d.wait_event(self.ev_run[i])  # the previous batch's kernel has read this chunk
+            s_h2d = self.s_h2d_all[i % len(self.s_h2d_all)]
+            s_d2h = self.s_d2h_all[i % len(self.s_d2h_all)]
+            with torch.cuda.stream(s_h2d):
+                s_h2d.wait_event(self.ev_run[i])  # the previous batch's kernel has read this chunk
                 if masked:
                     for b in range(b0, b1):
                         if lens[b] > 0:
@@ -198,7 +204,7 @@ class HostPrefill:
                 else:
                     self.x_dev[b0:b1].copy_(x_host[b0:b1], non_blocking=True)
                     sent += (b1 - b0) * self.seqlen * row_bytes
-                self.ev_in[i].record(self.s_h2d)
+                self.ev_in[i].record(s_h2d)
             with torch.cuda.stream(self.s_run):
                 self.s_run.wait_event(self.ev_in[i])
                 self.s_run.wait_event(self.ev_out[i])  # the previous batch's result has left this chunk
@@ -208,8 +214,8 @@ class HostPrefill:
                     out=self.y_dev[b0:b1].transpose(1, 2),
                 )
                 self.ev_run[i].record(self.s_run)
-            with torch.cuda.stream(self.s_d2h):
-                self.s_d2h.wait_event(self.ev_run[i])
+            with torch.cuda.stream(s_d2h):
+                s_d2h.wait_event(self.ev_run[i])
                 if out_rows is None:
                     y_host[b0:b1].copy_(self.y_dev[b0:b1], non_blocking=True)
                     received += (b1 - b0) * self.seqlen * row_bytes
@@ -218,7 +224,7 @@ class HostPrefill:
                         if out_rows[b] > 0:
                             y_host[b, : out_rows[b]].copy_(self.y_dev[b, : out_rows[b]], non_blocking=True)
                             received += out_rows[b] * row_bytes
-                self.ev_out[i].record(self.s_d2h)
+                self.ev_out[i].record(s_d2h)
         if out_rows is not None:
             const_ready.synchronize()  # a [dim] vector: arrives long before the first chunk is back
             for b in range(self.batch):
@@ -233,6 +239,5 @@ class HostPrefill:
     def join(self) -> None:
         """Order everything queued so far into the caller's current stream."""
         main = torch.cuda.current_stream(self.device)
-        main.wait_stream(self.s_d2h)
-        main.wait_stream(self.s_run)
-        main.wait_stream(self.s_h2d)
+        for s in self.s_d2h_all + [self.s_run] + self.s_h2d_all:
+            main.wait_stream(s)

@@ -45,36 +45,6 @@ def causal_conv1d_fwd(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torc
     return causal_conv1d_fn(x.contiguous(), weight, bias, activation="silu" if silu_activation else None)
 
 
-def _normalise_mask(attention_mask: torch.Tensor, B: int, T: int) -> torch.Tensor:
-    """Bring a mask to ``[B, T]`` the way the reference does (__init__.py:232-293)."""
-    m = attention_mask
-    if m.dim() > 2:
-        m = m.squeeze()
-    if m.dim() == 1:
-        if m.numel() == T:
-            m = m.view(1, T).expand(B, T)
-        elif m.numel() == B:
-            m = m.view(B, 1).expand(B, T)
-        elif m.numel() == B * T:
-            m = m.view(B, T)
-        else:
-            raise ValueError(f"Attention mask 1D length {m.numel()} cannot be normalized to (B, T)={(B, T)}")
-    elif m.dim() == 2:
-        if tuple(m.shape) == (B, T):
-            pass
-        elif tuple(m.shape) in ((1, T), (B, 1)):
-            m = m.expand(B, T)
-        elif tuple(m.shape) == (T, B):
-            m = m.t()
-        elif m.shape[0] == B and m.shape[1] > T:
-            m = m[:, -T:]  # generate step: a full-history mask against the current tokens
-        else:
-            raise ValueError(f"Attention mask 2D shape {tuple(m.shape)} must be broadcastable to (B, T)={(B, T)}")
-    else:
-        raise ValueError(f"Attention mask dim {m.dim()} not supported; expected 1D/2D convertible to (B, T)")
-    return m
-
-
 def short_conv_fused(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
                      attention_mask: Optional[torch.Tensor] = None, activation: bool = True,
                      residual: bool = True) -> torch.Tensor:
@@ -107,7 +77,10 @@ def short_conv_fused(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch
     _check_cuda(bias, "Bias tensor")
     _check_cuda(attention_mask, "Attention mask")
     x = x.contiguous()
-    m = _normalise_mask(attention_mask, B, T) if attention_mask is not None else None
+    # (the reference goes on to squeeze / broadcast / transpose other mask shapes, __init__.py:238-293, but its
+    # own check above, :215-221, lets nothing but [batch, seqlen] through: that code is unreachable and has
+    # no counterpart here)
+    m = attention_mask
     y = causal_conv1d_fn(x.transpose(1, 2), weight, bias, activation="silu" if activation else None,
                          attention_mask=m, residual=True if residual else None)
     return y.transpose(1, 2)
