@@ -227,6 +227,11 @@ typedef struct vc1d_prefill_bwd_args {
     int32_t init_len;
     int32_t zero_grads;         /* 1: the library clears dweight / dbias itself before accumulating (on the stream,
                                    folded into the tile-classification pre-pass when the launch has one) */
+    /* Packed variable-length rows, as in vc1d_prefill_args: sequence id of every step; taps and their
+     * gradients stay inside a run of equal ids.  Not combined with mask or initial_state
+     * (VC1D_E_SHAPE).  Such launches take the generic kernel. */
+    const int32_t* seq_idx;
+    int64_t seq_stride_b, seq_stride_t;
 } vc1d_prefill_bwd_args;
 
 VC1D_API int vc1d_prefill_bwd(const vc1d_prefill_bwd_args* args, void* stream);

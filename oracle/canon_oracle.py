@@ -356,6 +356,29 @@ def causal_conv1d_bwd_ref(
     return dx.to(x.dtype), dweight, dbias
 
 
+def causal_conv1d_packed_bwd_ref(x, weight, bias, dy, activation=None, *, seq_idx, residual: bool = False,
+                                 compute_dtype: torch.dtype = torch.float64):
+    """Oracle of the backward pass on packed variable-length rows (``seq_idx``): every maximal run of
+    equal ids is one sequence of causal_conv1d_bwd_ref; dweight and dbias add up over the runs."""
+    B, D, T = x.shape
+    dx = torch.zeros_like(x)
+    dweight = torch.zeros(D, weight.shape[1], dtype=compute_dtype)
+    dbias = torch.zeros(D, dtype=compute_dtype) if bias is not None else None
+    ids = seq_idx.to(torch.int64)
+    for b in range(B):
+        row = ids[b]
+        cuts = [0] + (torch.nonzero(row[1:] != row[:-1]).flatten() + 1).tolist() + [T]
+        for t0, t1 in zip(cuts[:-1], cuts[1:]):
+            if t1 > t0:
+                sdx, sdw, sdb = causal_conv1d_bwd_ref(x[b:b + 1, :, t0:t1], weight, bias, dy[b:b + 1, :, t0:t1], activation,
+                                                      residual=residual, compute_dtype=compute_dtype)
+                dx[b:b + 1, :, t0:t1] = sdx
+                dweight += sdw
+                if dbias is not None:
+                    dbias += sdb
+    return dx, dweight, dbias
+
+
 def causal_conv1d_update_bwd_ref(x, conv_state, weight, bias, dy, activation=None, *, residual: bool = False,
                                  compute_dtype: torch.dtype = torch.float64):
     """Oracle of the backward pass of one decode step (shifting state), restating

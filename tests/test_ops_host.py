@@ -46,7 +46,7 @@ def test_activation_and_seq_idx():
     # seq_idx is an operand like any other: host tensors are refused, never computed on the CPU
     with pytest.raises(ValueError, match="must be on a CUDA device"):
         V.causal_conv1d_fn(x, w, seq_idx=torch.zeros(2, 8, dtype=torch.int32))
-    with pytest.raises(NotImplementedError, match="forward-only"):
+    with pytest.raises(ValueError, match="must be on a CUDA device"):
         V.causal_conv1d_fn(x.requires_grad_(), w, seq_idx=torch.zeros(2, 8, dtype=torch.int32))
 
 

@@ -81,3 +81,33 @@ def test_update_backward_oracle_matches_autograd(L, act):
     dx, dst, dw, db = O.causal_conv1d_update_bwd_ref(x.detach(), st.detach(), w.detach(), b.detach(), dy, act, residual=True)
     for a, r in ((dx, x.grad), (dst, st.grad), (dw, w.grad), (db, b.grad)):
         assert torch.allclose(a, r, rtol=1e-10, atol=1e-10)
+
+
+RIGHT_PADDED_BWD = [c for c in GOLDEN_BWD_CASES if c.has("mask") and c.mask == "right"]
+
+
+@pytest.mark.parametrize("c", RIGHT_PADDED_BWD, ids=[repr(c) for c in RIGHT_PADDED_BWD])
+def test_packed_backward_oracle_equals_padded_backward_on_valid_positions(c):
+    """Gradients on packed rows (seq_idx) against the padded backward oracle, which is pinned to the
+    gradients of the reference's CanonLayer above: with the upstream gradient of the padded steps set to
+    zero, dx at the valid positions, dweight and dbias must be the same numbers.  (Without that, the
+    padded steps right behind a sequence send gradient into its last inputs and into the parameters.)"""
+    x, w, b, m, dy = _inputs(c)
+    lens = [int(v) for v in (m != 0).sum(1)]
+    if sum(lens) == 0:
+        pytest.skip("no valid position")
+    dy = dy * m.unsqueeze(-1).to(dy.dtype)
+    pdx, pdw, pdb = O.causal_conv1d_bwd_ref(x.transpose(1, 2), w, b, dy.transpose(1, 2), c.activation, attention_mask=m)
+    xp = torch.cat([x[i, :n] for i, n in enumerate(lens)], 0).unsqueeze(0)
+    dyp = torch.cat([dy[i, :n] for i, n in enumerate(lens)], 0).unsqueeze(0)
+    ids = torch.cat([torch.full((n,), i, dtype=torch.int32) for i, n in enumerate(lens)]).unsqueeze(0)
+    kdx, kdw, kdb = O.causal_conv1d_packed_bwd_ref(xp.transpose(1, 2), w, b, dyp.transpose(1, 2), c.activation,
+                                                   seq_idx=ids)
+    at = 0
+    for i, n in enumerate(lens):
+        assert torch.equal(kdx[0, :, at:at + n], pdx[i, :, :n]), f"sequence {i}"
+        at += n
+    assert torch.allclose(kdw, pdw, rtol=1e-9, atol=1e-9)
+    if b is not None:
+        # padded steps contribute silu'(bias) * 0 to dbias once their upstream gradient is zero
+        assert torch.allclose(kdb, pdb, rtol=1e-9, atol=1e-9)

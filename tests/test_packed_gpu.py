@@ -142,3 +142,85 @@ def test_packed_argument_errors():
         V.causal_conv1d_fn(x, w, seq_idx=ids, attention_mask=torch.ones(1, 40, device=DEV))
     with pytest.raises(ValueError, match="cannot be combined"):
         V.causal_conv1d_fn(x, w, seq_idx=ids, return_final_states=True)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("W", [2, 3, 4])
+@pytest.mark.parametrize("act", [None, "silu"])
+def test_packed_backward_against_oracle(act, W, dtype):
+    """Gradients on packed rows: dx, dweight, dbias against the float64 oracle (each run of equal ids
+    differentiated on its own), sequence starts at every offset of a thread's 128-row chunk."""
+    D = 72
+    lens = [1, 2, 3, 125, 1, 130, 4, 127, 128, 129, 64, 5]
+    x = O.seeded((1, sum(lens), D), 41, "normal", dtype)
+    dy = O.seeded((1, sum(lens), D), 42, "normal", dtype)
+    w = O.seeded((D, W), 43, "uniform", dtype)
+    b = O.seeded((D,), 44, "uniform", dtype)
+    ids = V.seq_idx_from_lengths(lens)
+    for residual in (False, True):
+        before = V.launch_count()
+        dx, dw, db = V.causal_conv1d_bwd(x.to(DEV).transpose(1, 2), w.to(DEV), b.to(DEV), dy.to(DEV).transpose(1, 2), act,
+                                         residual=residual, seq_idx=ids.to(DEV))
+        assert V.launch_count() == before + 1 and V.last_kernel() == "bwd_generic"
+        rdx, rdw, rdb = O.causal_conv1d_packed_bwd_ref(x.transpose(1, 2), w, b, dy.transpose(1, 2), act, seq_idx=ids,
+                                                       residual=residual)
+        sdx, _, _ = O.causal_conv1d_packed_bwd_ref(x.abs().transpose(1, 2), w.abs(), None, dy.abs().transpose(1, 2), None,
+                                                   seq_idx=ids, residual=residual)
+        ulp = 2.0 ** -23 if dtype == torch.float32 else 2.0 ** -7
+        bound = 1.1 * sdx.double() * (ulp * 1.01 + 4e-6) + 1e-7
+        assert bool(((dx.cpu().double() - rdx.double()).abs() <= bound).all())
+        n = sum(lens)
+        assert torch.allclose(dw.cpu().double(), rdw, rtol=2e-4, atol=2e-5 * (float(rdw.abs().max()) + 1e-3) * n ** 0.5)
+        assert torch.allclose(db.cpu().double(), rdb, rtol=2e-4, atol=2e-5 * (float(rdb.abs().max()) + 1e-3) * n ** 0.5)
+
+
+def test_packed_autograd_equals_padded_autograd():
+    """Training on packed rows: gradients of a loss over the valid positions equal those of the padded,
+    masked batch (whose backward runs on the TMA-staged kernel) -- dx bit for bit at the valid positions."""
+    B, T, D, W = 6, 300, 256, 4
+    g = torch.Generator().manual_seed(9)
+    lens = [300, 1, 77, 128, 129, 250]
+    x = torch.randn(B, T, D, generator=g).bfloat16()
+    coef = torch.randn(B, T, D, generator=g).bfloat16()
+    m = torch.arange(T)[None, :] < torch.tensor(lens)[:, None]
+    w0 = (torch.rand(D, W, generator=g) - 0.5).bfloat16()
+    b0 = (torch.rand(D, generator=g) - 0.5).bfloat16()
+
+    xd = x.to(DEV).requires_grad_(True)
+    wd, bd = w0.to(DEV).requires_grad_(True), b0.to(DEV).requires_grad_(True)
+    y = V.causal_conv1d_fn(xd.transpose(1, 2), wd, bd, activation="silu", attention_mask=m.to(DEV)).transpose(1, 2)
+    (y * (coef * m.unsqueeze(-1)).to(DEV)).sum().backward()
+
+    xp = pack(x, lens).to(DEV).requires_grad_(True)
+    cp = pack(coef, lens).to(DEV)
+    wp, bp = w0.to(DEV).requires_grad_(True), b0.to(DEV).requires_grad_(True)
+    ids = V.seq_idx_from_lengths(lens, device=DEV)
+    yp = V.causal_conv1d_fn(xp.transpose(1, 2), wp, bp, activation="silu", seq_idx=ids).transpose(1, 2)
+    (yp * cp).sum().backward()
+    at = 0
+    for i, n in enumerate(lens):
+        assert torch.equal(xp.grad[0, at:at + n], xd.grad[i, :n]), f"sequence {i}"
+        at += n
+    assert torch.allclose(wp.grad.float(), wd.grad.float(), rtol=2e-2, atol=2e-2 * float(wd.grad.float().abs().max()))
+    assert torch.allclose(bp.grad.float(), bd.grad.float(), rtol=2e-2, atol=2e-2 * float(bd.grad.float().abs().max()))
+
+
+def test_packed_ids_that_repeat_are_separate_sequences():
+    """Sequences are runs of equal ids: an id that comes back later in the row names a new sequence
+    (every kernel and the oracle agree on that)."""
+    D, W = 128, 4
+    ids = torch.tensor([[3, 3, 7, 3, 3, 3, 7, 7] * 40], dtype=torch.int32)
+    T = ids.shape[1]
+    x = O.seeded((1, T, D), 51, "normal", torch.float32)
+    w = O.seeded((D, W), 52, "uniform", torch.float32)
+    ref = O.causal_conv1d_packed_ref(x.transpose(1, 2), w, None, "silu", seq_idx=ids)
+    for kernel in ("generic", "tma"):
+        y = V.causal_conv1d_fn(x.to(DEV).transpose(1, 2), w.to(DEV), None, seq_idx=ids.to(DEV), activation="silu",
+                               kernel=kernel)
+        assert_close_to_oracle(y, ref, kernel)
+    dy = O.seeded((1, T, D), 53, "normal", torch.float32)
+    dx, dw, _ = V.causal_conv1d_bwd(x.to(DEV).transpose(1, 2), w.to(DEV), None, dy.to(DEV).transpose(1, 2), "silu",
+                                    seq_idx=ids.to(DEV))
+    rdx, rdw, _ = O.causal_conv1d_packed_bwd_ref(x.transpose(1, 2), w, None, dy.transpose(1, 2), "silu", seq_idx=ids)
+    assert torch.allclose(dx.cpu(), rdx, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(dw.cpu().double(), rdw, rtol=1e-4, atol=1e-4)

@@ -136,6 +136,9 @@ class PrefillBwdArgs(C.Structure):
         ("dinitial_state", C.c_void_p),
         ("init_len", C.c_int32),
         ("zero_grads", C.c_int32),
+        ("seq_idx", C.c_void_p),
+        ("seq_stride_b", C.c_int64),
+        ("seq_stride_t", C.c_int64),
     ]
 
 

@@ -29,6 +29,8 @@ struct BGParams {
     void* dinit;        // its gradient, or NULL
     float* dweight;
     float* dbias;
+    const int* seq;     // sequence id of every step (packed rows), or NULL
+    long long ssb, sst;
     long long sxb, sxd, sxt;  // elements
     long long sgb, sgd, sgt;
     long long sdb, sdd, sdt;
@@ -113,16 +115,36 @@ __global__ void __launch_bounds__(128) k_prefill_bwd_generic(const BGParams p) {
             T* drow = reinterpret_cast<T*>(p.dinit) + (b * p.D + d) * p.init_len;
             for (int col = 0; col < p.init_len - H; ++col) drow[col] = E::from_float(0.f);
         }
-        // xw[3] is xm[j], xw[2] xm[j-1], ...; gw likewise for g
+        // sequence id of a row (packed rows): a tap counts only between rows of one sequence
+        auto seq_id = [&](int t) -> int {
+            if (p.seq == nullptr || t < 0 || t >= p.T) return 0;
+            return p.seq[b * p.ssb + (long long)t * p.sst];
+        };
+        // xw[3] is xm[j], xw[2] xm[j-1], ...; gw likewise for g, idw for the sequence ids
         float xw[4] = {0.f, 0.f, 0.f, 0.f};
         float gw[4] = {0.f, 0.f, 0.f, 0.f};
+        int idw[4] = {0, 0, 0, 0};
         float mk_unused;
-        for (int i = 0; i < H; ++i) xw[4 - H + i] = masked_x(c0 - H + i, mk_unused);  // rows before the chunk
+        for (int i = 0; i < H; ++i) {  // rows before the chunk
+            xw[4 - H + i] = masked_x(c0 - H + i, mk_unused);
+            idw[4 - H + i] = seq_id(c0 - H + i);
+        }
         float mkw[4] = {1.f, 1.f, 1.f, 1.f};  // mask of rows j-3 .. j (for dx of row j-H)
         for (int j = c0; j < c1 + H; ++j) {
             xw[0] = xw[1]; xw[1] = xw[2]; xw[2] = xw[3];
             mkw[0] = mkw[1]; mkw[1] = mkw[2]; mkw[2] = mkw[3];
+            idw[0] = idw[1]; idw[1] = idw[2]; idw[2] = idw[3];
             xw[3] = masked_x(j, mkw[3]);
+            idw[3] = seq_id(j);
+            if (p.seq != nullptr) {
+                // inputs above the start of row j's sequence (the run of equal ids that ends at j) are no taps
+                // of row j, nor of any later row
+                bool cut = false;
+                for (int i = 2; i >= 0; --i) {
+                    cut |= (idw[i] != idw[3]);
+                    if (cut) xw[i] = 0.f;
+                }
+            }
             float g = 0.f;
             if (j < p.T) {
                 g = E::to_float(dy[b * p.sgb + (long long)d * p.sgd + (long long)j * p.sgt]);
@@ -147,7 +169,15 @@ __global__ void __launch_bounds__(128) k_prefill_bwd_generic(const BGParams p) {
             }
             if (t >= c0) {  // t < c1 holds by the loop bound
                 float acc = 0.f;
-                for (int w = 0; w < W; ++w) acc = fmaf(wt[w], gw[3 - w], acc);
+                // g of row j - w = t + (H - w) reaches input row t through weight[w]; with packed rows only
+                // while the run of equal ids that row t belongs to lasts
+                int reach = H;
+                if (p.seq != nullptr) {
+                    reach = 0;
+                    while (reach < H && idw[3 - H + reach + 1] == idw[3 - H]) ++reach;
+                }
+                for (int w = 0; w < W; ++w)
+                    if (H - w <= reach) acc = fmaf(wt[w], gw[3 - w], acc);
                 acc *= mkw[3 - H];
                 if (p.residual) acc += E::to_float(dy[b * p.sgb + (long long)d * p.sgd + (long long)t * p.sgt]);
                 dx[b * p.sdb + (long long)d * p.sdd + (long long)t * p.sdt] = E::from_float(acc);
@@ -167,6 +197,7 @@ cudaError_t launch_prefill_bwd_generic(const vc1d_prefill_bwd_args& a, cudaStrea
     p.weight = a.weight; p.bias = a.bias; p.mask = a.mask;
     p.init = a.initial_state; p.dinit = a.dinitial_state; p.init_len = a.init_len;
     p.dweight = a.dweight; p.dbias = a.dbias;
+    p.seq = a.seq_idx; p.ssb = a.seq_stride_b; p.sst = a.seq_stride_t;
     p.sxb = a.x_stride_b; p.sxd = a.x_stride_d; p.sxt = a.x_stride_t;
     p.sgb = a.dy_stride_b; p.sgd = a.dy_stride_d; p.sgt = a.dy_stride_t;
     p.sdb = a.dx_stride_b; p.sdd = a.dx_stride_d; p.sdt = a.dx_stride_t;

@@ -83,15 +83,21 @@ __global__ void __launch_bounds__(256) k_prefill_generic(const GParams p) {
         acc = (p.wdtype == VC1D_F32) ? reinterpret_cast<const float*>(p.bias)[d]
                                      : E::to_float(reinterpret_cast<const T*>(p.bias)[d]);
     }
+    // packed rows: only the steps right above t that carry its sequence id are taps
+    int reach = p.W - 1;
+    if (p.seq != nullptr) {
+        const int* ids = p.seq + b * p.ssb;
+        const int mine = ids[(long long)t * p.sst];
+        reach = 0;
+        while (reach < p.W - 1 && t - reach - 1 >= 0 && ids[(long long)(t - reach - 1) * p.sst] == mine) ++reach;
+    }
     for (int w = 0; w < p.W; ++w) {
         const long long widx = (long long)d * p.wsd + (long long)w * p.wsw;
         const float wv = (p.wdtype == VC1D_F32) ? reinterpret_cast<const float*>(p.weight)[widx]
                                                 : E::to_float(reinterpret_cast<const T*>(p.weight)[widx]);
-        const int tt = t - (p.W - 1 - w);
-        // a tap from another sequence of the same packed row does not count
-        if (p.seq != nullptr && tt >= 0 && p.seq[b * p.ssb + (long long)tt * p.sst] != p.seq[b * p.ssb + (long long)t * p.sst])
-            continue;
-        acc = fmaf(wv, masked_input<DT>(p, x, b, d, tt), acc);
+        const int back = p.W - 1 - w;
+        if (back > reach) continue;  // the tap lies in another sequence of the same packed row
+        acc = fmaf(wv, masked_input<DT>(p, x, b, d, t - back), acc);
     }
     if (p.act) acc = silu1<E::kPreciseSilu>(acc);
     if (p.res != nullptr) {

@@ -156,7 +156,8 @@ def causal_conv1d_fn(
         sequence it belongs to and a tap only counts when it carries the same value as the output
         step, so sequences laid end to end in one row (``seq_idx_from_lengths``) give exactly the
         results of a right-padded batch at the valid positions, without reading or writing padding.
-        The reference passes None (model/model.py:465); not combined with a mask or states,
+        The reference passes None (model/model.py:465); not combined with a mask or states; differentiable
+        (the backward of packed rows runs on the scalar kernel),
       ``initial_states[batch, dim, >=width-1]``: history used instead of zeros (its last width-1 columns),
       ``return_final_states`` / ``final_states_out``: also return the last ``state_len`` inputs as
       ``[batch, dim, state_len]`` (default state_len = width-1), right-aligned like
@@ -207,9 +208,8 @@ def causal_conv1d_fn(
                                 activation, **kw)
     if out is not None:
         raise ValueError("out= cannot be used when a gradient is required")
-    if seq_idx is not None:
-        raise NotImplementedError("seq_idx (packed rows) is forward-only")
     res_tensor = residual if isinstance(residual, torch.Tensor) else None
+    kw["seq_idx"] = seq_idx
     result = _CausalConv1dFunction.apply(x, weight, bias, res_tensor, activation, attention_mask,
                                          residual is True, return_final_states, final_states_out, kw,
                                          initial_states)
@@ -453,6 +453,7 @@ def causal_conv1d_bwd(
     kernel: Optional[str] = None,
     dynamic_schedule: Optional[bool] = None,
     tma: Optional[dict] = None,
+    seq_idx: Optional[torch.Tensor] = None,
 ):
     """Gradients of ``causal_conv1d_fn`` (with its fused mask / residual) for ``x[batch, dim, seqlen]``
     and the upstream gradient ``dy`` of the same shape: returns ``(dx, dweight, dbias)``.
@@ -463,7 +464,8 @@ def causal_conv1d_bwd(
     ``residual=True`` means the forward added ``x`` to its output.  Formulas: include/vc1d.h.
     With ``initial_states[batch, dim, >=width-1]`` (the history of a chunked continuation) a fourth
     result is returned: the gradient with respect to it.  ``tma``: tuning overrides of the TMA-staged
-    kernel (stages, ctas_per_sm, variant).
+    kernel (stages, ctas_per_sm, variant).  ``seq_idx[batch, seqlen]`` (int32): the forward ran on packed
+    rows; gradients stay inside each run of equal ids (scalar kernel; no mask, no initial state).
     """
     if x.dim() != 3:
         raise ValueError(f"Expected 3D input tensor (batch, dim, seqlen), got {x.dim()}D")
@@ -517,6 +519,16 @@ def causal_conv1d_bwd(
     a.dweight = dweight.data_ptr() if dweight is not None else None
     a.dbias = dbias.data_ptr() if dbias is not None else None
     a.zero_grads = 1
+    if seq_idx is not None:
+        _require_cuda(seq_idx, "seq_idx")
+        if tuple(seq_idx.shape) != (batch, seqlen):
+            raise ValueError(f"seq_idx shape {tuple(seq_idx.shape)} does not match input shape ({batch}, {seqlen})")
+        if attention_mask is not None or initial_states is not None:
+            raise ValueError("seq_idx cannot be combined with attention_mask, initial_states or final states")
+        if seq_idx.dtype != torch.int32:
+            seq_idx = seq_idx.to(torch.int32)
+        a.seq_idx = seq_idx.data_ptr()
+        a.seq_stride_b, a.seq_stride_t = seq_idx.stride()
     dinit = None
     if initial_states is not None:
         s0 = initial_states
@@ -598,7 +610,9 @@ class _CausalConv1dFunction(torch.autograd.Function):
                 final_states_out, kw, initial_states):
         kw = dict(kw)
         kw["residual"] = True if residual_is_x else res_tensor
-        result = _prefill_forward(x, weight, bias, None, initial_states, return_final_states, final_states_out,
+        seq_idx = kw.pop("seq_idx", None)
+        ctx.seq_idx = seq_idx
+        result = _prefill_forward(x, weight, bias, seq_idx, initial_states, return_final_states, final_states_out,
                                   activation, **kw)
         y, state = result if isinstance(result, tuple) else (result, None)
         ctx.save_for_backward(x, weight, bias if bias is not None else x.new_empty(0),
@@ -624,7 +638,7 @@ class _CausalConv1dFunction(torch.autograd.Function):
             x, weight, bias if ctx.has_bias else None, dy, ctx.activation,
             attention_mask=mask if ctx.has_mask else None, residual=ctx.residual_is_x,
             initial_states=init if ctx.has_init else None,
-            need_dweight=need_w, need_dbias=need_b and ctx.has_bias,
+            need_dweight=need_w, need_dbias=need_b and ctx.has_bias, seq_idx=ctx.seq_idx,
         )
         dx, dw, db = grads[0], grads[1], grads[2]
         dinit = grads[3] if ctx.has_init else None
