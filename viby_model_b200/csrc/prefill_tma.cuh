@@ -802,7 +802,11 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         if (p.inline_cls) {
             // class of every tile of the launch, one thread per tile; the producer meanwhile has its
             // first tile in flight and waits for this table before its second claim
-            for (int tile = threadIdx.x; tile < p.n_rowtiles; tile += G::kConsumerThreads) {
+            // (every CTA starts at another tile, so that the CTAs of the grid do not all ask the L2 for
+            // the same mask bytes at the same moment)
+            const int rot = (int)(((unsigned)(blockIdx.y * gridDim.x + blockIdx.x) * 61u) % (unsigned)p.n_rowtiles);
+            for (int i = threadIdx.x; i < p.n_rowtiles; i += G::kConsumerThreads) {
+                const int tile = (i + rot) % p.n_rowtiles;
                 const int bb = tile / p.n_ttile;
                 const int tt = tile - bb * p.n_ttile;
                 sts_u8(table + tile, classify_tile_thread(p, bb, tt * G::kTileRows, H, G::kTileRows));

@@ -17,6 +17,11 @@ Two things keep the PCIe link, which bounds this path, busy with useful bytes on
 """
 from __future__ import annotations
 
+import ctypes
+import os
+
+import numpy as np
+from concurrent.futures import ThreadPoolExecutor
 from typing import Optional
 
 import torch
@@ -119,6 +124,14 @@ class HostPrefill:
         self.zero_in = torch.zeros(1, 1, dim, dtype=dtype, device=self.device)
         self.zero_mask = torch.zeros(1, 1, dtype=mask_dtype, device=self.device) if masked else None
         self.last_d2h_bytes = 0
+        self._fill = True  # (timing experiments switch the host-side fill off; results are then incomplete)
+        # the host-side fill: plain memory copies out of a block of constant rows, on a few worker threads
+        self._fill_workers = max(1, min(8, (os.cpu_count() or 2) // 2))
+        self._pool = ThreadPoolExecutor(max_workers=self._fill_workers) if self.skip_constant_rows else None
+        self._fill_futures = []
+        self._const_blocks = ([torch.empty(256, dim, dtype=dtype) for _ in range(2)]
+                              if self.skip_constant_rows else None)
+        self._runs = 0
         self.x_dev = torch.empty(batch, seqlen, dim, dtype=dtype, device=self.device)
         self.y_dev = torch.empty_like(self.x_dev)
         self.m_dev = torch.empty(batch, seqlen, dtype=mask_dtype, device=self.device) if masked else None
@@ -128,6 +141,7 @@ class HostPrefill:
         self.s_h2d_all = [torch.cuda.Stream(self.device) for _ in range(k)]
         self.s_d2h_all = [torch.cuda.Stream(self.device) for _ in range(k)]
         self.s_run = torch.cuda.Stream(self.device)
+        self.s_const = torch.cuda.Stream(self.device)  # the constant row: must not queue behind earlier batches
         n = (batch + self.chunk - 1) // self.chunk
         self.ev_in = [torch.cuda.Event() for _ in range(n)]
         self.ev_run = [torch.cuda.Event() for _ in range(n)]
@@ -154,10 +168,13 @@ class HostPrefill:
     @staticmethod
     def valid_prefix_lengths(mask_host: torch.Tensor) -> list:
         """Per sequence, the index after its last non-zero mask entry (0 when all are zero)."""
-        nz = mask_host != 0
+        # (numpy on purpose: a parallel region of the tensor library here would leave its worker threads
+        # spinning on the cores that the copy and fill threads of this class need)
+        m = mask_host.view(torch.uint8).numpy() if mask_host.dtype == torch.bool else mask_host.float().numpy()
+        nz = m != 0
         T = nz.shape[1]
-        last = T - nz.flip(1).to(torch.uint8).argmax(1)
-        return torch.where(nz.any(1), last, torch.zeros_like(last)).tolist()
+        last = T - np.argmax(nz[:, ::-1], axis=1)
+        return np.where(nz.any(axis=1), last, 0).tolist()
 
     def run(self, x_host: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], activation,
             mask_host: Optional[torch.Tensor], y_host: torch.Tensor, *, join: bool = True) -> torch.Tensor:
@@ -180,13 +197,13 @@ class HostPrefill:
             # One masked single-step launch computes that row; the host fills it in while the copies run.
             width = weight.shape[1]
             out_rows = [min(self.seqlen, n + width - 1) for n in self.valid_prefix_lengths(mask_host)]
-            with torch.cuda.stream(self.s_run):
-                self.s_run.wait_stream(main)
+            with torch.cuda.stream(self.s_const):
+                self.s_const.wait_stream(main)
                 causal_conv1d_fn(self.zero_in.transpose(1, 2), weight, bias, activation=activation,
                                  attention_mask=self.zero_mask, out=self.const_dev.transpose(1, 2))
                 self.const_host.copy_(self.const_dev, non_blocking=True)
                 const_ready = torch.cuda.Event()
-                const_ready.record(self.s_run)
+                const_ready.record(self.s_const)
             received += row_bytes
         for i, b0 in enumerate(range(0, self.batch, self.chunk)):
             b1 = min(b0 + self.chunk, self.batch)
@@ -225,19 +242,48 @@ class HostPrefill:
                             y_host[b, : out_rows[b]].copy_(self.y_dev[b, : out_rows[b]], non_blocking=True)
                             received += out_rows[b] * row_bytes
                 self.ev_out[i].record(s_d2h)
-        if out_rows is not None:
-            const_ready.synchronize()  # a [dim] vector: arrives long before the first chunk is back
+        if out_rows is not None and self._fill:
+            # the host writes the constant rows on a worker thread while this thread goes on enqueueing (the
+            # fill of a Canon-D batch takes a few milliseconds of host time: about as long as the copies)
+            self._wait_fill(keep=1)  # the fill of the batch before the previous one has long finished
+            const_ready.synchronize()  # a [dim] vector on a stream of its own: a few tens of microseconds
+            blk = self._const_blocks[self._runs % 2]  # (the previous batch's fill may still be reading the other)
+            self._runs += 1
+            for r in range(blk.shape[0]):  # plain copies: no parallel region of the tensor library on this path
+                ctypes.memmove(blk[r].data_ptr(), self.const_host.data_ptr(), row_bytes)
+            src, block_bytes = blk.data_ptr(), blk.numel() * blk.element_size()
+            pieces = []  # (destination address, bytes): at most const_block rows each
             for b in range(self.batch):
-                if out_rows[b] < self.seqlen:
-                    y_host[b, out_rows[b]:] = self.const_host[0]
+                at = y_host[b, out_rows[b]:].data_ptr() if out_rows[b] < self.seqlen else 0
+                left = (self.seqlen - out_rows[b]) * row_bytes
+                while left > 0:
+                    n = min(left, block_bytes)
+                    pieces.append((at, n))
+                    at += n
+                    left -= n
+            k = self._fill_workers
+
+            def fill(part):
+                for dst, n in part:
+                    ctypes.memmove(dst, src, n)  # releases the GIL
+
+            self._fill_futures.append([self._pool.submit(fill, pieces[i::k]) for i in range(k)])
         self.last_h2d_bytes = sent
         self.last_d2h_bytes = received
         if join:
             self.join()
         return y_host
 
+    def _wait_fill(self, keep: int = 0) -> None:
+        """Wait for the host-side fills of all but the ``keep`` most recent run() calls."""
+        while len(self._fill_futures) > keep:
+            for f in self._fill_futures.pop(0):
+                f.result()
+
     def join(self) -> None:
-        """Order everything queued so far into the caller's current stream."""
+        """Order everything queued so far into the caller's current stream (and wait for the host-side
+        fill of the constant rows, when there is one)."""
+        self._wait_fill()
         main = torch.cuda.current_stream(self.device)
-        for s in self.s_d2h_all + [self.s_run] + self.s_h2d_all:
+        for s in self.s_d2h_all + [self.s_run, self.s_const] + self.s_h2d_all:
             main.wait_stream(s)
