@@ -459,7 +459,7 @@ def main():
         # ---- end to end: pinned host in, pinned host out, every step -------------------------
         e2e = None
         if not args.no_e2e:
-            e2e = bench_e2e(ctx, HostPrefill, cfg, x_host, m_host, w, b, x, y, steps, padded_tokens)
+            e2e = bench_e2e(ctx, HostPrefill, cfg, x_host, m_host, w, b, x, y, steps, padded_tokens, host_threads)
             e2e["main"]["numa_node"] = numa_node
             e2e["main"]["numa_note"] = numa_note
             e2e["main"]["host_threads_per_rank"] = host_threads
@@ -560,7 +560,7 @@ def main():
 # --------------------------------------------------------------------------------------------------
 # sections
 # --------------------------------------------------------------------------------------------------
-def bench_e2e(ctx, HostPrefill, cfg, x_host, m_host, w, b, x_dev, y_dev, steps, padded_tokens):
+def bench_e2e(ctx, HostPrefill, cfg, x_host, m_host, w, b, x_dev, y_dev, steps, padded_tokens, host_threads):
     """The step through HostPrefill, host buffers in and out, in three variants; and the plain copy
     rate of the same byte counts over the same link (two streams, no kernel) for comparison."""
     dev, world = ctx.dev, ctx.world
@@ -569,7 +569,7 @@ def bench_e2e(ctx, HostPrefill, cfg, x_host, m_host, w, b, x_dev, y_dev, steps, 
 
     def run(**kw):
         pipe = HostPrefill(cfg.batch, cfg.seqlen, cfg.dim, cfg.dtype, device=dev, chunk_batch=4,
-                           mask_dtype=torch.bool, **kw)
+                           mask_dtype=torch.bool, fill_workers=max(1, min(8, host_threads // 2)), **kw)
         y_host.fill_(0)
         for _ in range(3):
             pipe.run(x_host, w, b, cfg.activation, m_host, y_host)

@@ -113,7 +113,8 @@ def _bind_to_gpu_numa_node(device_index: int) -> Optional[int]:
 class HostPrefill:
     def __init__(self, batch: int, seqlen: int, dim: int, dtype: torch.dtype, device="cuda",
                  chunk_batch: int = 4, masked: bool = True, mask_dtype: torch.dtype = torch.int64,
-                 send_masked_rows: bool = False, skip_constant_rows: bool = False, copy_streams: int = 1):
+                 send_masked_rows: bool = False, skip_constant_rows: bool = False, copy_streams: int = 1,
+                 fill_workers: Optional[int] = None):
         self.device = torch.device(device)
         self.batch, self.seqlen, self.dim, self.dtype = batch, seqlen, dim, dtype
         self.chunk = max(1, min(chunk_batch, batch))
@@ -126,7 +127,8 @@ class HostPrefill:
         self.last_d2h_bytes = 0
         self._fill = True  # (timing experiments switch the host-side fill off; results are then incomplete)
         # the host-side fill: plain memory copies out of a block of constant rows, on a few worker threads
-        self._fill_workers = max(1, min(8, (os.cpu_count() or 2) // 2))
+        self._fill_workers = (max(1, int(fill_workers)) if fill_workers is not None
+                              else max(1, min(8, (os.cpu_count() or 2) // 2)))
         self._pool = ThreadPoolExecutor(max_workers=self._fill_workers) if self.skip_constant_rows else None
         self._fill_futures = []
         self._const_blocks = ([torch.empty(256, dim, dtype=dtype) for _ in range(2)]
