@@ -144,7 +144,7 @@ typedef struct vc1d_prefill_args {
                                     while its first tile is in flight (small masks only) */
     int32_t tma_pdl;             /* main kernel launched as a programmatic dependent of whatever precedes it in
                                     the stream: 1 = only after a pre-pass, 2 = always */
-    int32_t tma_static_first;    /* tiles every CTA takes without a claim before it starts claiming: 1..8 */
+    int32_t tma_static_first;    /* tiles every CTA takes without a claim before it starts claiming */
     int32_t tma_test_expire;     /* self-test of the bounded waits: 1 = every CTA withholds its first tile and
                                     polls only 4096 times, so the waits for that tile expire, the kernel
                                     returns normally with y incomplete and vc1d_tma_timeouts() has grown */

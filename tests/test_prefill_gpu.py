@@ -555,13 +555,14 @@ def _mask_of_kind(kind, B, T, seed):
                                  dict(classify=2, static_first=2, pdl=2), dict(rows_per_thread=4, empty_store=2)],
                          ids=lambda d: ",".join(f"{k}={v}" for k, v in d.items()))
 @pytest.mark.parametrize("mask_kind", ["right", "left", "holes", "zeros", "ones"])
-@pytest.mark.parametrize("mask_dtype", [torch.bool, torch.int64])
-def test_tma_scheduling_variants_agree(mask_dtype, mask_kind, tma):
+@pytest.mark.parametrize("mask_dtype,D", [(torch.bool, 1160), (torch.int64, 1160), (torch.bool, 960)])
+def test_tma_scheduling_variants_agree(mask_dtype, D, mask_kind, tma):
     """Every way the TMA-staged kernel can hand out, classify and store its tiles gives the bits of the
     register-window kernel: bulk-stored or consumer-stored constant tiles, tile classes from the
-    pre-pass or worked out inside the kernel, chunked claims, unclaimed first tiles.  The shape has a
-    last time tile that is not full and a last channel slab that is half outside the tensor."""
-    B, T, D, W = 20, 1008, 1160, 4
+    pre-pass or worked out inside the kernel, chunked claims, unclaimed first tiles.  The shapes have a
+    last time tile that is not full and either a last 256-byte channel slab that is half outside the
+    tensor (1160 channels) or 128-byte slabs and 128-row tiles (960 channels, the Canon-B width)."""
+    B, T, W = 20, 1008, 4
     x = O.seeded((B, T, D), 77, "normal", torch.bfloat16)
     w = O.seeded((D, W), 78, "uniform", torch.bfloat16)
     b = O.seeded((D,), 79, "uniform", torch.bfloat16)

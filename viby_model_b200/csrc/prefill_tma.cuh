@@ -1046,8 +1046,12 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     p.chunk = (a.tma_claim_chunk == 2 || a.tma_claim_chunk == 4) ? a.tma_claim_chunk : 1;
     if (tiles_per_cta < 4LL * p.chunk) p.chunk = 1;
     // two unclaimed tiles per CTA: both copies start back to back at the top of the kernel
-    p.static_first = (a.tma_static_first >= 1 && a.tma_static_first <= 8) ? a.tma_static_first : 2;
-    if (tiles_per_cta < 2LL * p.static_first) p.static_first = 1;
+    p.static_first = (a.tma_static_first >= 1 && a.tma_static_first <= 1024) ? a.tma_static_first : 2;
+    {
+        // every unclaimed tile j0 + k * g must exist: k < n_rowtiles / g; leave a few tiles to the counters
+        const long long whole = n_rowtiles / g;
+        if (p.static_first > whole - 2) p.static_first = (int)(whole - 2 > 1 ? whole - 2 : 1);
+    }
     const bool use_scratch = tiles_per_cta >= 4 && a.scratch != nullptr && 4LL * (n_slab + 1) <= kSchedCounterBytes &&
                              a.scratch_bytes >= kSchedCounterBytes + table_need &&
                              (reinterpret_cast<uintptr_t>(a.scratch) & 15u) == 0;
