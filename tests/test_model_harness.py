@@ -71,7 +71,7 @@ def test_cuda_branch_semantics_agree_with_fallback_on_valid_positions():
     assert torch.allclose(logits[valid], ref[valid], rtol=1e-4, atol=1e-5)
 
 
-FULL = dict(hidden_size=640, intermediate_size=1728, num_attention_heads=4, num_key_value_heads=1,
+FULL_CONFIG = dict(hidden_size=640, intermediate_size=1728, num_attention_heads=4, num_key_value_heads=1,
             num_hidden_layers=18, vocab_size=25600, rms_norm_eps=1e-6, rope_theta=1e6, sliding_window=512,
             canon_kernel=4, canon_bias=True, canon_activation=True, max_positions=2048)
 
@@ -104,13 +104,17 @@ def test_tiny_model_with_kernels_matches_reference_logits():
 
 
 @pytest.mark.gpu
-def test_config4_full_model_prefill_and_decode():
+@pytest.mark.parametrize("bias_and_activation", [True, False], ids=["bias+silu", "reference-defaults"])
+def test_config4_full_model_prefill_and_decode(bias_and_activation):
+    """bias + SiLU exercises every fused path; the second run uses the reference's defaults
+    (canon_bias=False, canon_activation=False, model/model.py:55-58) with fewer decode steps."""
     import viby_model_b200 as V
     from parity import ulp_distance
 
     dev = torch.device("cuda")
     B, T = int(os.environ.get("VC1D_CFG4_BATCH", 64)), 1024
-    steps = int(os.environ.get("VC1D_CFG4_DECODE_STEPS", 256))
+    steps = int(os.environ.get("VC1D_CFG4_DECODE_STEPS", 256 if bias_and_activation else 24))
+    FULL = dict(FULL_CONFIG, canon_bias=bias_and_activation, canon_activation=bias_and_activation)
     params = random_params(FULL, 4, torch.bfloat16, dev)
     g = torch.Generator().manual_seed(44)
     ids = torch.randint(0, FULL["vocab_size"], (B, T), generator=g).to(dev)
@@ -142,10 +146,12 @@ def test_config4_full_model_prefill_and_decode():
     worst = 0
     for (name, layer, x, m, out, conv_term), fused in zip(hp.canon_inputs, fused_calls):
         w = params[f"model.layers.{layer}.{name}.weight"].squeeze(1)
-        b = params[f"model.layers.{layer}.{name}.bias_param"]
+        b = params.get(f"model.layers.{layer}.{name}.bias_param")
         conv = torch.nn.functional.conv1d(torch.nn.functional.pad(x.transpose(1, 2).float(), (3, 0)),
-                                          w.float().unsqueeze(1), b.float(), groups=x.shape[-1])
-        ref = torch.nn.functional.silu(conv).to(x.dtype).transpose(1, 2)
+                                          w.float().unsqueeze(1), None if b is None else b.float(), groups=x.shape[-1])
+        if FULL["canon_activation"]:
+            conv = torch.nn.functional.silu(conv)
+        ref = conv.to(x.dtype).transpose(1, 2)
         ulp = ulp_distance(conv_term.contiguous(), ref.contiguous())
         bad = (ulp > 1) & ((conv_term.float() - ref.float()).abs() > 1e-6)
         assert not bool(bad.any()), (name, layer, int(bad.sum()), int(ulp.max()))
