@@ -639,3 +639,36 @@ print("EXPIRED", expired)
                        cwd=str(__import__("conftest").ROOT))
     assert r.returncode == 0, r.stdout + r.stderr
     assert "EXPIRED" in r.stdout
+
+
+def test_config5_full_batch_addresses_beyond_32_bits():
+    """The whole ragged configuration on one GPU: 512 x 4096 x 3456 bf16 = 14.5 GB in, 14.5 GB out, so byte
+    offsets pass 2^32 and the launch has 32768 tiles per channel slab (two-bit class table).  Sequences from
+    the start, the middle and the end of the batch must equal the same sequences launched on their own
+    (small offsets, byte-per-tile table), and the packed launch of the whole batch must agree with both."""
+    cfg = WL.RAGGED_SWEEP
+    free, _ = torch.cuda.mem_get_info()
+    if free < 40 * 2 ** 30:
+        pytest.skip("needs 40 GB of free device memory")
+    lens = WL.sequence_lengths(cfg).tolist()
+    x = WL.prefill_inputs(cfg, device=DEV, generate_on="cuda")
+    m = WL.attention_mask(cfg, device=DEV, dtype=torch.bool)
+    w, b = WL.weights(cfg.cfg, cfg.dim, cfg.width, cfg.dtype, device=DEV)
+    assert x.numel() * x.element_size() > 2 ** 33
+    before = V.launch_count()
+    y = V.causal_conv1d_fn(x.transpose(1, 2), w, b, activation="silu", attention_mask=m)
+    assert V.launch_count() - before == 2 and V.last_kernel() == "tma"
+    for i in (0, 1, 255, 256, 300, 510, 511):
+        yi = V.causal_conv1d_fn(x[i:i + 1].transpose(1, 2), w, b, activation="silu", attention_mask=m[i:i + 1])
+        assert torch.equal(yi, y[i:i + 1]), f"sequence {i}"
+    y = y.transpose(1, 2)  # [B, T, D]
+    xp = torch.cat([x[i, :n] for i, n in enumerate(lens)], 0).unsqueeze(0)
+    ids = V.seq_idx_from_lengths(lens, device=DEV)
+    yp = V.causal_conv1d_fn(xp.transpose(1, 2), w, b, activation="silu", seq_idx=ids).transpose(1, 2)
+    at = 0
+    for i, n in enumerate(lens):
+        if i % 37 == 0 or i > 505:
+            assert torch.equal(yp[0, at:at + n], y[i, :n]), f"packed sequence {i}"
+        at += n
+    torch.cuda.synchronize()
+    assert V.tma_timeouts() == 0
