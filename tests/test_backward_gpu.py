@@ -368,3 +368,38 @@ def test_gradient_flows_through_the_returned_final_state(T1, L, masked):
     assert torch.allclose(s0.grad.cpu().double(), xr.grad[:, :T0].transpose(1, 2), **tol)
     assert torch.allclose(wd.grad.cpu().double(), wr.grad, **tol)
     assert torch.allclose(bd.grad.cpu().double(), br.grad, **tol)
+
+
+def test_backward_of_the_whole_ragged_configuration():
+    """512 x 4096 x 3456 bf16: x, dy and dx are 14.5 GB each, byte offsets pass 2^32.  dx of sequences from the
+    start, the middle and the end of the batch must equal the same sequences differentiated on their own;
+    dweight / dbias of the first 8 sequences launched together must equal the sum of their single launches."""
+    from viby_model_b200 import workloads as WL
+
+    free, _ = torch.cuda.mem_get_info()
+    if free < 60 * 2 ** 30:
+        pytest.skip("needs 60 GB of free device memory")
+    cfg = WL.RAGGED_SWEEP
+    x = WL.prefill_inputs(cfg, device=DEV, generate_on="cuda")
+    m = WL.attention_mask(cfg, device=DEV, dtype=torch.bool)
+    w, b = WL.weights(cfg.cfg, cfg.dim, cfg.width, cfg.dtype, device=DEV)
+    dy = torch.empty_like(x)
+    g = torch.Generator(device=DEV).manual_seed(5)
+    for i in range(0, cfg.batch, 64):
+        dy[i:i + 64] = torch.randn(dy[i:i + 64].shape, generator=g, device=DEV).to(cfg.dtype)
+    xv, dyv = x.transpose(1, 2), dy.transpose(1, 2)
+    dx, dw, db = V.causal_conv1d_bwd(xv, w, b, dyv, "silu", attention_mask=m)
+    assert V.last_kernel() == "bwd_tma"
+    for i in (0, 1, 255, 256, 511):
+        dxi, _, _ = V.causal_conv1d_bwd(xv[i:i + 1], w, b, dyv[i:i + 1], "silu", attention_mask=m[i:i + 1])
+        assert torch.equal(dxi, dx[i:i + 1]), f"sequence {i}"
+    _, dw8, db8 = V.causal_conv1d_bwd(xv[:8], w, b, dyv[:8], "silu", attention_mask=m[:8])
+    dws, dbs = torch.zeros_like(dw8), torch.zeros_like(db8)
+    for i in range(8):
+        _, dwi, dbi = V.causal_conv1d_bwd(xv[i:i + 1], w, b, dyv[i:i + 1], "silu", attention_mask=m[i:i + 1])
+        dws += dwi
+        dbs += dbi
+    assert torch.allclose(dw8, dws, rtol=1e-4, atol=1e-2) and torch.allclose(db8, dbs, rtol=1e-4, atol=1e-2)
+    assert bool(torch.isfinite(dw).all()) and bool(torch.isfinite(db).all())
+    torch.cuda.synchronize()
+    assert V.tma_timeouts() == 0
