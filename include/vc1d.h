@@ -229,7 +229,7 @@ typedef struct vc1d_prefill_bwd_args {
                                    folded into the tile-classification pre-pass when the launch has one) */
     /* Packed variable-length rows, as in vc1d_prefill_args: sequence id of every step; taps and their
      * gradients stay inside a run of equal ids.  Not combined with mask or initial_state
-     * (VC1D_E_SHAPE).  Such launches take the generic kernel. */
+     * (VC1D_E_SHAPE). */
     const int32_t* seq_idx;
     int64_t seq_stride_b, seq_stride_t;
 } vc1d_prefill_bwd_args;

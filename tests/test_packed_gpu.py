@@ -144,14 +144,16 @@ def test_packed_argument_errors():
         V.causal_conv1d_fn(x, w, seq_idx=ids, return_final_states=True)
 
 
+@pytest.mark.parametrize("kernel", ["generic", "tma"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("W", [2, 3, 4])
 @pytest.mark.parametrize("act", [None, "silu"])
-def test_packed_backward_against_oracle(act, W, dtype):
+def test_packed_backward_against_oracle(act, W, dtype, kernel):
     """Gradients on packed rows: dx, dweight, dbias against the float64 oracle (each run of equal ids
-    differentiated on its own), sequence starts at every offset of a thread's 128-row chunk."""
-    D = 72
-    lens = [1, 2, 3, 125, 1, 130, 4, 127, 128, 129, 64, 5]
+    differentiated on its own), sequence starts at every offset of a thread's rows and at tile and
+    chunk edges, in the scalar and in the TMA-staged kernel."""
+    D = 72 if kernel == "generic" else 256
+    lens = [1, 2, 3, 125, 1, 130, 4, 127, 128, 129, 64, 5, 7, 8, 9, 1, 1, 63, 65, 16, 15, 17, 2]
     x = O.seeded((1, sum(lens), D), 41, "normal", dtype)
     dy = O.seeded((1, sum(lens), D), 42, "normal", dtype)
     w = O.seeded((D, W), 43, "uniform", dtype)
@@ -160,8 +162,8 @@ def test_packed_backward_against_oracle(act, W, dtype):
     for residual in (False, True):
         before = V.launch_count()
         dx, dw, db = V.causal_conv1d_bwd(x.to(DEV).transpose(1, 2), w.to(DEV), b.to(DEV), dy.to(DEV).transpose(1, 2), act,
-                                         residual=residual, seq_idx=ids.to(DEV))
-        assert V.launch_count() == before + 1 and V.last_kernel() == "bwd_generic"
+                                         residual=residual, seq_idx=ids.to(DEV), kernel=kernel)
+        assert V.launch_count() - before in (1, 2) and V.last_kernel() == "bwd_" + kernel
         rdx, rdw, rdb = O.causal_conv1d_packed_bwd_ref(x.transpose(1, 2), w, b, dy.transpose(1, 2), act, seq_idx=ids,
                                                        residual=residual)
         sdx, _, _ = O.causal_conv1d_packed_bwd_ref(x.abs().transpose(1, 2), w.abs(), None, dy.abs().transpose(1, 2), None,
@@ -177,7 +179,7 @@ def test_packed_backward_against_oracle(act, W, dtype):
 def test_packed_autograd_equals_padded_autograd():
     """Training on packed rows: gradients of a loss over the valid positions equal those of the padded,
     masked batch (whose backward runs on the TMA-staged kernel) -- dx bit for bit at the valid positions."""
-    B, T, D, W = 6, 300, 256, 4
+    B, T, D, W = 6, 300, 512, 4  # large enough for both backward passes to take the TMA-staged kernel
     g = torch.Generator().manual_seed(9)
     lens = [300, 1, 77, 128, 129, 250]
     x = torch.randn(B, T, D, generator=g).bfloat16()
@@ -219,8 +221,9 @@ def test_packed_ids_that_repeat_are_separate_sequences():
                                kernel=kernel)
         assert_close_to_oracle(y, ref, kernel)
     dy = O.seeded((1, T, D), 53, "normal", torch.float32)
-    dx, dw, _ = V.causal_conv1d_bwd(x.to(DEV).transpose(1, 2), w.to(DEV), None, dy.to(DEV).transpose(1, 2), "silu",
-                                    seq_idx=ids.to(DEV))
     rdx, rdw, _ = O.causal_conv1d_packed_bwd_ref(x.transpose(1, 2), w, None, dy.transpose(1, 2), "silu", seq_idx=ids)
-    assert torch.allclose(dx.cpu(), rdx, rtol=1e-4, atol=1e-5)
-    assert torch.allclose(dw.cpu().double(), rdw, rtol=1e-4, atol=1e-4)
+    for kernel in ("generic", "tma"):
+        dx, dw, _ = V.causal_conv1d_bwd(x.to(DEV).transpose(1, 2), w.to(DEV), None, dy.to(DEV).transpose(1, 2), "silu",
+                                        seq_idx=ids.to(DEV), kernel=kernel)
+        assert torch.allclose(dx.cpu(), rdx, rtol=1e-4, atol=1e-5), kernel
+        assert torch.allclose(dw.cpu().double(), rdw, rtol=1e-4, atol=1e-4), kernel

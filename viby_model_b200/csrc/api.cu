@@ -291,14 +291,13 @@ VC1D_API int vc1d_prefill_bwd(const vc1d_prefill_bwd_args* a, void* stream) {
             err = launch_prefill_bwd_generic(*a, s);
             break;
         case VC1D_KERNEL_TMA:
-            if (!cl || !tma_available() || a->initial_state != nullptr || a->seq_idx != nullptr) return VC1D_E_STRIDE;
+            if (!cl || !tma_available() || a->initial_state != nullptr) return VC1D_E_STRIDE;
             err = launch_prefill_bwd_tma(*a, s);
             break;
         default: {
             const long long elems = (long long)a->batch * a->dim * a->seqlen;
             err = cudaErrorNotSupported;
-            if (cl && a->initial_state == nullptr && a->seq_idx == nullptr && a->seqlen >= 16 && elems >= (1LL << 18) &&
-                tma_available())
+            if (cl && a->initial_state == nullptr && a->seqlen >= 16 && elems >= (1LL << 18) && tma_available())
                 err = launch_prefill_bwd_tma(*a, s);
             if (err == cudaErrorNotSupported) err = launch_prefill_bwd_generic(*a, s);
             break;

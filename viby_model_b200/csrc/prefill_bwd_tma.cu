@@ -38,6 +38,16 @@ cudaError_t launch_prefill_bwd_tma(const vc1d_prefill_bwd_args& a, cudaStream_t 
     p.mask_dtype = a.mask_dtype;
     p.residual = a.residual != 0;
     p.stages = 0;
+    p.seg_mode = 0;
+    if (a.seq_idx != nullptr) {
+        // sequence ids travel the mask's path (per-row values, tile classes): a value other than one marks
+        // the first row of a sequence
+        p.mask = a.seq_idx;
+        p.mask_dtype = VC1D_I32;
+        p.smb = a.seq_stride_b;
+        p.smt = a.seq_stride_t;
+        p.seg_mode = 1;
+    }
     switch (a.dtype) {
         case VC1D_F32: return tma::launch_bwd_dt<VC1D_F32>(a, p, s);
         case VC1D_BF16: return tma::launch_bwd_dt<VC1D_BF16>(a, p, s);

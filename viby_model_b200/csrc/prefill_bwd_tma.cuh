@@ -11,9 +11,10 @@
 // Here a tile is 64 rows x one channel slab of one sequence.  The producer warp brings in two
 // boxes per tile with bulk tensor copies: x rows [t0-H, t0+64+H) and dy rows [t0, t0+64+H), H = W-1
 // (rows outside the sequence arrive as zeros, which is both the causal padding of x and "no
-// gradient from beyond the end").  A consumer thread owns 8 bytes of channels and 8 consecutive
-// rows; it walks 8+H rows once with two register windows (masked inputs, g), so each pre[t] is
-// built once per thread, each g[t] feeds the W outputs that use it, and nothing is re-read.  The
+// gradient from beyond the end").  A consumer thread owns 4 or 8 bytes of channels and 8 or 16
+// consecutive rows (BwdGeometry); it walks its rows + H once with two register windows (masked
+// inputs, g), so each pre[t] is built once per thread, each g[t] feeds the W outputs that use it,
+// and nothing is re-read.  The
 // thread's dweight / dbias partial sums stay in registers across all tiles of its CTA (a CTA keeps
 // its channel slab); at the end the CTA adds them up through shared memory and issues one atomic
 // add per (channel, tap).  HBM traffic is the algorithmic minimum: x and dy read once, dx written once.
@@ -43,6 +44,7 @@ struct BwdParams {
     int mask_dtype;
     int residual;
     int stages;
+    int seg_mode;  // mask holds int32 sequence ids (packed rows): no multipliers, taps stay inside a run of equal ids
 };
 
 // VARIANT 0: a thread owns 8 bytes of channels and 8 consecutive rows.  VARIANT 1 (16-bit I/O): 4
@@ -303,10 +305,26 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES, VARIANT>::kThre
             mp.smt = p.smt;
             mp.mask_dtype = p.mask_dtype;
             mp.T = p.T;
+            mp.seg_mode = p.seg_mode;
             if (mj < R + 2 * H) mkv = tile_mask(mp, (long long)b * p.smb, tfirst - H + mj);
         }
         // rows of this warp whose mask values are all one take the code without mask arithmetic
         const bool warp_masked = cls == TILE_MIXED && !__all_sync(0xffffffffu, mkv == 1.0f);
+        // x box row n has just been put into its window slot.  With a mask: multiply it.  With packed rows a
+        // value other than one means that a sequence starts at this row: the rows above it are no taps of it
+        // or of anything after it, so the other slots of the window are cleared.
+        auto mask_row = [&](float2 (&xw)[W][NP], int n, float mk) {
+            if (p.seg_mode) {
+                if (mk != 1.0f) {
+#pragma unroll
+                    for (int v = 1; v < W; ++v)
+#pragma unroll
+                        for (int q = 0; q < NP; ++q) xw[(n + v) % W][q] = make_float2(0.f, 0.f);
+                }
+            } else {
+                apply_mask<DT, VB>(xw[n % W], mk, 1);
+            }
+        };
         auto rows = [&](auto mk_c) {
             constexpr bool MK = decltype(mk_c)::value;
             float2 xw[W][NP];  // masked inputs: row n lives in slot n % W
@@ -316,7 +334,7 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES, VARIANT>::kThre
                 uint32_t raw[NW];
                 S::lds(xrow + n * G::kRowBytes, raw);
                 S::unpack(raw, xw[n % W]);
-                if constexpr (MK) apply_mask<DT, VB>(xw[n % W], __shfl_sync(0xffffffffu, mkv, msrc + n), 1);
+                if constexpr (MK) mask_row(xw, n, __shfl_sync(0xffffffffu, mkv, msrc + n));
             }
             static_for<0, R + H>([&](auto jc) {
                 constexpr int jj = decltype(jc)::value;
@@ -325,7 +343,7 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES, VARIANT>::kThre
                     uint32_t raw[NW];
                     S::lds(xrow + n * G::kRowBytes, raw);
                     S::unpack(raw, xw[n % W]);
-                    if constexpr (MK) apply_mask<DT, VB>(xw[n % W], __shfl_sync(0xffffffffu, mkv, msrc + n), 1);
+                    if constexpr (MK) mask_row(xw, n, __shfl_sync(0xffffffffu, mkv, msrc + n));
                 }
                 float2 g[NP];
                 {
@@ -356,16 +374,33 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES, VARIANT>::kThre
                 if constexpr (jj >= H) {
                     constexpr int k = jj - H;  // output row: dx[t] = sum_w weight[w] * g[t + (W-1-w)], t + H = jj
                     float2 acc[NP];
+                    // g of row k + H - w reaches input row k through weight[w]; with packed rows only while
+                    // the sequence of row k lasts, i.e. for the first `reach` rows behind it
+                    int reach = H;
+                    if constexpr (MK) {
+                        if (p.seg_mode) {
+                            reach = 0;
+                            bool open = true;
+    #pragma unroll
+                            for (int u = 1; u <= H; ++u) {
+                                open = open && (__shfl_sync(0xffffffffu, mkv, msrc + H + k + u) == 1.0f);
+                                if (open) reach = u;
+                            }
+                        }
+                    }
     #pragma unroll
                     for (int q = 0; q < NP; ++q) {
-                        acc[q] = mul2(wp[0][q], gw[jj % W][q]);
+                        acc[q] = (reach == H) ? mul2(wp[0][q], gw[jj % W][q]) : make_float2(0.f, 0.f);
     #pragma unroll
-                        for (int w = 1; w < W; ++w) acc[q] = fma2(wp[w][q], gw[(jj - w + W) % W][q], acc[q]);
+                        for (int w = 1; w < W; ++w)
+                            if (H - w <= reach) acc[q] = fma2(wp[w][q], gw[(jj - w + W) % W][q], acc[q]);
                     }
                     if constexpr (MK) {
-                        const float mk = __shfl_sync(0xffffffffu, mkv, msrc + H + k);
+                        if (!p.seg_mode) {
+                            const float mk = __shfl_sync(0xffffffffu, mkv, msrc + H + k);
     #pragma unroll
-                        for (int q = 0; q < NP; ++q) acc[q] = mul2(acc[q], make_float2(mk, mk));
+                            for (int q = 0; q < NP; ++q) acc[q] = mul2(acc[q], make_float2(mk, mk));
+                        }
                     }
                     if (p.residual) {
                         uint32_t raw[NW];
@@ -518,13 +553,14 @@ cudaError_t launch_bwd_kernel(const vc1d_prefill_bwd_args& a, const BwdParams& b
     const int n_db = a.dbias != nullptr ? a.dim : 0;
     if (use_sched) {
         p.sched = reinterpret_cast<unsigned int*>(a.scratch);
-        if (a.mask != nullptr && a.scratch_bytes >= kSchedCounterBytes + n_rowtiles) {
+        if (p.mask != nullptr && a.scratch_bytes >= kSchedCounterBytes + n_rowtiles) {
             // class of every tile from its R + 2H mask rows (pre-pass shared with the forward kernel)
             TmaParams cp = {};
-            cp.mask = a.mask;
-            cp.smb = a.mask_stride_b;
-            cp.smt = a.mask_stride_t;
-            cp.mask_dtype = a.mask_dtype;
+            cp.mask = p.mask;
+            cp.smb = p.smb;
+            cp.smt = p.smt;
+            cp.mask_dtype = p.mask_dtype;
+            cp.seg_mode = p.seg_mode;
             cp.B = a.batch;
             cp.T = a.seqlen;
             cp.n_ttile = p.n_ttile;

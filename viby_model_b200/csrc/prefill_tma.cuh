@@ -12,18 +12,26 @@
 // weights of its slab in registers for its whole life.
 //
 // Which tile a CTA takes next.  With scratch memory from the caller, the CTAs of a slab claim
-// tiles from one counter per slab (atomicAdd, one tile ahead; a CTA's first tile needs no claim),
+// tiles from one counter per slab (atomicAdd, one tile ahead; a CTA's first tiles need no claim),
 // so a CTA that met cheap tiles or runs on a faster SM takes more; the last CTA to finish resets
 // the counters.  Without scratch, or when a CTA would own fewer than four tiles, CTA j of a slab
 // walks tiles j, j + G, j + 2G, ...  Either way neighbouring CTAs touch neighbouring rows at
 // about the same time, so the (W-1)-row halo of a tile is an L2 hit.
 //
 // Masks.  Every tile has a class: all of its mask rows are one (the maskless code runs), mixed, or
-// every tap of every row is masked.  A tile of the last class takes a ring slot but no bulk copy:
-// no byte of it is requested from HBM and the consumers store act(bias).  The classes come from
-// a pre-pass kernel (one byte per tile in scratch memory, copied to shared memory by every CTA)
-// or, without scratch, from the CTA's own prologue; the main kernel is launched as a programmatic
-// dependent of the pre-pass.  Mask values are looked at again only inside mixed tiles.
+// every tap of every row is masked.  A tile of the last class is never loaded and never reaches
+// the consumers: its rows are all act(bias), and the producer writes them with bulk tensor stores
+// out of a few constant rows the CTA keeps in shared memory (when y cannot be described by a
+// tensor map the tile takes a ring slot without a copy and the consumers store it).  The classes
+// come from a pre-pass kernel (one byte per tile in scratch memory, copied to shared memory by
+// every CTA, two bits per tile for very long batches) or, without scratch, from the CTA's own
+// prologue; the main kernel is launched as a programmatic dependent of the pre-pass.  Mask values
+// are looked at again only inside mixed tiles.
+//
+// Packed rows.  With sequence ids instead of a mask (several sequences laid end to end in one
+// row) the per-row value that travels the mask's path says "a sequence starts here"; a tile
+// without a start in its rows is an ordinary tile, in the others the consumers clear their
+// history window at every start.
 //
 // Pipeline.  One producer warp and eight consumer warps share a ring of stages guarded by
 // full/done mbarriers.  For every tile the producer writes a 32-byte descriptor (class, rows that

@@ -156,8 +156,7 @@ def causal_conv1d_fn(
         sequence it belongs to and a tap only counts when it carries the same value as the output
         step, so sequences laid end to end in one row (``seq_idx_from_lengths``) give exactly the
         results of a right-padded batch at the valid positions, without reading or writing padding.
-        The reference passes None (model/model.py:465); not combined with a mask or states; differentiable
-        (the backward of packed rows runs on the scalar kernel),
+        The reference passes None (model/model.py:465); not combined with a mask or states; differentiable,
       ``initial_states[batch, dim, >=width-1]``: history used instead of zeros (its last width-1 columns),
       ``return_final_states`` / ``final_states_out``: also return the last ``state_len`` inputs as
       ``[batch, dim, state_len]`` (default state_len = width-1), right-aligned like
@@ -465,7 +464,7 @@ def causal_conv1d_bwd(
     With ``initial_states[batch, dim, >=width-1]`` (the history of a chunked continuation) a fourth
     result is returned: the gradient with respect to it.  ``tma``: tuning overrides of the TMA-staged
     kernel (stages, ctas_per_sm, variant).  ``seq_idx[batch, seqlen]`` (int32): the forward ran on packed
-    rows; gradients stay inside each run of equal ids (scalar kernel; no mask, no initial state).
+    rows; gradients stay inside each run of equal ids (no mask, no initial state).
     """
     if x.dim() != 3:
         raise ValueError(f"Expected 3D input tensor (batch, dim, seqlen), got {x.dim()}D")
