@@ -122,11 +122,12 @@ typedef struct vc1d_prefill_args {
     int32_t tma_slab_bytes;      /* channel slab of a tile: 128 or 256 bytes */
     int32_t tma_rows_per_thread; /* 4 or 8 consecutive rows per thread and tile */
     /* Optional scratch for the TMA-staged kernel's dynamic tile scheduler: device memory, 16-byte
-     * aligned, at least 4096 + batch * ceil(seqlen / 32) bytes.  Its first 4096 bytes (one claim
-     * counter per channel slab) must be ZERO before its first use; every launch leaves them zeroed.
-     * With a mask a small pre-pass kernel fills the rest with one class byte per tile.  Launches
-     * that may overlap on the GPU must not share it.  NULL, too small, or more than 1023 channel
-     * slabs = static tile assignment. */
+     * aligned, at least 4096 + batch * ceil(seqlen / 32) bytes (4096 + 2 * batch * ceil(seqlen / 32)
+     * + 64 if class tables are to be kept between launches, see tma_kept_tables).  Its first 4096
+     * bytes (one claim counter per channel slab) must be ZERO before its first use; every launch
+     * leaves them zeroed.  With a mask a small pre-pass kernel fills a table behind them with one
+     * class byte per tile.  Launches that may overlap on the GPU must not share it.  NULL, too small,
+     * or more than 1023 channel slabs = static tile assignment. */
     void* scratch;
     int64_t scratch_bytes;
     /* Packed variable-length rows (the seq_idx argument of causal_conv1d_fn, signature at
@@ -148,6 +149,14 @@ typedef struct vc1d_prefill_args {
     int32_t tma_test_expire;     /* self-test of the bounded waits: 1 = every CTA withholds its first tile and
                                     polls only 4096 times, so the waits for that tile expire, the kernel
                                     returns normally with y incomplete and vc1d_tma_timeouts() has grown */
+    int32_t tma_kept_tables;     /* Class tables that earlier launches left in `scratch` and that are still current:
+                                    bit k = the one of tile-height slot k (vc1d_last_class_table() names the slot a
+                                    launch used).  A launch whose slot's bit is set runs no pre-pass.  The caller
+                                    vouches for it: the launch that wrote the table had the same mask (or seq_idx)
+                                    contents and strides, batch, seqlen, width, skip_masked_loads and the same
+                                    presence of residual and initial_state, and nothing but vc1d_prefill has
+                                    written to `scratch` since. */
+    int32_t tma_reserved;        /* 0 */
 } vc1d_prefill_args;
 
 VC1D_API int vc1d_prefill(const vc1d_prefill_args* args, void* stream);
@@ -331,6 +340,12 @@ VC1D_API uint64_t vc1d_launch_count(void);
  * "update_bwd").  Per host thread: a backward pass run by an autograd worker thread does not show
  * up in the thread that called the forward. */
 VC1D_API const char* vc1d_last_kernel(void);
+
+/* What the calling thread's last vc1d_prefill did with tile-class tables in `scratch`.  Low byte: 0 = touched
+   none, 1 = its pre-pass wrote the table of its tile-height slot, 2 = it read the one already there
+   (tma_kept_tables), 3 = the buffer has room for one table only and the pre-pass wrote it at the front: no
+   table there can be kept.  Bits 8 and up: the slot (0, 1, 2).  No reference counterpart. */
+VC1D_API int vc1d_last_class_table(void);
 
 /* Number of bounded mbarrier waits that expired inside the TMA-staged kernels since the process
  * started (0 in a healthy run; a CTA whose wait expires abandons its remaining tiles).  Reads a

@@ -605,6 +605,129 @@ def test_tma_class_table_of_a_very_long_batch():
     assert V.tma_timeouts() == 0
 
 
+def test_tile_classes_are_kept_while_the_mask_is_unchanged():
+    """Consecutive masked launches on one stream share their tile classes: the pre-pass runs for the first
+    of them and again as soon as anything the classes depend on differs (mask written in place, another
+    mask of equal contents, another sequence length, a backward launch in between), not when only the
+    channel count differs (a model's Canon calls A-D share the mask; each tile height has its own table).  Every result bit-equal to a launch
+    with the sharing switched off."""
+    B, T, W = 64, 1024, 4  # enough tiles per CTA for dynamic claims, which is what the class table serves
+    g = torch.Generator(device=DEV).manual_seed(11)
+    xs = {D: torch.randn(B, T, D, generator=g, device=DEV).bfloat16() for D in (640, 960)}
+    ws = {D: dev(O.seeded((D, W), D, "uniform", torch.bfloat16)) for D in xs}
+    bs = {D: dev(O.seeded((D,), D + 1, "uniform", torch.bfloat16)) for D in xs}
+    lens = torch.randint(1, T + 1, (B,), generator=torch.Generator().manual_seed(12))
+    m = (torch.arange(T)[None, :] < lens[:, None]).to(DEV)
+
+    def run(D, mask, **kw):
+        before = V.launch_count()
+        y = V.causal_conv1d_fn(xs[D].transpose(1, 2), ws[D], bs[D], activation="silu", attention_mask=mask, **kw)
+        assert V.last_kernel() == "tma"
+        return y, V.launch_count() - before
+
+    def fresh(D, mask):
+        was = V.reuse_tile_classes(False)
+        try:
+            y, n = run(D, mask)
+        finally:
+            V.reuse_tile_classes(was)
+        assert n == 2
+        return y
+
+    want = {D: fresh(D, m) for D in xs}
+    y, n = run(640, m)
+    assert n == 2 and torch.equal(y, want[640])  # pre-pass + main kernel
+    y, n = run(960, m)
+    assert n == 2 and torch.equal(y, want[960])  # 128-byte channel slabs, tiles twice as high: a table of its own
+    for D in (640, 960, 640, 960):
+        y, n = run(D, m)
+        assert n == 1 and torch.equal(y, want[D]), D  # the classes that an earlier launch left
+    # the mask written in place: torch counts it, the classes are worked out again
+    m[3, :] = False
+    m[4, 100:900] = False
+    want = {D: fresh(D, m) for D in xs}
+    y, n = run(960, m)
+    assert n == 2 and torch.equal(y, want[960])
+    y, n = run(960, m)
+    assert n == 1 and torch.equal(y, want[960])
+    # a view of the same memory is the same mask; another tensor of equal contents is not
+    y, n = run(640, m)
+    assert n == 2 and torch.equal(y, want[640])
+    y, n = run(640, m[:, :])
+    assert n == 1 and torch.equal(y, want[640])
+    m2 = m.clone()
+    y, n = run(640, m2)
+    assert n == 2 and torch.equal(y, want[640])
+    # a mask that dies and one of other contents that may take its place in memory
+    del m2
+    m3 = ~m
+    m3[:, 0] = True
+    want3 = fresh(640, m3)
+    y, n = run(640, m3)
+    assert n == 2 and torch.equal(y, want3)
+    # other options that the classes depend on
+    y, n = run(640, m3)
+    assert n == 1
+    y, n = run(640, m3, residual=True)
+    assert n == 2 and torch.equal(y, V.causal_conv1d_fn(xs[640].transpose(1, 2), ws[640], bs[640], activation="silu",
+                                                        attention_mask=m3, residual=True, kernel="channel_last"))
+    # a backward launch between two forward launches writes its own classes to the same scratch memory
+    y, n = run(640, m3)
+    assert n == 2
+    V.causal_conv1d_bwd(xs[640].transpose(1, 2), ws[640], bs[640], torch.ones_like(xs[640]).transpose(1, 2), "silu",
+                        attention_mask=m3, kernel="tma")
+    y, n = run(640, m3)
+    assert n == 2 and torch.equal(y, want3)
+    # a shorter batch with a mask at the same address and version: another number of tiles
+    xs_short = xs[640][:, :512]
+    before = V.launch_count()
+    y = V.causal_conv1d_fn(xs_short.transpose(1, 2), ws[640], bs[640], activation="silu", attention_mask=m3[:, :512])
+    assert V.launch_count() - before == 2
+    assert torch.equal(y, V.causal_conv1d_fn(xs_short.transpose(1, 2), ws[640], bs[640], activation="silu",
+                                             attention_mask=m3[:, :512], kernel="channel_last"))
+    torch.cuda.synchronize()
+    assert V.tma_timeouts() == 0
+
+
+def test_kept_tile_classes_and_cuda_graphs():
+    """A captured launch never relies on classes from outside its graph: replays stay correct after eager
+    launches with other masks have used the stream's scratch memory."""
+    B, T, D = 64, 1024, 640
+    g = torch.Generator(device=DEV).manual_seed(13)
+    x = torch.randn(B, T, D, generator=g, device=DEV).bfloat16()
+    w = dev(O.seeded((D, 4), 5, "uniform", torch.bfloat16))
+    lens = torch.randint(1, T + 1, (B,), generator=torch.Generator().manual_seed(14))
+    m = (torch.arange(T)[None, :] < lens[:, None]).to(DEV)
+    other = ~m
+    want = V.causal_conv1d_fn(x.transpose(1, 2), w, None, activation="silu", attention_mask=m, kernel="channel_last")
+    want_other = V.causal_conv1d_fn(x.transpose(1, 2), w, None, activation="silu", attention_mask=other, kernel="channel_last")
+    y = torch.empty_like(x)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        V.causal_conv1d_fn(x.transpose(1, 2), w, None, activation="silu", attention_mask=m, out=y.transpose(1, 2))
+        V.causal_conv1d_fn(x.transpose(1, 2), w, None, activation="silu", attention_mask=m, out=y.transpose(1, 2))
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            V.causal_conv1d_fn(x.transpose(1, 2), w, None, activation="silu", attention_mask=m, out=y.transpose(1, 2))
+            V.causal_conv1d_fn(x.transpose(1, 2), w, None, activation="silu", attention_mask=m, out=y.transpose(1, 2))
+    torch.cuda.current_stream().wait_stream(side)
+    for _ in range(2):
+        with torch.cuda.stream(side):
+            z = V.causal_conv1d_fn(x.transpose(1, 2), w, None, activation="silu", attention_mask=other)
+            assert torch.equal(z, want_other)
+            side.synchronize()
+        y.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y.transpose(1, 2), want)
+        with torch.cuda.stream(side):
+            z = V.causal_conv1d_fn(x.transpose(1, 2), w, None, activation="silu", attention_mask=m)
+            assert torch.equal(z, want)
+    assert V.tma_timeouts() == 0
+
+
 def test_bounded_waits_expire_and_report():
     """Failure detection of the TMA-staged kernel, provoked without faulting anything: with the
     self-test switch every producer warp withholds its first tile and every wait polls only 4096 times,

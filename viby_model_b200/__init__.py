@@ -16,7 +16,7 @@ that library raises ImportError: there is no CPU or PyTorch fallback.
 """
 from ._cabi import last_kernel, launch_count, library_path, set_pdl, tma_timeouts
 from .ops import (causal_conv1d_bwd, causal_conv1d_fn, causal_conv1d_fn_multi, causal_conv1d_update,
-                  causal_conv1d_update_bwd, seq_idx_from_lengths)
+                  causal_conv1d_update_bwd, reuse_tile_classes, seq_idx_from_lengths)
 from .short_conv import causal_conv1d_fwd, short_conv_fused, short_conv_update
 from . import compile_ops  # noqa: F401  (registers torch.ops.vc1d.* for torch.compile)
 
@@ -35,5 +35,6 @@ __all__ = [
     "library_path",
     "tma_timeouts",
     "set_pdl",
+    "reuse_tile_classes",
 ]
 __version__ = "0.1.0"

@@ -88,6 +88,8 @@ class PrefillArgs(C.Structure):
         ("tma_pdl", C.c_int32),
         ("tma_static_first", C.c_int32),
         ("tma_test_expire", C.c_int32),
+        ("tma_kept_tables", C.c_int32),
+        ("tma_reserved", C.c_int32),
     ]
 
 
@@ -229,6 +231,7 @@ EXPORTS = {
     "vc1d_status_string": (C.c_char_p, [C.c_int]),
     "vc1d_launch_count": (C.c_uint64, []),
     "vc1d_last_kernel": (C.c_char_p, []),
+    "vc1d_last_class_table": (C.c_int, []),
     "vc1d_tma_timeouts": (C.c_uint, []),
     "vc1d_set_pdl": (C.c_int, [C.c_int]),
 }

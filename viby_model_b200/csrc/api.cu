@@ -11,6 +11,7 @@ namespace vc1d {
 namespace {
 std::atomic<uint64_t> g_launches{0};
 thread_local const char* t_last_kernel = "none";
+thread_local int t_class_table = 0;
 std::atomic<int> g_sm_count[64];
 }  // namespace
 
@@ -36,6 +37,8 @@ bool pdl_enabled() {
     const int o = g_pdl_override.load(std::memory_order_relaxed);
     return o < 0 ? env_on : (o != 0);
 }
+
+void note_class_table(int state) { t_class_table = state; }
 
 void note_launch(const char* kernel_name) {
     g_launches.fetch_add(1, std::memory_order_relaxed);
@@ -213,6 +216,7 @@ extern "C" {
 
 VC1D_API int vc1d_prefill(const vc1d_prefill_args* a, void* stream) {
     using namespace vc1d;
+    note_class_table(0);
     const int st = check_prefill(a);
     if (st != VC1D_OK) return st;
     if ((long long)a->batch * a->dim * a->seqlen == 0) return VC1D_OK;
@@ -366,6 +370,8 @@ VC1D_API const char* vc1d_status_string(int status) {
 VC1D_API uint64_t vc1d_launch_count(void) { return vc1d::g_launches.load(std::memory_order_relaxed); }
 
 VC1D_API const char* vc1d_last_kernel(void) { return vc1d::t_last_kernel; }
+
+VC1D_API int vc1d_last_class_table(void) { return vc1d::t_class_table; }
 
 VC1D_API unsigned int vc1d_tma_timeouts(void) { return vc1d::tma_timeouts(); }
 

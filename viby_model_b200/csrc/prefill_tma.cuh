@@ -95,6 +95,7 @@ struct TmaParams {
     int chunk;       // consecutive tiles per dynamic claim
     int empty_tma;   // tiles without any live tap are written by one bulk tensor store each
     int inline_cls;  // every CTA classifies all tiles itself (consumer warps, while the first tile is in flight)
+    int table_early;  // the class table was written by an earlier launch's pre-pass: it may be read before the grid dependency wait
     int mask_vec;    // mask rows are contiguous and 16-byte aligned: whole tiles are classified with 128-bit loads
     int static_first;  // tiles a CTA takes without a claim (j0, j0 + G, ...) before the counter hands out the rest
     unsigned spin_limit;  // polls after which a wait gives up
@@ -542,7 +543,7 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
     // two bulk copies.  (Tiles are assigned statically when there is a mask.)
     // Launched with programmatic stream serialization, this grid may start while its predecessor in
     // the stream is still running: nothing above touched global memory, everything below may.
-    griddep_wait();
+    auto copy_table = [&]() {
     if (p.gtable != nullptr && p.table_in_smem == 2) {
         // large launches: two bits per tile, sixteen tiles to a word (the scratch table is padded to 16)
         const int n16 = (p.n_rowtiles + 15) >> 4;
@@ -565,6 +566,11 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         }
         for (int i = (n16 << 4) + threadIdx.x; i < p.n_rowtiles; i += G::kThreads) sts_u8(table + i, __ldcg(p.gtable + i));
     }
+    };
+    // a table kept from an earlier launch is older than anything this grid could be waiting for
+    if (p.table_early) copy_table();
+    griddep_wait();
+    if (!p.table_early) copy_table();
     if (p.mask != nullptr && p.gtable == nullptr && !p.inline_cls) {
         for (int i = warp; i < n_my; i += G::kThreads / 32) {
             int b, t0;
@@ -1046,7 +1052,19 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     p.sched = nullptr;
     p.gtable = nullptr;
     p.table_in_smem = 0;
-    const long long table_need = p.mask != nullptr ? n_rowtiles : 0;
+    // Class tables of the three tile heights (64, 128, 32 rows) have places of their own behind the
+    // counters, each as long as this batch and seqlen need, so that launches of different geometry that
+    // share a mask (the Canon layers of one block differ in width) can each keep theirs.  A scratch
+    // buffer with room for one table only has it at the front.
+    constexpr int kRegion = G::kTileRows == 64 ? 0 : (G::kTileRows == 128 ? 1 : 2);
+    auto table_len = [&](int rows) { return ((long long)a.batch * ((a.seqlen + rows - 1) / rows) + 15) / 16 * 16; };
+    long long tab_off = kRegion == 0 ? 0 : (kRegion == 1 ? table_len(64) : table_len(64) + table_len(128));
+    bool own_region = true;
+    if (p.mask != nullptr && a.scratch_bytes < kSchedCounterBytes + tab_off + (n_rowtiles + 15) / 16 * 16) {
+        tab_off = 0;
+        own_region = false;
+    }
+    const long long table_need = p.mask != nullptr ? tab_off + n_rowtiles : 0;
     // dynamic claims pay off once a CTA has several tiles; with two or three the claim round trips
     // (and, with a mask, the pre-pass) cost more than the balance gains
     p.spin_limit = a.tma_test_expire ? (1u << 12) : kSpinLimit;
@@ -1086,11 +1104,12 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
         if (p.inline_cls) {
             table_bytes = (int)((n_rowtiles + 15) / 16 * 16);
         } else if (p.mask != nullptr) {
-            tab = reinterpret_cast<unsigned char*>(a.scratch) + kSchedCounterBytes;
+            tab = reinterpret_cast<unsigned char*>(a.scratch) + kSchedCounterBytes + tab_off;
             if (n_rowtiles <= kSmemTableCap) {
                 p.table_in_smem = 1;
                 table_bytes = (int)((n_rowtiles + 15) / 16 * 16);
-            } else if (n_rowtiles <= 4LL * kSmemTableCap && a.scratch_bytes >= kSchedCounterBytes + (n_rowtiles + 15) / 16 * 16) {
+            } else if (n_rowtiles <= 4LL * kSmemTableCap &&
+                       a.scratch_bytes >= kSchedCounterBytes + tab_off + (n_rowtiles + 15) / 16 * 16) {
                 p.table_in_smem = 2;
                 table_bytes = (int)((n_rowtiles + 15) / 16 * 4);
             }
@@ -1126,7 +1145,13 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     cfg.stream = s;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (tab != nullptr) {
+    // tma_kept_tables: the caller vouches that the table at this geometry's place is the one the pre-pass would write
+    const bool keep_table = tab != nullptr && own_region && a.tma_classify == 0 && ((a.tma_kept_tables >> kRegion) & 1) != 0;
+    p.table_early = keep_table ? 1 : 0;
+    note_class_table(tab == nullptr ? 0 : ((keep_table ? 2 : (own_region ? 1 : 3)) | (kRegion << 8)));
+    if (keep_table) {
+        p.gtable = tab;
+    } else if (tab != nullptr) {
         const long long threads = n_rowtiles * 32;
         cfg.gridDim = dim3((unsigned)((threads + 255) / 256));
         cfg.blockDim = dim3(256);

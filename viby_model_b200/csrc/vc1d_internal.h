@@ -19,6 +19,8 @@ bool pdl_enabled();
 
 // Kernel launch bookkeeping shared by all launchers.
 void note_launch(const char* kernel_name);
+// what the calling thread's last prefill launch did with a class table in scratch: 0 none, 1 written, 2 kept
+void note_class_table(int state);
 
 // Channel-last prefill: x/y (and residual) have channel stride 1, dim % vec == 0, every
 // base pointer and every batch/time stride is 16-byte aligned.

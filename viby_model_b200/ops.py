@@ -245,6 +245,69 @@ def causal_conv1d_fn_multi(xs, weight: torch.Tensor, bias: Optional[torch.Tensor
     return outs
 
 
+# The tile classes of a masked (or packed) launch are a function of the mask alone, and a model hands one
+# mask to every Canon call of a forward pass (72 of them in the reference's network).  Per scratch buffer
+# this remembers whose pre-pass filled the class table: the mask tensor itself (kept alive, so that its
+# address cannot pass to another tensor), its version counter (torch counts every in-place write), and
+# the other things the classes depend on.  A launch that finds its own record there skips the pre-pass.
+# Writes that torch does not see (a foreign kernel given the raw pointer) are not noticed: such callers
+# switch this off with reuse_tile_classes(False).
+_CLASS_TABLES = {}  # (device, stream) -> {tile-height slot: (scratch buffer, mask, version, signature)}
+_REUSE_CLASSES = True
+
+
+def reuse_tile_classes(enabled: bool) -> bool:
+    """Let consecutive masked launches on one stream share their tile classes while the mask tensor is
+    unchanged (default on).  Returns the previous setting."""
+    global _REUSE_CLASSES
+    previous, _REUSE_CLASSES = _REUSE_CLASSES, bool(enabled)
+    _CLASS_TABLES.clear()
+    return previous
+
+
+def _mask_version(m: torch.Tensor):
+    try:
+        return m._version
+    except RuntimeError:  # inference tensors keep no version counter
+        return None
+
+
+def _scratch_bytes(batch: int, seqlen: int) -> int:
+    """Claim counters plus room for a class table per tile height."""
+    return 4096 + 2 * batch * ((seqlen + 31) // 32) + 64
+
+
+def _class_table_begin(a, sc: Optional[torch.Tensor], slot, m: torch.Tensor, sig):
+    """Before a forward launch with mask (or seq_idx) `m` on scratch `sc`: names the kept tables whose record
+    matches.  Returns what _class_table_end needs to make a record of this launch, or None."""
+    a.tma_kept_tables = 0
+    if sc is None or not _REUSE_CLASSES or a.tma_classify != 0 or _SCRATCH.get(slot) is not sc:
+        return None  # switched off, an explicit choice, or a scratch buffer of this call's own (graph capture, compiled region)
+    version = _mask_version(m)
+    if version is None:
+        return None
+    for region, (rsc, rm, rversion, rsig) in _CLASS_TABLES.get(slot, {}).items():
+        if (rsc is sc and rsig == sig and rversion == version and rm._version == version
+                and rm.data_ptr() == m.data_ptr() and rm.shape == m.shape and rm.stride() == m.stride()
+                and rm.dtype == m.dtype):
+            a.tma_kept_tables |= 1 << region
+    return version
+
+
+def _class_table_end(a, sc, slot, m, version, sig) -> None:
+    """After the launch: the table it wrote (if it wrote one) replaces the record of its place."""
+    a.tma_kept_tables = 0  # argument structs are kept for later calls
+    st = _cabi.lib.vc1d_last_class_table()
+    state, region = st & 0xFF, st >> 8
+    if state == 1:
+        if version is not None:
+            _CLASS_TABLES.setdefault(slot, {})[region] = (sc, m, version, sig)
+        else:
+            _CLASS_TABLES.get(slot, {}).pop(region, None)
+    elif state == 3:
+        _CLASS_TABLES.pop(slot, None)
+
+
 def _prefill_fast(x, weight, bias, activation, attention_mask, skip_masked_loads, residual, want_state, state_len):
     """Cached-signature path of _prefill_forward for the calls a Canon layer makes (no initial state,
     no preallocated outputs, no tuning overrides).  Returns (result, key); result is None when the
@@ -273,15 +336,22 @@ def _prefill_fast(x, weight, bias, activation, attention_mask, skip_masked_loads
         a.final_state = final_states.data_ptr()
     dev = x.device
     stream = _stream_handle(dev)
+    sc = None
     if _DYNAMIC_DEFAULT:
-        sc = _scheduler_scratch(dev, stream, 4096 + x.shape[0] * ((x.shape[2] + 31) // 32))
+        sc = _scheduler_scratch(dev, stream, _scratch_bytes(x.shape[0], x.shape[2]))
         a.scratch = sc.data_ptr()
         a.scratch_bytes = sc.numel() * 4
+    if m is not None:
+        slot = (dev.index, stream)
+        sig = ("mask", x.shape[0], x.shape[2], weight.shape[-1], bool(skip_masked_loads), residual is True, False)
+        version = _class_table_begin(a, sc, slot, m, sig)
     if dev.index != torch.cuda.current_device():
         with torch.cuda.device(dev):
             st = _cabi.lib.vc1d_prefill(C.byref(a), stream)
     else:
         st = _cabi.lib.vc1d_prefill(C.byref(a), stream)
+    if m is not None:
+        _class_table_end(a, sc, slot, m, version, sig)
     if st != 0:
         _cabi.check(st, "causal_conv1d_fn")
     return ((out, final_states) if want_state else out), key
@@ -415,15 +485,24 @@ def _prefill_forward(
             setattr(a, "tma_" + key, int(value))
 
     stream = _stream_handle(x.device)
+    sc = None
     if dynamic_schedule or (dynamic_schedule is None and _DYNAMIC_DEFAULT):
-        sc = _scheduler_scratch(x.device, stream, 4096 + batch * ((seqlen + 31) // 32))
+        sc = _scheduler_scratch(x.device, stream, _scratch_bytes(batch, seqlen))
         a.scratch = sc.data_ptr()
         a.scratch_bytes = sc.numel() * sc.element_size()
+    classes_of = seq_idx if seq_idx is not None else attention_mask
+    if classes_of is not None:
+        slot = (x.device.index, stream)
+        sig = ("ids" if seq_idx is not None else "mask", batch, seqlen, width, bool(skip_masked_loads),
+               a.residual is not None, initial_states is not None)
+        version = _class_table_begin(a, sc, slot, classes_of, sig)
     if x.device.index != torch.cuda.current_device():
         with torch.cuda.device(x.device):
             st = _cabi.lib.vc1d_prefill(C.byref(a), stream)
     else:
         st = _cabi.lib.vc1d_prefill(C.byref(a), stream)
+    if classes_of is not None:
+        _class_table_end(a, sc, slot, classes_of, version, sig)
     _cabi.check(st, "causal_conv1d_fn")
     if fast_key is not None and weight is weight_given and bias is bias_given:
         # remember the validated struct for later calls with the same shapes, strides and options
@@ -553,9 +632,10 @@ def causal_conv1d_bwd(
             setattr(a, "tma_" + key, int(value))
     stream = _stream_handle(x.device)
     if dynamic_schedule or (dynamic_schedule is None and _DYNAMIC_DEFAULT):
-        sc = _scheduler_scratch(x.device, stream, 4096 + batch * ((seqlen + 31) // 32))
+        sc = _scheduler_scratch(x.device, stream, _scratch_bytes(batch, seqlen))
         a.scratch = sc.data_ptr()
         a.scratch_bytes = sc.numel() * sc.element_size()
+        _CLASS_TABLES.pop((x.device.index, stream), None)  # the backward pre-pass writes its own classes there
     if x.device.index != torch.cuda.current_device():
         with torch.cuda.device(x.device):
             st = _cabi.lib.vc1d_prefill_bwd(C.byref(a), stream)
