@@ -122,12 +122,13 @@ typedef struct vc1d_prefill_args {
     int32_t tma_slab_bytes;      /* channel slab of a tile: 128 or 256 bytes */
     int32_t tma_rows_per_thread; /* 4 or 8 consecutive rows per thread and tile */
     /* Optional scratch for the TMA-staged kernel's dynamic tile scheduler: device memory, 16-byte
-     * aligned, at least 4096 + batch * ceil(seqlen / 32) bytes (4096 + 2 * batch * ceil(seqlen / 32)
-     * + 64 if class tables are to be kept between launches, see tma_kept_tables).  Its first 4096
-     * bytes (one claim counter per channel slab) must be ZERO before its first use; every launch
-     * leaves them zeroed.  With a mask a small pre-pass kernel fills a table behind them with one
-     * class byte per tile.  Launches that may overlap on the GPU must not share it.  NULL, too small,
-     * or more than 1023 channel slabs = static tile assignment. */
+     * aligned, at least 4096 + batch * ceil(seqlen / 32) bytes; with 4096 + 4 * batch * ceil(seqlen / 32)
+     * + 128 bytes tables of launches of different tile height do not overwrite each other (see
+     * tma_kept_tables) and a masked launch of up to 4096 tiles gets its tiles as a list ordered by
+     * cost.  Its first 4096 bytes (claim counters) must be ZERO before its first use; every launch
+     * leaves them zeroed.  With a mask a small pre-pass kernel fills a table behind them (a class byte
+     * per tile, or the ordered list).  Launches that may overlap on the GPU must not share it.  NULL,
+     * too small, or more than 1015 channel slabs = static tile assignment. */
     void* scratch;
     int64_t scratch_bytes;
     /* Packed variable-length rows (the seq_idx argument of causal_conv1d_fn, signature at
@@ -141,8 +142,9 @@ typedef struct vc1d_prefill_args {
     int32_t tma_claim_chunk;     /* consecutive tiles a CTA takes per claim: 1, 2 or 4 */
     int32_t tma_empty_store;     /* tiles whose taps are all masked: 1 = stored by the consumer warps,
                                     2 = one bulk tensor store per tile from a constant tile in shared memory */
-    int32_t tma_classify;        /* tile classes of a masked launch: 1 = pre-pass kernel, 2 = by every CTA itself
-                                    while its first tile is in flight (small masks only) */
+    int32_t tma_classify;        /* tile classes of a masked launch: 0 = pre-pass kernel, writing the ordered tile list
+                                    where the launch is small enough for it; 1 = pre-pass kernel, class bytes only;
+                                    2 = by every CTA itself while its first tile is in flight (small masks only) */
     int32_t tma_pdl;             /* main kernel launched as a programmatic dependent of whatever precedes it in
                                     the stream: 1 = only after a pre-pass, 2 = always */
     int32_t tma_static_first;    /* tiles every CTA takes without a claim before it starts claiming */
@@ -153,7 +155,7 @@ typedef struct vc1d_prefill_args {
                                     bit k = the one of tile-height slot k (vc1d_last_class_table() names the slot a
                                     launch used).  A launch whose slot's bit is set runs no pre-pass.  The caller
                                     vouches for it: the launch that wrote the table had the same mask (or seq_idx)
-                                    contents and strides, batch, seqlen, width, skip_masked_loads and the same
+                                    contents and strides, batch, seqlen, width, skip_masked_loads, tma_classify and the same
                                     presence of residual and initial_state, and nothing but vc1d_prefill has
                                     written to `scratch` since. */
     int32_t tma_reserved;        /* 0 */

@@ -88,7 +88,8 @@ struct TmaParams {
     int skip;
     int init_len;
     int res_is_x;
-    int table_in_smem;  // every CTA copies the pre-pass class table to shared memory: 1 = a byte per tile, 2 = two bits
+    int table_in_smem;  // every CTA copies the pre-pass class table to shared memory: 1 = a byte per tile, 2 = two bits,
+                        // 3 = the pre-pass wrote an ordered tile list instead (16 bits per claim position)
     int state_len;
     int stages;      // ring depth (2..kMaxStages)
     int seg_mode;    // mask holds int32 sequence ids (packed variable-length rows), not multipliers
@@ -149,7 +150,12 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int c0, int
                  : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// until the bulk stores committed so far have read their shared-memory source (their writes to global memory
+// are complete, like every other store, when the grid is)
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_tensormap(const void* tmap) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
+}
 // makes this thread's earlier shared-memory writes visible to bulk copies issued afterwards
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ float lds_f32(uint32_t a) {
@@ -178,6 +184,11 @@ __device__ __forceinline__ void lds_desc(uint32_t a, int& cls, int& rows, long l
     unsigned lo, hi;
     asm volatile("ld.volatile.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(cls), "=r"(rows), "=r"(lo), "=r"(hi) : "r"(a));
     yoff = (long long)(((unsigned long long)hi << 32) | lo);
+}
+__device__ __forceinline__ int lds_u16(uint32_t a) {
+    unsigned short v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(a));
+    return (int)v;
 }
 __device__ __forceinline__ int lds_u8(uint32_t a) {
     int v;
@@ -463,9 +474,17 @@ constexpr int kSchedCounterBytes = 4096;
 constexpr int kSmemTableCap = 16384;  // largest pre-pass class table a CTA copies into shared memory
 
 // (For the backward pass it can also clear the fp32 gradient accumulators, which saves a launch.)
+// With `order` the pre-pass writes a list of all tiles in the order the claims hand them out instead:
+// tiles with something to read from the front (ends[0] counts them), tiles without any live tap from
+// the back (ends[1]).  Entry = tile number | class << 14.  The cheap tiles (a few bulk stores each) are
+// then the last to be claimed, which evens out the moments at which the CTAs of a launch run dry.
+// ends[] must be zero at the start; the main kernel that follows leaves them zeroed.
+constexpr int kOrderedCap = 4096;         // most tiles a launch may have for the ordered list (8 KB of shared memory)
+constexpr int kOrderCounters = 1016;      // ends[] = the last words of the counter region of the scratch buffer
 static __global__ void __launch_bounds__(256) k_classify_tiles(const TmaParams p, unsigned char* table, int tile_rows, int H,
                                                                int box_rows, float* zero_a = nullptr, int n_a = 0,
-                                                               float* zero_b = nullptr, int n_b = 0) {
+                                                               float* zero_b = nullptr, int n_b = 0,
+                                                               unsigned short* order = nullptr, unsigned int* ends = nullptr) {
     griddep_wait();  // the table may still be read by the previous launch on this stream
     griddep_launch_dependents();
     {
@@ -480,7 +499,15 @@ static __global__ void __launch_bounds__(256) k_classify_tiles(const TmaParams p
     const int b = (int)(tile / p.n_ttile);
     const int tt = (int)(tile - (long long)b * p.n_ttile);
     const int cls = classify_tile(p, b, tt * tile_rows, H, box_rows, lane);
-    if (lane == 0) table[tile] = (unsigned char)cls;
+    if (lane == 0) {
+        if (order != nullptr) {
+            const unsigned n = (unsigned)p.n_rowtiles;
+            const unsigned pos = cls == TILE_EMPTY ? n - 1u - atomicAdd(ends + 1, 1u) : atomicAdd(ends, 1u);
+            if (pos < n) order[pos] = (unsigned short)((unsigned)tile | ((unsigned)cls << 14));
+        } else {
+            table[tile] = (unsigned char)cls;
+        }
+    }
 }
 
 template <int DT, int W, int SLAB_BYTES, int VB, int RPT, bool ACT>
@@ -518,6 +545,10 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
     const int slab_ch0 = slab * G::kSlabElems;
     const int n_my = (j0 < p.n_rowtiles) ? (p.n_rowtiles - j0 + stride - 1) / stride : 0;
 
+    if (threadIdx.x == G::kConsumerWarps * 32) {  // the producer's first lane: the descriptors its copies will name
+        prefetch_tensormap(&tmap_x);
+        if (kC) prefetch_tensormap(&tmap_y);
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(bars + 8 * s, 1);                              // full: the producer's arrive (+ tx bytes)
@@ -544,7 +575,15 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
     // Launched with programmatic stream serialization, this grid may start while its predecessor in
     // the stream is still running: nothing above touched global memory, everything below may.
     auto copy_table = [&]() {
-    if (p.gtable != nullptr && p.table_in_smem == 2) {
+    if (p.gtable != nullptr && p.table_in_smem == 3) {
+        const int n16 = (p.n_rowtiles + 7) >> 3;  // eight entries to 16 bytes; the list is padded to that
+        const uint4* src = reinterpret_cast<const uint4*>(p.gtable);
+        for (int i = threadIdx.x; i < n16; i += G::kThreads) {
+            const uint4 v = __ldcg(src + i);
+            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(table + 16 * i), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                         : "memory");
+        }
+    } else if (p.gtable != nullptr && p.table_in_smem == 2) {
         // large launches: two bits per tile, sixteen tiles to a word (the scratch table is padded to 16)
         const int n16 = (p.n_rowtiles + 15) >> 4;
         const uint4* src = reinterpret_cast<const uint4*>(p.gtable);
@@ -694,11 +733,28 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         float mv[NMK], mv_now[NMK];
 #pragma unroll
         for (int k = 0; k < NMK; ++k) mv[k] = 1.0f;
+        // claim position -> tile and class
+        auto resolve = [&](int pos, int i, int& bb, int& tt0, int& c) {
+            if (p.table_in_smem == 3) {
+                const int e = lds_u16(table + 2u * (uint32_t)pos);
+                const int id = e & 0x3fff;
+                c = e >> 14;
+                bb = id / p.n_ttile;
+                tt0 = (id - bb * p.n_ttile) * G::kTileRows;
+            } else {
+                locate(pos, bb, tt0);
+                c = tile_class(i, bb, tt0);
+            }
+        };
         if (rt >= 0) {
-            locate(rt, b, t0);
             // (classifying in the kernel: the consumer warps are still filling the table, so the
             // producer works out the class of its first tile by itself)
-            cls = p.inline_cls ? classify_tile(p, b, t0, H, G::kBoxRows, lane) : tile_class(0, b, t0);
+            if (p.inline_cls) {
+                locate(rt, b, t0);
+                cls = classify_tile(p, b, t0, H, G::kBoxRows, lane);
+            } else {
+                resolve(rt, 0, b, t0, cls);
+            }
             if (cls == TILE_MIXED) fetch_mask(b, t0, mv);
         }
         bool const_ready = false;  // the consumers have written the constant tile
@@ -717,7 +773,6 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
             }
             rt = next_tile();
             if (rt >= 0) {
-                locate(rt, b, t0);
                 if (!table_ready) {
                     table_ready = mbar_wait(tbar, 0, p.spin_limit);
                     if (!table_ready) {
@@ -726,7 +781,7 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
                         break;
                     }
                 }
-                cls = tile_class(i + 1, b, t0);
+                resolve(rt, i + 1, b, t0, cls);
                 if (cls == TILE_MIXED) fetch_mask(b, t0, mv);
             }
             if (put_done) continue;
@@ -774,11 +829,12 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
             const unsigned done = atomicAdd(p.sched + gridDim.x, 1u);
             if (done == n_ctas - 1) {
                 for (unsigned k = 0; k <= gridDim.x; ++k) p.sched[k] = 0u;
+                if (p.table_in_smem == 3) p.sched[kOrderCounters] = p.sched[kOrderCounters + 1] = 0u;  // the pre-pass's
                 __threadfence();
             }
         }
         // the bulk stores read the constant tile: shared memory must outlive them
-        if (kC && lane == 0) bulk_wait_all();
+        if (kC && lane == 0) bulk_wait_read();
         // No copy of this CTA may still be in flight when it ends.  Normally the consumers, who wait for
         // every copy, outlive this warp; if their waits expired they are gone already, so the copies
         // started here are waited for here as well (bounded like every wait).
@@ -1057,13 +1113,16 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     // share a mask (the Canon layers of one block differ in width) can each keep theirs.  A scratch
     // buffer with room for one table only has it at the front.
     constexpr int kRegion = G::kTileRows == 64 ? 0 : (G::kTileRows == 128 ? 1 : 2);
-    auto table_len = [&](int rows) { return ((long long)a.batch * ((a.seqlen + rows - 1) / rows) + 15) / 16 * 16; };
+    // (a place holds two bytes per tile: a class byte each, or the ordered list of a launch of up to kOrderedCap tiles)
+    auto table_len = [&](int rows) { return ((long long)a.batch * ((a.seqlen + rows - 1) / rows) + 15) / 16 * 32; };
     long long tab_off = kRegion == 0 ? 0 : (kRegion == 1 ? table_len(64) : table_len(64) + table_len(128));
     bool own_region = true;
-    if (p.mask != nullptr && a.scratch_bytes < kSchedCounterBytes + tab_off + (n_rowtiles + 15) / 16 * 16) {
+    if (p.mask != nullptr && a.scratch_bytes < kSchedCounterBytes + tab_off + table_len(G::kTileRows)) {
         tab_off = 0;
         own_region = false;
     }
+    const bool ordered = p.mask != nullptr && a.tma_classify == 0 && n_rowtiles <= kOrderedCap &&
+                         a.scratch_bytes >= kSchedCounterBytes + tab_off + table_len(G::kTileRows);
     const long long table_need = p.mask != nullptr ? tab_off + n_rowtiles : 0;
     // dynamic claims pay off once a CTA has several tiles; with two or three the claim round trips
     // (and, with a mask, the pre-pass) cost more than the balance gains
@@ -1078,7 +1137,7 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
         const long long whole = n_rowtiles / g;
         if (p.static_first > whole - 2) p.static_first = (int)(whole - 2 > 1 ? whole - 2 : 1);
     }
-    const bool use_scratch = tiles_per_cta >= 4 && a.scratch != nullptr && 4LL * (n_slab + 1) <= kSchedCounterBytes &&
+    const bool use_scratch = tiles_per_cta >= 4 && a.scratch != nullptr && n_slab + 1 <= kOrderCounters &&
                              a.scratch_bytes >= kSchedCounterBytes + table_need &&
                              (reinterpret_cast<uintptr_t>(a.scratch) & 15u) == 0;
     unsigned char* tab = nullptr;
@@ -1105,7 +1164,10 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
             table_bytes = (int)((n_rowtiles + 15) / 16 * 16);
         } else if (p.mask != nullptr) {
             tab = reinterpret_cast<unsigned char*>(a.scratch) + kSchedCounterBytes + tab_off;
-            if (n_rowtiles <= kSmemTableCap) {
+            if (ordered) {
+                p.table_in_smem = 3;
+                table_bytes = (int)((n_rowtiles + 7) / 8 * 16);
+            } else if (n_rowtiles <= kSmemTableCap) {
                 p.table_in_smem = 1;
                 table_bytes = (int)((n_rowtiles + 15) / 16 * 16);
             } else if (n_rowtiles <= 4LL * kSmemTableCap &&
@@ -1146,7 +1208,7 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     // tma_kept_tables: the caller vouches that the table at this geometry's place is the one the pre-pass would write
-    const bool keep_table = tab != nullptr && own_region && a.tma_classify == 0 && ((a.tma_kept_tables >> kRegion) & 1) != 0;
+    const bool keep_table = tab != nullptr && own_region && a.tma_classify != 2 && ((a.tma_kept_tables >> kRegion) & 1) != 0;
     p.table_early = keep_table ? 1 : 0;
     note_class_table(tab == nullptr ? 0 : ((keep_table ? 2 : (own_region ? 1 : 3)) | (kRegion << 8)));
     if (keep_table) {
@@ -1156,8 +1218,10 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
         cfg.gridDim = dim3((unsigned)((threads + 255) / 256));
         cfg.blockDim = dim3(256);
         cfg.dynamicSmemBytes = 0;
-        const cudaError_t e = cudaLaunchKernelEx(&cfg, k_classify_tiles, p, tab, (int)G::kTileRows, (int)G::kH,
-                                                 (int)G::kBoxRows, (float*)nullptr, 0, (float*)nullptr, 0);
+        const cudaError_t e = cudaLaunchKernelEx(
+            &cfg, k_classify_tiles, p, tab, (int)G::kTileRows, (int)G::kH, (int)G::kBoxRows, (float*)nullptr, 0, (float*)nullptr,
+            0, ordered ? reinterpret_cast<unsigned short*>(tab) : (unsigned short*)nullptr,
+            ordered ? p.sched + kOrderCounters : (unsigned int*)nullptr);
         if (e != cudaSuccess) return e;
         note_launch("classify");
         p.gtable = tab;

@@ -274,14 +274,14 @@ def _mask_version(m: torch.Tensor):
 
 def _scratch_bytes(batch: int, seqlen: int) -> int:
     """Claim counters plus room for a class table per tile height."""
-    return 4096 + 2 * batch * ((seqlen + 31) // 32) + 64
+    return 4096 + 4 * batch * ((seqlen + 31) // 32) + 128
 
 
 def _class_table_begin(a, sc: Optional[torch.Tensor], slot, m: torch.Tensor, sig):
     """Before a forward launch with mask (or seq_idx) `m` on scratch `sc`: names the kept tables whose record
     matches.  Returns what _class_table_end needs to make a record of this launch, or None."""
     a.tma_kept_tables = 0
-    if sc is None or not _REUSE_CLASSES or a.tma_classify != 0 or _SCRATCH.get(slot) is not sc:
+    if sc is None or not _REUSE_CLASSES or a.tma_classify not in (0, 1) or _SCRATCH.get(slot) is not sc:
         return None  # switched off, an explicit choice, or a scratch buffer of this call's own (graph capture, compiled region)
     version = _mask_version(m)
     if version is None:
@@ -343,7 +343,7 @@ def _prefill_fast(x, weight, bias, activation, attention_mask, skip_masked_loads
         a.scratch_bytes = sc.numel() * 4
     if m is not None:
         slot = (dev.index, stream)
-        sig = ("mask", x.shape[0], x.shape[2], weight.shape[-1], bool(skip_masked_loads), residual is True, False)
+        sig = ("mask", x.shape[0], x.shape[2], weight.shape[-1], bool(skip_masked_loads), residual is True, False, 0)
         version = _class_table_begin(a, sc, slot, m, sig)
     if dev.index != torch.cuda.current_device():
         with torch.cuda.device(dev):
@@ -494,7 +494,7 @@ def _prefill_forward(
     if classes_of is not None:
         slot = (x.device.index, stream)
         sig = ("ids" if seq_idx is not None else "mask", batch, seqlen, width, bool(skip_masked_loads),
-               a.residual is not None, initial_states is not None)
+               a.residual is not None, initial_states is not None, int(a.tma_classify))
         version = _class_table_begin(a, sc, slot, classes_of, sig)
     if x.device.index != torch.cuda.current_device():
         with torch.cuda.device(x.device):
