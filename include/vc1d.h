@@ -146,7 +146,7 @@ typedef struct vc1d_prefill_args {
                                     where the launch is small enough for it; 1 = pre-pass kernel, class bytes only;
                                     2 = by every CTA itself while its first tile is in flight (small masks only) */
     int32_t tma_pdl;             /* main kernel launched as a programmatic dependent of whatever precedes it in
-                                    the stream: 1 = only after a pre-pass, 2 = always */
+                                    the stream: 0 = always, 1 = only when the launch uses a tile table */
     int32_t tma_static_first;    /* tiles every CTA takes without a claim before it starts claiming */
     int32_t tma_test_expire;     /* self-test of the bounded waits: 1 = every CTA withholds its first tile and
                                     polls only 4096 times, so the waits for that tile expire, the kernel

@@ -550,7 +550,8 @@ def _mask_of_kind(kind, B, T, seed):
     return torch.ones(B, T, dtype=torch.bool)
 
 
-@pytest.mark.parametrize("tma", [dict(empty_store=1), dict(empty_store=2), dict(classify=2), dict(static_first=3),
+@pytest.mark.parametrize("tma", [dict(empty_store=1), dict(empty_store=2), dict(classify=1), dict(classify=2), dict(static_first=3),
+                                 dict(classify=1, empty_store=1),
                                  dict(claim_chunk=2), dict(claim_chunk=4, empty_store=1),
                                  dict(classify=2, static_first=2, pdl=2), dict(rows_per_thread=4, empty_store=2)],
                          ids=lambda d: ",".join(f"{k}={v}" for k, v in d.items()))
@@ -558,8 +559,10 @@ def _mask_of_kind(kind, B, T, seed):
 @pytest.mark.parametrize("mask_dtype,D", [(torch.bool, 1160), (torch.int64, 1160), (torch.bool, 960)])
 def test_tma_scheduling_variants_agree(mask_dtype, D, mask_kind, tma):
     """Every way the TMA-staged kernel can hand out, classify and store its tiles gives the bits of the
-    register-window kernel: bulk-stored or consumer-stored constant tiles, tile classes from the
-    pre-pass or worked out inside the kernel, chunked claims, unclaimed first tiles.  The shapes have a
+    register-window kernel: bulk-stored or consumer-stored constant tiles, tiles handed out from the
+    pre-pass's list ordered by cost (the default at this size) or in their natural order with a class byte
+    each, classes worked out inside the kernel, chunked claims, unclaimed first tiles.  The second and third
+    launch of each case use the list or table that the first one left.  The shapes have a
     last time tile that is not full and either a last 256-byte channel slab that is half outside the
     tensor (1160 channels) or 128-byte slabs and 128-row tiles (960 channels, the Canon-B width)."""
     B, T, W = 20, 1008, 4

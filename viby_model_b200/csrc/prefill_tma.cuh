@@ -606,10 +606,15 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         for (int i = (n16 << 4) + threadIdx.x; i < p.n_rowtiles; i += G::kThreads) sts_u8(table + i, __ldcg(p.gtable + i));
     }
     };
-    // a table kept from an earlier launch is older than anything this grid could be waiting for
+    // A table kept from an earlier launch is older than anything this grid could be waiting for.  With it
+    // (or without a mask) the producer can work out its first tile before the wait, which it then
+    // passes in its own branch; so do the consumer warps.
+    const bool early = p.mask == nullptr || p.table_early;
     if (p.table_early) copy_table();
-    griddep_wait();
-    if (!p.table_early) copy_table();
+    if (!early) {
+        griddep_wait();
+        copy_table();
+    }
     if (p.mask != nullptr && p.gtable == nullptr && !p.inline_cls) {
         for (int i = warp; i < n_my; i += G::kThreads / 32) {
             int b, t0;
@@ -755,8 +760,9 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
             } else {
                 resolve(rt, 0, b, t0, cls);
             }
-            if (cls == TILE_MIXED) fetch_mask(b, t0, mv);
         }
+        if (early) griddep_wait();  // from here on global memory is touched
+        if (rt >= 0 && cls == TILE_MIXED) fetch_mask(b, t0, mv);
         bool const_ready = false;  // the consumers have written the constant tile
         bool table_ready = !p.inline_cls;  // the consumers have classified every tile
         for (int i = 0; live && rt >= 0; ++i) {
@@ -764,9 +770,9 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
 #pragma unroll
             for (int k = 0; k < NMK; ++k) mv_now[k] = mv[k];
             bool put_done = false;
-            if (!table_ready && !(cls_now == TILE_EMPTY && kC)) {
-                // first tile of a CTA that classifies in the kernel: start its copy before waiting for
-                // the table the next claim needs
+            if (i == 0 && !(cls_now == TILE_EMPTY && kC)) {
+                // a CTA's first tile: its copy starts before anything else is looked at (a CTA that
+                // classifies in the kernel would otherwise wait for the table the next claim needs)
                 put_tile(b_now, t0_now, cls_now, mv_now);
                 advance();
                 put_done = true;
@@ -848,6 +854,7 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         const bool ch_ok = d0 < p.D;  // dim is a multiple of the 128-bit vector: a slice is in or out as a whole
         const int rbase = grp * R;
 
+        if (early) griddep_wait();
         float2 wp[W][NP];
         float2 bp[NP];
         load_weights<DT, W, VB>(p, d0, ch_ok, wp, bp);
@@ -1195,14 +1202,13 @@ cudaError_t launch_kernel(const vc1d_prefill_args& a, const TmaParams& base, cud
             if (dev >= 0 && dev < 64) granted[dev].store(smem, std::memory_order_release);
         }
     }
-    // A masked launch with a pre-pass uses programmatic stream serialization for both kernels: each
-    // may start while its predecessor in the stream drains, and waits (griddep_wait) before it
-    // touches global memory, which hides the pre-pass and both launch latencies.  Launches without
-    // a pre-pass are serialized normally: letting dense launches overlap brought nothing.
+    // Both kernels are launched with programmatic stream serialization: each may start while its
+    // predecessor in the stream drains, and waits (griddep_wait) before it touches global memory, which
+    // hides the launch latencies and the part of the prologue that needs no global memory.
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed =
-        (pdl_enabled() && (tab != nullptr || a.tma_pdl == 2)) ? 1 : 0;
+        (pdl_enabled() && (tab != nullptr || a.tma_pdl != 1)) ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
     cfg.stream = s;
     cfg.attrs = attr;
