@@ -344,7 +344,7 @@ def main():
     ap.add_argument("--no-ragged", action="store_true")
     ap.add_argument("--no-shapes", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--only", default=None, choices=["headline", "decode_saturating", "ragged", "backward"],
+    ap.add_argument("--only", default=None, choices=["headline", "decode_saturating", "ragged", "backward", "model_prefill"],
                     help="run one section and print its figures (for profiling: few launches, small footprint)")
     ap.add_argument("--state-len", type=int, default=3, help="state length of --only decode_saturating")
     ap.add_argument("--circular", action="store_true", help="circular state for --only decode_saturating")
@@ -401,6 +401,9 @@ def main():
         return
     if args.only == "ragged":
         emit({"ragged_sweep": bench_ragged(ctx, steps=min(steps, 10))})
+        return
+    if args.only == "model_prefill":
+        emit({"model_prefill_step": bench_model_prefill_step(ctx)})
         return
 
     # ---- workload: this rank's 32 sequences ---------------------------------------------------
@@ -479,6 +482,7 @@ def main():
         decode = None if args.no_decode else bench_decode(ctx)
         model_step = None if args.no_decode else bench_model_decode_step(ctx)
         shapes = None if args.no_shapes else bench_shapes(ctx)
+        model_prefill = None if args.no_shapes else bench_model_prefill_step(ctx)
         del x_host
         ragged = None if args.no_ragged else bench_ragged(ctx, steps=10)
 
@@ -559,6 +563,8 @@ def main():
         line["model_decode_step"] = model_step
     if shapes is not None:
         line["shapes"] = shapes
+    if model_prefill is not None:
+        line["model_prefill_step"] = model_prefill
     if ragged is not None:
         line["ragged_sweep"] = ragged
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -871,6 +877,49 @@ def bench_shapes(ctx):
                      "frac_of_measured_peak": nbytes / (ms * 1e-3) / 1e9 / ctx.peak,
                      "tokens_per_s": ctx.world * B * T / (ms * 1e-3)}
         del x, y
+    return out
+
+
+def bench_model_prefill_step(ctx):
+    """The 72 Canon prefill calls of one forward pass of the whole-model configuration (18 blocks x Canon
+    A, B, C, D at 640 / 960 / 640 / 3456 channels; batch 64 x 1024 tokens, bf16, no bias, no activation:
+    the reference's defaults) with the padding mask applied inside the kernel, every call handed the same
+    mask tensor as the reference's network does (model/model.py:1021-1055).  Tile classes are worked
+    out once per tile height and kept for the other calls; the second figure does it on every call; the
+    third is the dense call pattern of the reference's own layer (mask multiplied in beforehand)."""
+    V, WL, dev = ctx.V, ctx.WL, ctx.dev
+    B, T, W, layers = 64, 1024, 4, 18
+    dims = [640, 960, 640, 3456]
+    g = torch.Generator(device=dev).manual_seed(6)
+    xs = {D: torch.randn(B, T, D, generator=g, device=dev).bfloat16() for D in set(dims)}
+    ys = {D: torch.empty_like(x) for D, x in xs.items()}
+    ws = {D: (torch.rand(D, W, generator=g, device=dev) - 0.5).bfloat16() for D in set(dims)}
+    lens = torch.randint(128, T + 1, (B,), generator=torch.Generator().manual_seed(7))
+    mask = (torch.arange(T)[None, :] < lens[:, None]).to(dev)
+    valid = int(lens.sum())
+    nbytes = layers * sum((valid + B * T) * D * 2 for D in dims)
+    dense_bytes = layers * sum(2 * B * T * D * 2 for D in dims)
+
+    def step(m):
+        for _ in range(layers):
+            for D in dims:
+                V.causal_conv1d_fn(xs[D].transpose(1, 2), ws[D], None, attention_mask=m, out=ys[D].transpose(1, 2))
+
+    out = {"calls_per_step": 4 * layers, "batch": B, "seq_len": T, "channels": dims, "layers": layers,
+           "valid_tokens": valid, "bytes_per_step": nbytes, "dense_bytes_per_step": dense_bytes}
+    for name, m, keep, nb in (("masked_classes_kept", mask, True, nbytes), ("masked_classified_every_call", mask, False, nbytes),
+                              ("dense", None, True, dense_bytes)):
+        was = V.reuse_tile_classes(keep)
+        try:
+            before = V.launch_count()
+            ms_rank, host_s = ctx.time_loop(lambda: step(m), 5, warmup=2)
+            launches = (V.launch_count() - before) // 7
+        finally:
+            V.reuse_tile_classes(was)
+        ms = ctx.max_over_ranks(ms_rank) / 5
+        out[name] = {"ms_per_step": ms, "us_per_call": ms * 1e3 / (4 * layers), "launches_per_step": launches,
+                     "achieved_gbs": nb / (ms * 1e-3) / 1e9, "frac_of_measured_peak": nb / (ms * 1e-3) / 1e9 / ctx.peak,
+                     "tokens_per_s": ctx.world * B * T / (ms * 1e-3), "host_enqueue_us_per_step": host_s / 5 * 1e6}
     return out
 
 

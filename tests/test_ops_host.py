@@ -95,3 +95,61 @@ def test_custom_ops_have_shape_functions():
         assert dx.stride() == x.stride() and dw.shape == (64, 4) and dw.dtype == torch.float32 and db.shape == (64,)
         s = torch.empty(2, 64, 4, device="cuda", dtype=torch.bfloat16)
         assert torch.ops.vc1d.update(x[..., 0], s, w, b, None, 1, False).shape == (2, 64)
+
+
+def test_kept_tile_tables_bookkeeping(monkeypatch):
+    """Host side of the tile tables kept between masked launches (ops._class_table_begin/_end): a table is
+    offered to a launch only for the same scratch buffer, the same mask memory, layout and torch version
+    counter and the same options; what the launch reports (vc1d_last_class_table) updates the record of
+    its tile-height place.  No kernel runs: the report is faked."""
+    from viby_model_b200 import _cabi, ops
+
+    report = {"value": 0}
+    monkeypatch.setattr(_cabi.lib, "vc1d_last_class_table", lambda: report["value"], raising=False)
+    monkeypatch.setattr(ops, "_CLASS_TABLES", {})
+    a = _cabi.PrefillArgs()
+    slot = (0, 1234)
+    sc = torch.zeros(16, dtype=torch.int32)
+    monkeypatch.setitem(ops._SCRATCH, slot, sc)
+    m = torch.ones(4, 8, dtype=torch.bool)
+    sig = ("mask", 4, 8, 4, True, False, False, 0)
+
+    def launch(mask, says, signature=sig, scratch=sc):
+        version = ops._class_table_begin(a, scratch, slot, mask, signature)
+        offered = a.tma_kept_tables
+        report["value"] = says
+        ops._class_table_end(a, scratch, slot, mask, version, signature)
+        assert a.tma_kept_tables == 0  # argument structs are reused
+        return offered
+
+    WROTE, READ, FRONT = 1, 2, 3
+    assert launch(m, WROTE) == 0  # nothing known yet; the pre-pass wrote place 0
+    assert launch(m, READ) == 1
+    assert launch(m[:, :], READ) == 1  # a view of the same memory
+    assert launch(m, WROTE | (1 << 8), sig[:3] + (4,) + sig[4:]) == 1  # place 1 (another tile height) written
+    assert launch(m, READ) == 3
+    assert launch(m, 0, sig[:4] + (False,) + sig[5:]) == 0  # other options: not the same classes
+    assert launch(m, READ) == 3  # ... and that launch (on a kernel without tables) touched none
+    assert launch(m.clone(), 0) == 0  # equal contents elsewhere in memory
+    m[0, 0] = False  # torch counts the write
+    assert launch(m, WROTE) == 0
+    assert launch(m, READ) == 1  # place 1 holds the classes of the old contents and is not offered
+    other = torch.zeros(16, dtype=torch.int32)
+    assert launch(m, 0, scratch=other) == 0  # not the stream's buffer: a call's own scratch
+    assert launch(m, READ) == 1
+    assert launch(m, FRONT) == 1  # a buffer with room for one table: whatever was there is gone
+    assert launch(m, READ) == 0
+    assert launch(m, WROTE) == 0
+    with torch.inference_mode():
+        untracked = torch.ones(4, 8, dtype=torch.bool)
+    assert launch(untracked, WROTE) == 0  # no version counter: never kept
+    assert launch(untracked, WROTE) == 0
+    assert launch(m, READ) == 0  # and its pre-pass overwrote place 0
+    was = ops.reuse_tile_classes(False)
+    try:
+        assert launch(m, WROTE) == 0
+        assert launch(m, WROTE) == 0
+    finally:
+        ops.reuse_tile_classes(was)
+    a.tma_classify = 2  # an explicit choice of the caller
+    assert launch(m, 0) == 0
