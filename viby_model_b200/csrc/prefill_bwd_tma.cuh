@@ -144,6 +144,10 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES, VARIANT>::kThre
     const int slab_ch0 = slab * G::kSlabElems;
     const int n_my = (j0 < p.n_rowtiles) ? (p.n_rowtiles - j0 + stride - 1) / stride : 0;
 
+    if (threadIdx.x == G::kConsumerWarps * 32) {
+        prefetch_tensormap(&tmap_x);
+        prefetch_tensormap(&tmap_g);
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(bars + 8 * s, 1);
@@ -151,8 +155,8 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES, VARIANT>::kThre
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // launched as a programmatic dependent of the tile-classification pre-pass when there is one:
-    // nothing above touched global memory
+    // launched as a programmatic dependent of whatever precedes it in the stream (the tile-classification
+    // pre-pass when there is one): nothing above touched global memory
     griddep_wait();
     __syncthreads();
 
@@ -217,6 +221,9 @@ __global__ void __launch_bounds__(BwdGeometry<DT, W, SLAB_BYTES, VARIANT>::kThre
             __syncwarp();
             advance();
         }
+        // every tile of this CTA is on its way: a dependent launch of the stream may take the slots that CTAs
+        // free as they finish
+        griddep_launch_dependents();
         if (live && claim()) {
             if (lane == 0) {
                 sts_desc(flags + 32 * s_ring, TILE_END, 0, 0);
@@ -569,10 +576,20 @@ cudaError_t launch_bwd_kernel(const vc1d_prefill_bwd_args& a, const BwdParams& b
             cp.init = nullptr;
             unsigned char* tab = reinterpret_cast<unsigned char*>(a.scratch) + kSchedCounterBytes;
             const long long threads = n_rowtiles * 32;
-            k_classify_tiles<<<(unsigned)((threads + 255) / 256), 256, 0, s>>>(
-                cp, tab, (int)G::kTileRows, (int)G::kH, (int)G::kXRows, zero_pending ? a.dweight : nullptr,
-                zero_pending ? n_dw : 0, zero_pending ? a.dbias : nullptr, zero_pending ? n_db : 0);
-            const cudaError_t e = cudaGetLastError();
+            // (the pre-pass waits for its predecessor before it writes anything: it may start while that one drains)
+            cudaLaunchAttribute pattr[1];
+            pattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            pattr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+            cudaLaunchConfig_t pcfg = {};
+            pcfg.gridDim = dim3((unsigned)((threads + 255) / 256));
+            pcfg.blockDim = dim3(256);
+            pcfg.stream = s;
+            pcfg.attrs = pattr;
+            pcfg.numAttrs = 1;
+            const cudaError_t e = cudaLaunchKernelEx(
+                &pcfg, k_classify_tiles, cp, tab, (int)G::kTileRows, (int)G::kH, (int)G::kXRows,
+                zero_pending ? a.dweight : (float*)nullptr, zero_pending ? n_dw : 0, zero_pending ? a.dbias : (float*)nullptr,
+                zero_pending ? n_db : 0, (unsigned short*)nullptr, (unsigned int*)nullptr);
             if (e != cudaSuccess) return e;
             zero_pending = false;
             note_launch("classify");
@@ -585,10 +602,11 @@ cudaError_t launch_bwd_kernel(const vc1d_prefill_bwd_args& a, const BwdParams& b
         if (e != cudaSuccess) return e;
     }
     note_launch("bwd_tma");
-    // after a pre-pass the main kernel is its programmatic dependent: its launch and prologue overlap it
+    // the main kernel is a programmatic dependent of its predecessor (the pre-pass when there is one): its launch
+    // and prologue overlap it
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = (pdl_enabled() && p.gtable != nullptr) ? 1 : 0;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)n_slab, (unsigned)g);
     cfg.blockDim = dim3(G::kThreads);
