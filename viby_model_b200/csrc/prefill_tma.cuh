@@ -96,7 +96,8 @@ struct TmaParams {
     int chunk;       // consecutive tiles per dynamic claim
     int empty_tma;   // tiles without any live tap are written by one bulk tensor store each
     int inline_cls;  // every CTA classifies all tiles itself (consumer warps, while the first tile is in flight)
-    int table_early;  // the class table was written by an earlier launch's pre-pass: it may be read before the grid dependency wait
+    int table_early;  // the table or list was written by an earlier launch's pre-pass: it may be read before the
+                      // grid dependency wait
     int mask_vec;    // mask rows are contiguous and 16-byte aligned: whole tiles are classified with 128-bit loads
     int static_first;  // tiles a CTA takes without a claim (j0, j0 + G, ...) before the counter hands out the rest
     unsigned spin_limit;  // polls after which a wait gives up
@@ -569,42 +570,43 @@ __global__ void __launch_bounds__(Geometry<DT, W, SLAB_BYTES, VB, RPT>::kThreads
         t0 = tt * G::kTileRows;
     };
 
-    // ---- prologue with a mask: classify all of this CTA's tiles, one warp per tile, all warps ----
-    // at once.  The producer then only reads a byte per tile, so no mask latency ever sits between
-    // two bulk copies.  (Tiles are assigned statically when there is a mask.)
+    // ---- prologue with a mask: the class of every tile this CTA may take is in shared memory before ----
+    // the tile loop starts (the pre-pass's table or list copied from scratch memory, or, without
+    // scratch, this CTA's own tiles classified here, one warp per tile), so no mask latency ever sits
+    // between two bulk copies.
     // Launched with programmatic stream serialization, this grid may start while its predecessor in
-    // the stream is still running: nothing above touched global memory, everything below may.
+    // the stream is still running: nothing above touched global memory.
     auto copy_table = [&]() {
-    if (p.gtable != nullptr && p.table_in_smem == 3) {
-        const int n16 = (p.n_rowtiles + 7) >> 3;  // eight entries to 16 bytes; the list is padded to that
-        const uint4* src = reinterpret_cast<const uint4*>(p.gtable);
-        for (int i = threadIdx.x; i < n16; i += G::kThreads) {
-            const uint4 v = __ldcg(src + i);
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(table + 16 * i), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                         : "memory");
-        }
-    } else if (p.gtable != nullptr && p.table_in_smem == 2) {
-        // large launches: two bits per tile, sixteen tiles to a word (the scratch table is padded to 16)
-        const int n16 = (p.n_rowtiles + 15) >> 4;
-        const uint4* src = reinterpret_cast<const uint4*>(p.gtable);
-        for (int i = threadIdx.x; i < n16; i += G::kThreads) {
-            const uint4 v = __ldcg(src + i);
-            const unsigned wv[4] = {v.x, v.y, v.z, v.w};
-            unsigned packed = 0u;
+        if (p.gtable != nullptr && p.table_in_smem == 3) {
+            const int n16 = (p.n_rowtiles + 7) >> 3;  // eight entries to 16 bytes; the list is padded to that
+            const uint4* src = reinterpret_cast<const uint4*>(p.gtable);
+            for (int i = threadIdx.x; i < n16; i += G::kThreads) {
+                const uint4 v = __ldcg(src + i);
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(table + 16 * i), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                             : "memory");
+            }
+        } else if (p.gtable != nullptr && p.table_in_smem == 2) {
+            // large launches: two bits per tile, sixteen tiles to a word (the scratch table is padded to 16)
+            const int n16 = (p.n_rowtiles + 15) >> 4;
+            const uint4* src = reinterpret_cast<const uint4*>(p.gtable);
+            for (int i = threadIdx.x; i < n16; i += G::kThreads) {
+                const uint4 v = __ldcg(src + i);
+                const unsigned wv[4] = {v.x, v.y, v.z, v.w};
+                unsigned packed = 0u;
 #pragma unroll
-            for (int k = 0; k < 16; ++k) packed |= ((wv[k >> 2] >> (8 * (k & 3))) & 3u) << (2 * k);
-            sts_s32(table + 4 * i, (int)packed);
+                for (int k = 0; k < 16; ++k) packed |= ((wv[k >> 2] >> (8 * (k & 3))) & 3u) << (2 * k);
+                sts_s32(table + 4 * i, (int)packed);
+            }
+        } else if (p.gtable != nullptr && p.table_in_smem) {
+            const int n16 = p.n_rowtiles >> 4;
+            const uint4* src = reinterpret_cast<const uint4*>(p.gtable);
+            for (int i = threadIdx.x; i < n16; i += G::kThreads) {
+                const uint4 v = __ldcg(src + i);  // written by the pre-pass while this grid was already resident: no read-only path
+                asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(table + 16 * i), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                             : "memory");
+            }
+            for (int i = (n16 << 4) + threadIdx.x; i < p.n_rowtiles; i += G::kThreads) sts_u8(table + i, __ldcg(p.gtable + i));
         }
-    } else if (p.gtable != nullptr && p.table_in_smem) {
-        const int n16 = p.n_rowtiles >> 4;
-        const uint4* src = reinterpret_cast<const uint4*>(p.gtable);
-        for (int i = threadIdx.x; i < n16; i += G::kThreads) {
-            const uint4 v = __ldcg(src + i);  // written by the pre-pass while this grid was already resident: no read-only path
-            asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(table + 16 * i), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                         : "memory");
-        }
-        for (int i = (n16 << 4) + threadIdx.x; i < p.n_rowtiles; i += G::kThreads) sts_u8(table + i, __ldcg(p.gtable + i));
-    }
     };
     // A table kept from an earlier launch is older than anything this grid could be waiting for.  With it
     // (or without a mask) the producer can work out its first tile before the wait, which it then
