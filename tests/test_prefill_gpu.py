@@ -731,6 +731,35 @@ def test_kept_tile_classes_and_cuda_graphs():
     assert V.tma_timeouts() == 0
 
 
+def test_kept_tile_classes_on_two_streams():
+    """Two streams with a mask each, launches interleaved from one host thread: every stream has its own
+    scratch memory and its own record of kept tables, so neither sees the other's classes."""
+    B, T, D = 64, 1024, 640
+    g = torch.Generator(device=DEV).manual_seed(21)
+    x = torch.randn(B, T, D, generator=g, device=DEV).bfloat16()
+    w = dev(O.seeded((D, 4), 5, "uniform", torch.bfloat16))
+    b = dev(O.seeded((D,), 6, "uniform", torch.bfloat16))
+    lens = torch.randint(1, T + 1, (B,), generator=torch.Generator().manual_seed(22))
+    masks = [(torch.arange(T)[None, :] < lens[:, None]).to(DEV), (torch.arange(T)[None, :] >= (T - lens)[:, None]).to(DEV)]
+    want = [V.causal_conv1d_fn(x.transpose(1, 2), w, b, activation="silu", attention_mask=m, kernel="channel_last") for m in masks]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    outs = [[], []]
+    counts = [[], []]
+    for it in range(6):
+        for k in (0, 1):
+            with torch.cuda.stream(streams[k]):
+                before = V.launch_count()
+                outs[k].append(V.causal_conv1d_fn(x.transpose(1, 2), w, b, activation="silu", attention_mask=masks[k]))
+                counts[k].append(V.launch_count() - before)
+    torch.cuda.synchronize()
+    for k in (0, 1):
+        assert counts[k] == [2, 1, 1, 1, 1, 1], counts[k]
+        for y in outs[k]:
+            assert torch.equal(y, want[k])
+    assert V.tma_timeouts() == 0
+
+
 def test_bounded_waits_expire_and_report():
     """Failure detection of the TMA-staged kernel, provoked without faulting anything: with the
     self-test switch every producer warp withholds its first tile and every wait polls only 4096 times,
