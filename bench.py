@@ -344,7 +344,7 @@ def main():
     ap.add_argument("--no-ragged", action="store_true")
     ap.add_argument("--no-shapes", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--only", default=None, choices=["headline", "decode_saturating", "ragged", "backward", "model_prefill"],
+    ap.add_argument("--only", default=None, choices=["headline", "decode_saturating", "ragged", "backward", "model_prefill", "model_decode"],
                     help="run one section and print its figures (for profiling: few launches, small footprint)")
     ap.add_argument("--state-len", type=int, default=3, help="state length of --only decode_saturating")
     ap.add_argument("--circular", action="store_true", help="circular state for --only decode_saturating")
@@ -404,6 +404,9 @@ def main():
         return
     if args.only == "model_prefill":
         emit({"model_prefill_step": bench_model_prefill_step(ctx)})
+        return
+    if args.only == "model_decode":
+        emit({"model_decode_step": bench_model_decode_step(ctx)})
         return
 
     # ---- workload: this rank's 32 sequences ---------------------------------------------------
@@ -843,6 +846,18 @@ def bench_model_decode_step(ctx):
     ms_rank, _ = ctx.time_loop(graph.replay, n, warmup=3)
     ms = ctx.max_over_ranks(ms_rank) / n
     res["graph"] = {"us_per_step": ms * 1e3, "us_per_call": ms * 1e3 / len(calls), "gbs": nbytes / (ms * 1e-3) / 1e9}
+    # The same 72 problems as ONE launch (vc1d_update_multi).  Inside one network they depend on each other and
+    # cannot be batched like this; the figure is what a table of independent steps (several requests, beams or
+    # networks decoded side by side) costs against a launch each.
+    xs, states, ws, outs = ([c[k] for c in calls] for k in (0, 1, 2, 3))
+
+    table = V.UpdateTable(xs, states, ws, None, None, outs=outs)
+    ms_rank, host_s = ctx.time_loop(table.launch, n, warmup=3)
+    ms = ctx.max_over_ranks(ms_rank) / n
+    res["independent_steps_in_one_launch"] = {
+        "us_per_step": ms * 1e3, "us_per_call": ms * 1e3 / len(calls), "gbs": nbytes / (ms * 1e-3) / 1e9,
+        "frac_of_measured_peak": nbytes / (ms * 1e-3) / 1e9 / ctx.peak, "kernel": V.last_kernel(),
+        "host_enqueue_us_per_step": host_s / n * 1e6}
     res["bound"] = "launch"
     return res
 

@@ -283,6 +283,15 @@ typedef struct vc1d_update_args {
 
 VC1D_API int vc1d_update(const vc1d_update_args* args, void* stream);
 
+/* Several independent decode steps in ONE kernel launch (a table of problems instead of a launch each): calls[i]
+ * is a complete vc1d_update_args, with its own batch, dim, state_len, width, activation, strides and buffers; all
+ * of one I/O dtype; at most VC1D_UPDATE_MULTI_MAX of them.  The problems must be independent of each other (none
+ * reads what another writes): the Canon steps of one token of one network are NOT (each feeds the next), the
+ * steps of several requests, networks or beams are.  Results are those of vc1d_update called on each, bit for
+ * bit.  The reference has no counterpart; it launches one kernel per Canon step (model/model.py:305-311). */
+#define VC1D_UPDATE_MULTI_MAX 80
+VC1D_API int vc1d_update_multi(const vc1d_update_args* calls, int32_t n_calls, void* stream);
+
 /*
  * Backward of one decode step (causal_conv1d_update), for the state the step STARTED from:
  *     win = last W entries of [conv_state | x] (or the circular history);  pre = bias + win . weight

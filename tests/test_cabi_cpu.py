@@ -155,3 +155,30 @@ def test_header_is_plain_c(tmp_path):
     assert sizes == [_cabi.lib.vc1d_sizeof_prefill_args(), _cabi.lib.vc1d_sizeof_update_args(),
                      _cabi.lib.vc1d_sizeof_prefill_bwd_args(), _cabi.lib.vc1d_sizeof_update_bwd_args()]
     assert int(out[4]) == 61440
+
+
+def test_update_multi_rejects_bad_tables_without_launching():
+    """vc1d_update_multi validates every problem of its table like vc1d_update, wants one I/O dtype and at
+    most VC1D_UPDATE_MULTI_MAX problems; empty tables and empty problems are a successful no-op."""
+    limit = int(re.search(r"#define VC1D_UPDATE_MULTI_MAX (\d+)", HEADER).group(1))
+    assert limit == _cabi.UPDATE_MULTI_MAX
+    before = _cabi.launch_count()
+    table = (_cabi.UpdateArgs * 3)()
+    for i in range(3):
+        table[i] = _update_args(batch=0)  # nothing to do
+    assert _cabi.lib.vc1d_update_multi(table, 3, None) == _cabi.VC1D_OK
+    assert _cabi.lib.vc1d_update_multi(None, 0, None) == _cabi.VC1D_OK
+    assert _cabi.lib.vc1d_update_multi(None, 2, None) == _cabi.VC1D_E_NULL
+    assert _cabi.lib.vc1d_update_multi(table, limit + 1, None) == _cabi.VC1D_E_SHAPE
+    assert _cabi.lib.vc1d_update_multi(table, -1, None) == _cabi.VC1D_E_SHAPE
+    table[1] = _update_args(width=7)
+    assert _cabi.lib.vc1d_update_multi(table, 3, None) == _cabi.VC1D_E_WIDTH
+    table[1] = _update_args()  # pointers are NULL
+    assert _cabi.lib.vc1d_update_multi(table, 3, None) == _cabi.VC1D_E_NULL
+    # two problems that look valid (the addresses are never dereferenced: the table is refused first)
+    fake = dict(x=1 << 20, y=2 << 20, conv_state=3 << 20, weight=4 << 20, x_stride_b=8, x_stride_d=1, y_stride_b=8,
+                y_stride_d=1, s_stride_b=24, s_stride_d=3, s_stride_l=1, w_stride_d=4, w_stride_w=1)
+    table[0] = _update_args(**fake)
+    table[1] = _update_args(dtype=_cabi.VC1D_F32, wdtype=_cabi.VC1D_F32, **fake)
+    assert _cabi.lib.vc1d_update_multi(table, 2, None) == _cabi.VC1D_E_DTYPE
+    assert _cabi.launch_count() == before

@@ -183,3 +183,108 @@ def test_config3_decode_1024_steps(L):
     full = torch.cat([pre, toks.transpose(0, 1)], dim=1).to(DEV)
     y_full = V.causal_conv1d_fn(full.transpose(1, 2), wd, bd)
     assert torch.equal(y_full[..., cfg.prefill_len:].cpu(), ys.permute(1, 2, 0))
+
+
+def _multi_problems(dtype, seed=7):
+    """Decode steps of different shapes, layouts and options: (batch, dim, state_len, width, bias, layout)."""
+    g = torch.Generator().manual_seed(seed)
+    specs = [(64, 640, 4, 4, False, "dense"), (64, 960, 4, 4, True, "dense"), (64, 3456, 4, 4, True, "dense"),
+             (7, 128, 3, 4, True, "dense"), (5, 72, 3, 4, True, "x3d"), (3, 21, 5, 3, True, "dense"),
+             (4, 64, 8, 4, False, "dense"), (6, 96, 4, 4, True, "strided_state"), (9, 256, 4, 4, True, "circular"),
+             (2, 64, 2, 3, True, "dense"), (1, 8, 4, 4, True, "dense")]
+    problems = []
+    for B, D, L, W, has_bias, layout in specs:
+        x = torch.randn(B, D, generator=g).to(dtype).to(DEV)
+        w = (torch.rand(D, W, generator=g) - 0.5).to(dtype).to(DEV)
+        b = (torch.rand(D, generator=g) - 0.5).to(dtype).to(DEV) if has_bias else None
+        state = torch.randn(B, D, L, generator=g).to(dtype).to(DEV)
+        seqlens = None
+        if layout == "strided_state":
+            state = torch.randn(B, L, D, generator=g).to(dtype).to(DEV).transpose(1, 2)  # [B, D, L] view, channel stride 1
+        if layout == "circular":
+            seqlens = torch.randint(0, 50, (B,), generator=g).to(torch.int32).to(DEV)
+        if layout == "x3d":
+            x = x.unsqueeze(-1)
+        problems.append((x, state, w, b, seqlens))
+    return problems
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("activation", [None, "silu"])
+def test_update_multi_matches_separate_calls(dtype, activation):
+    """Eleven independent decode steps of different shapes in one launch (vc1d_update_multi): outputs and
+    states bit-equal to causal_conv1d_update on each, whichever code a problem takes inside the kernel
+    (vectorised for the most common width and state length, scalar for the rest: other lengths, strided or
+    circular states, odd channel counts)."""
+    problems = _multi_problems(dtype)
+    want_y, want_s = [], []
+    for x, state, w, b, seqlens in problems:
+        s2 = state.clone()
+        want_y.append(V.causal_conv1d_update(x, s2, w, b, activation, seqlens))
+        want_s.append(s2)
+    for step in range(2):  # twice: the states move on
+        if step == 1:
+            for i, (x, state, w, b, seqlens) in enumerate(problems):
+                want_y[i] = V.causal_conv1d_update(x, want_s[i], w, b, activation, seqlens)
+        before = V.launch_count()
+        ys = V.causal_conv1d_update_multi([p[0] for p in problems], [p[1] for p in problems], [p[2] for p in problems],
+                                          [p[3] for p in problems], activation, [p[4] for p in problems])
+        assert V.launch_count() == before + 1 and V.last_kernel() == "update_multi"
+        for i, (x, state, w, b, seqlens) in enumerate(problems):
+            assert ys[i].shape == x.shape, i
+            assert torch.equal(bits(ys[i]), bits(want_y[i])), (step, i)
+            assert torch.equal(bits(state.contiguous()), bits(want_s[i].contiguous())), (step, i)
+
+
+def test_update_table_steps_its_buffers_again():
+    """A table built once and launched for several tokens: new inputs are written into its x buffers, the
+    states move on in place, every step bit-equal to separate calls."""
+    dtype = torch.bfloat16
+    problems = _multi_problems(dtype, seed=9)[:6]
+    table = V.UpdateTable([p[0] for p in problems], [p[1] for p in problems], [p[2] for p in problems],
+                          [p[3] for p in problems], "silu")
+    assert len(table) == 6
+    shadow = [p[1].clone() for p in problems]
+    g = torch.Generator(device=DEV).manual_seed(10)
+    for step in range(4):
+        for x, *_ in problems:
+            x.copy_(torch.randn(x.shape, generator=g, device=DEV).to(dtype))
+        before = V.launch_count()
+        ys = table.launch()
+        assert V.launch_count() == before + 1
+        for i, (x, state, w, b, _) in enumerate(problems):
+            want = V.causal_conv1d_update(x, shadow[i], w, b, "silu")
+            assert torch.equal(bits(ys[i]), bits(want)), (step, i)
+            assert torch.equal(bits(state), bits(shadow[i])), (step, i)
+
+
+def test_update_multi_against_oracle_and_in_chunks():
+    """More problems than one launch holds (80): split over launches; every result against the CPU oracle."""
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(31)
+    n, B, D, L, W = 100, 4, 64, 3, 4
+    xs = [torch.randn(B, D, generator=g).to(dtype) for _ in range(n)]
+    ws = [(torch.rand(D, W, generator=g) - 0.5).to(dtype) for _ in range(n)]
+    bs = [(torch.rand(D, generator=g) - 0.5).to(dtype) for _ in range(n)]
+    states = [torch.randn(B, D, L, generator=g).to(dtype) for _ in range(n)]
+    sd = [s.to(DEV) for s in states]
+    before = V.launch_count()
+    ys = V.causal_conv1d_update_multi([x.to(DEV) for x in xs], sd, [w.to(DEV) for w in ws], [b.to(DEV) for b in bs], "silu")
+    assert V.launch_count() == before + 2
+    for i in range(n):
+        ref = O.causal_conv1d_update_ref(xs[i], states[i], ws[i], bs[i], "silu")  # moves states[i] on
+        assert_close_to_oracle(ys[i], ref, f"problem {i}")
+        assert torch.equal(bits(sd[i].cpu()), bits(states[i])), i
+
+
+def test_update_multi_argument_errors():
+    x = torch.zeros(2, 64, device=DEV)
+    s = torch.zeros(2, 64, 3, device=DEV)
+    w = torch.zeros(64, 4, device=DEV)
+    with pytest.raises(ValueError, match="same length"):
+        V.causal_conv1d_update_multi([x, x], [s], [w, w])
+    with pytest.raises(ValueError, match="one dtype"):
+        V.causal_conv1d_update_multi([x, x.bfloat16()], [s, s.bfloat16()], [w, w.bfloat16()])
+    with pytest.raises(ValueError, match="doesn't match conv_state"):
+        V.causal_conv1d_update_multi([x], [torch.zeros(3, 64, 3, device=DEV)], [w])
+    assert V.causal_conv1d_update_multi([], [], []) == []

@@ -15,8 +15,8 @@ The operators call hand-written CUDA kernels through the C ABI of include/vc1d.h
 that library raises ImportError: there is no CPU or PyTorch fallback.
 """
 from ._cabi import last_kernel, launch_count, library_path, set_pdl, tma_timeouts
-from .ops import (causal_conv1d_bwd, causal_conv1d_fn, causal_conv1d_fn_multi, causal_conv1d_update,
-                  causal_conv1d_update_bwd, reuse_tile_classes, seq_idx_from_lengths)
+from .ops import (UpdateTable, causal_conv1d_bwd, causal_conv1d_fn, causal_conv1d_fn_multi, causal_conv1d_update,
+                  causal_conv1d_update_bwd, causal_conv1d_update_multi, reuse_tile_classes, seq_idx_from_lengths)
 from .short_conv import causal_conv1d_fwd, short_conv_fused, short_conv_update
 from . import compile_ops  # noqa: F401  (registers torch.ops.vc1d.* for torch.compile)
 
@@ -27,6 +27,8 @@ __all__ = [
     "causal_conv1d_fn_multi",
     "seq_idx_from_lengths",
     "causal_conv1d_update_bwd",
+    "causal_conv1d_update_multi",
+    "UpdateTable",
     "causal_conv1d_fwd",
     "short_conv_fused",
     "short_conv_update",

@@ -11,6 +11,7 @@ from pathlib import Path
 
 # ---- constants mirrored from include/vc1d.h -------------------------------------------------
 VC1D_ABI_VERSION = 1
+UPDATE_MULTI_MAX = 80  # VC1D_UPDATE_MULTI_MAX
 
 VC1D_F32, VC1D_BF16, VC1D_F16 = 0, 1, 2
 VC1D_U8, VC1D_I32, VC1D_I64 = 8, 9, 10
@@ -223,6 +224,7 @@ EXPORTS = {
     "vc1d_prefill_bwd": (C.c_int, [C.POINTER(PrefillBwdArgs), C.c_void_p]),
     "vc1d_sizeof_prefill_bwd_args": (C.c_uint32, []),
     "vc1d_update": (C.c_int, [C.POINTER(UpdateArgs), C.c_void_p]),
+    "vc1d_update_multi": (C.c_int, [C.POINTER(UpdateArgs), C.c_int32, C.c_void_p]),
     "vc1d_update_bwd": (C.c_int, [C.POINTER(UpdateBwdArgs), C.c_void_p]),
     "vc1d_sizeof_update_bwd_args": (C.c_uint32, []),
     "vc1d_abi_version": (C.c_int, []),

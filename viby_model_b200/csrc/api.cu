@@ -328,6 +328,28 @@ VC1D_API int vc1d_update(const vc1d_update_args* a, void* stream) {
     return (int)err;
 }
 
+VC1D_API int vc1d_update_multi(const vc1d_update_args* calls, int32_t n_calls, void* stream) {
+    using namespace vc1d;
+    if (n_calls == 0) return VC1D_OK;
+    if (calls == nullptr) return VC1D_E_NULL;
+    if (n_calls < 0 || n_calls > VC1D_UPDATE_MULTI_MAX) return VC1D_E_SHAPE;
+    // problems with nothing to do are left out; the rest must share the I/O dtype (one kernel instantiation)
+    static thread_local vc1d_update_args live[VC1D_UPDATE_MULTI_MAX];
+    unsigned char vec_ok[VC1D_UPDATE_MULTI_MAX];
+    int n = 0;
+    for (int i = 0; i < n_calls; ++i) {
+        const int st = check_update(&calls[i]);
+        if (st != VC1D_OK) return st;
+        if ((long long)calls[i].batch * calls[i].dim == 0) continue;
+        if (n > 0 && calls[i].dtype != live[0].dtype) return VC1D_E_DTYPE;
+        live[n] = calls[i];
+        vec_ok[n] = (calls[i].kernel == VC1D_KERNEL_AUTO && update_vec_ok(&calls[i])) ? 1 : 0;
+        ++n;
+    }
+    if (n == 0) return VC1D_OK;
+    return (int)launch_update_multi(live, n, vec_ok, reinterpret_cast<cudaStream_t>(stream));
+}
+
 VC1D_API int vc1d_update_bwd(const vc1d_update_bwd_args* a, void* stream) {
     using namespace vc1d;
     if (a == nullptr) return VC1D_E_NULL;

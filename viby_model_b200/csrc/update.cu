@@ -33,20 +33,16 @@ struct UParams {
     int residual;
     int nb;      // sequences one thread of the vectorised kernel walks
     int w_fast;  // weights contiguous [D,W] (and bias) in the I/O dtype, 16-byte aligned
+    int vec;     // (several problems in one launch) this problem takes the vectorised code
 };
 
 template <int DT, int W, int L>
-__global__ void __launch_bounds__(256, 2) k_update_vec(const UParams p) {
+__device__ __forceinline__ void update_vec_body(const UParams& p) {
     using E = Elem<DT>;
     using T = typename E::type;
     using PK = Pack<DT>;
     constexpr int VEC = E::kVec;
     constexpr int UB = 2;  // sequences in flight per thread
-    // Launched with programmatic stream serialization: consecutive decode steps depend on each other
-    // through conv_state, so every thread waits for the previous kernel before its first access,
-    // while the launch itself and the scheduling of the CTAs overlap the previous step's tail.
-    griddep_wait();
-    griddep_launch_dependents();
     const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (g >= p.total) return;
     const int lane = (int)(g % p.nvec);
@@ -150,6 +146,16 @@ __global__ void __launch_bounds__(256, 2) k_update_vec(const UParams p) {
             }
         }
     }
+}
+
+template <int DT, int W, int L>
+__global__ void __launch_bounds__(256, 2) k_update_vec(const UParams p) {
+    // Launched with programmatic stream serialization: consecutive decode steps depend on each other
+    // through conv_state, so every thread waits for the previous kernel before its first access,
+    // while the launch itself and the scheduling of the CTAs overlap the previous step's tail.
+    griddep_wait();
+    griddep_launch_dependents();
+    update_vec_body<DT, W, L>(p);
 }
 
 // One channel per lane, for states whose state_len columns of one channel are one or two 128-bit
@@ -297,7 +303,7 @@ __global__ void __launch_bounds__(256) k_update_lane(const UParams p) {
 
 // Scalar kernel: any strides, any state_len >= width-1, shifting or circular state.
 template <int DT>
-__global__ void __launch_bounds__(256) k_update_generic(const UParams p) {
+__device__ __forceinline__ void update_generic_body(const UParams& p) {
     using E = Elem<DT>;
     using T = typename E::type;
     const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -350,6 +356,30 @@ __global__ void __launch_bounds__(256) k_update_generic(const UParams p) {
     y[b * p.syb + (long long)d * p.syd] = E::from_float(acc);
 }
 
+template <int DT>
+__global__ void __launch_bounds__(256) k_update_generic(const UParams p) {
+    update_generic_body<DT>(p);
+}
+
+// Several independent problems in one launch: blockIdx.y names the problem, whose parameters sit in the
+// kernel's parameter space.  A problem that fits the vectorised code for this instantiation's width and
+// state length takes it; every other one takes the scalar code.
+constexpr int kMultiMax = VC1D_UPDATE_MULTI_MAX;
+struct UMulti {
+    UParams calls[kMultiMax];
+};
+template <int DT, int W, int L>
+__global__ void __launch_bounds__(256, 2) k_update_multi(const __grid_constant__ UMulti m) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const UParams& p = m.calls[blockIdx.y];
+    if ((long long)blockIdx.x * blockDim.x >= p.total) return;
+    if (p.vec)
+        update_vec_body<DT, W, L>(p);
+    else
+        update_generic_body<DT>(p);
+}
+
 UParams make_params(const vc1d_update_args& a) {
     UParams p;
     p.x = reinterpret_cast<const char*>(a.x);
@@ -377,6 +407,7 @@ UParams make_params(const vc1d_update_args& a) {
     p.nvec = 0;
     p.total = 0;
     p.nb = 1;
+    p.vec = 0;
     p.w_fast = (a.wdtype == a.dtype && a.w_stride_w == 1 && a.w_stride_d == a.width &&
                 (reinterpret_cast<uintptr_t>(a.weight) & 15u) == 0 &&
                 (a.bias == nullptr || (reinterpret_cast<uintptr_t>(a.bias) & 15u) == 0))
@@ -457,6 +488,79 @@ cudaError_t launch_update_vec(const vc1d_update_args& a, cudaStream_t s) {
         case VC1D_F32: return launch_vec_w<VC1D_F32>(p, grid, block, s);
         case VC1D_BF16: return launch_vec_w<VC1D_BF16>(p, grid, block, s);
         default: return launch_vec_w<VC1D_F16>(p, grid, block, s);
+    }
+}
+
+// n problems (all of one I/O dtype) in one launch.  vec_ok[i]: problem i meets the layout conditions of the
+// vectorised kernel.  The vectorised code is instantiated for the width and state length that most of those
+// problems share; the others run the scalar code.
+namespace {
+template <int DT, int W, int L>
+cudaError_t launch_multi_wl(const UMulti& m, dim3 grid, int block, cudaStream_t s) {
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3((unsigned)block);
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, k_update_multi<DT, W, L>, m);
+}
+template <int DT>
+cudaError_t launch_multi_dt(const UMulti& m, int W, int L, dim3 grid, int block, cudaStream_t s) {
+#define VC1D_MULTI(WW, LL) \
+    if (W == WW && L == LL) return launch_multi_wl<DT, WW, LL>(m, grid, block, s);
+    VC1D_MULTI(2, 1) VC1D_MULTI(2, 2) VC1D_MULTI(2, 3) VC1D_MULTI(2, 4) VC1D_MULTI(2, 8)
+    VC1D_MULTI(3, 2) VC1D_MULTI(3, 3) VC1D_MULTI(3, 4) VC1D_MULTI(3, 8)
+    VC1D_MULTI(4, 3) VC1D_MULTI(4, 4) VC1D_MULTI(4, 8)
+#undef VC1D_MULTI
+    return launch_multi_wl<DT, 4, 3>(m, grid, block, s);  // no problem takes the vectorised code
+}
+}  // namespace
+
+cudaError_t launch_update_multi(const vc1d_update_args* calls, int n, const unsigned char* vec_ok, cudaStream_t s) {
+    if (n < 1 || n > kMultiMax) return cudaErrorInvalidValue;
+    // the (width, state length) pair most vectorisable problems have
+    int best_w = 4, best_l = 3, best_n = 0;
+    for (int i = 0; i < n; ++i) {
+        if (!vec_ok[i]) continue;
+        int cnt = 0;
+        for (int j = 0; j < n; ++j)
+            if (vec_ok[j] && calls[j].width == calls[i].width && calls[j].state_len == calls[i].state_len) ++cnt;
+        if (cnt > best_n) {
+            best_n = cnt;
+            best_w = calls[i].width;
+            best_l = calls[i].state_len;
+        }
+    }
+    static thread_local UMulti m;  // 15 KB: not on the stack
+    const int block = 128;
+    long long max_blocks = 1;
+    for (int i = 0; i < n; ++i) {
+        const vc1d_update_args& a = calls[i];
+        UParams p = make_params(a);
+        p.vec = (best_n > 0 && vec_ok[i] && a.width == best_w && a.state_len == best_l) ? 1 : 0;
+        if (p.vec) {
+            const int vec = 16 / elem_bytes(a.dtype);
+            p.nvec = a.dim / vec;
+            p.nb = 1;  // decode batches that share a launch are small: one sequence per thread
+            p.total = (long long)a.batch * p.nvec;
+        } else {
+            p.total = (long long)a.batch * a.dim;
+        }
+        const long long blocks = (p.total + block - 1) / block;
+        if (blocks > max_blocks) max_blocks = blocks;
+        m.calls[i] = p;
+    }
+    if (max_blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    note_launch("update_multi");
+    const dim3 grid((unsigned)max_blocks, (unsigned)n);
+    switch (calls[0].dtype) {
+        case VC1D_F32: return launch_multi_dt<VC1D_F32>(m, best_w, best_l, grid, block, s);
+        case VC1D_BF16: return launch_multi_dt<VC1D_BF16>(m, best_w, best_l, grid, block, s);
+        default: return launch_multi_dt<VC1D_F16>(m, best_w, best_l, grid, block, s);
     }
 }
 

@@ -58,6 +58,8 @@ bool update_lane_supports(int dtype, int state_len, int width);
 
 // Any strides, shifting or circular state.
 cudaError_t launch_update_generic(const vc1d_update_args& a, cudaStream_t s);
+// n independent problems of one I/O dtype in one launch; vec_ok[i] = problem i fits the vectorised code
+cudaError_t launch_update_multi(const vc1d_update_args* calls, int n, const unsigned char* vec_ok, cudaStream_t s);
 
 // Backward of one decode step: any strides, shifting or circular state.
 cudaError_t launch_update_bwd(const vc1d_update_bwd_args& a, cudaStream_t s);

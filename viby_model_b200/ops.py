@@ -783,6 +783,85 @@ def causal_conv1d_update(
     return _CausalConv1dUpdateFunction.apply(x, conv_state, weight, bias, activation, cache_seqlens, residual)[0]
 
 
+class UpdateTable:
+    """A table of independent decode steps that one kernel launch runs (vc1d_update_multi): step i is
+    ``causal_conv1d_update(xs[i], conv_states[i], weights[i], biases[i], activation)``, each with its own batch,
+    channel count and state length, all of one dtype and on one device.  The table is validated and built
+    once; ``launch()`` then costs one library call per 80 steps.  The buffers are the ones given here: write
+    the next inputs into ``xs[i]`` (or pass tensors that something else fills), read ``outs[i]``; the states
+    are updated in place.
+
+    The steps must not depend on each other.  The Canon steps of one token of one network do (Canon A feeds
+    attention, whose output feeds Canon C, ...; model/model.py:1021-1055): a table is for the steps of
+    several requests, beams or networks that are decoded side by side.  No gradient."""
+
+    def __init__(self, xs, conv_states, weights, biases=None, activation=None, cache_seqlens=None, *,
+                 residual: bool = False, outs=None):
+        n = len(xs)
+        if not (len(conv_states) == n and len(weights) == n):
+            raise ValueError("xs, conv_states and weights must have the same length")
+        biases = [None] * n if biases is None else biases
+        cache_seqlens = [None] * n if cache_seqlens is None else cache_seqlens
+        outs = [None] * n if outs is None else outs
+        if not (len(biases) == n and len(cache_seqlens) == n and len(outs) == n):
+            raise ValueError("biases, cache_seqlens and outs must have one entry per step")
+        self.device = xs[0].device if n else None
+        self.outs = []
+        self._keep = []  # every tensor whose memory the table names
+        self._table = (_cabi.UpdateArgs * max(n, 1))()
+        self._n = n
+        for i in range(n):
+            x = xs[i]
+            squeeze = x.dim() == 3 and x.shape[-1] == 1
+            if squeeze:
+                x = x.squeeze(-1)
+            if x.device != self.device:
+                raise ValueError("all steps of one launch must live on one device")
+            if x.dtype != xs[0].dtype:
+                raise ValueError("all steps of one launch must have one dtype")
+            a, out, w, b, cs = _build_update_args(x, conv_states[i], weights[i], biases[i], activation,
+                                                  cache_seqlens[i], residual, outs[i], None, 0)
+            self._table[i] = a
+            self._keep.append((x, conv_states[i], w, b, cs, out))
+            self.outs.append(out.unsqueeze(-1) if squeeze else out)
+
+    def __len__(self):
+        return self._n
+
+    def launch(self):
+        """Enqueues the steps on the device's current stream; returns ``outs``."""
+        if self._n == 0:
+            return self.outs
+        stream = _stream_handle(self.device)
+        limit = _cabi.UPDATE_MULTI_MAX
+        size = C.sizeof(_cabi.UpdateArgs)
+        base = C.addressof(self._table)
+        other = self.device.index != torch.cuda.current_device()
+        if other:
+            prev = torch.cuda.current_device()
+            torch.cuda.set_device(self.device)
+        try:
+            for first in range(0, self._n, limit):
+                st = _cabi.lib.vc1d_update_multi(C.cast(base + first * size, C.POINTER(_cabi.UpdateArgs)),
+                                                 min(limit, self._n - first), stream)
+                if st != 0:
+                    _cabi.check(st, "causal_conv1d_update_multi")
+        finally:
+            if other:
+                torch.cuda.set_device(prev)
+        return self.outs
+
+
+def causal_conv1d_update_multi(xs, conv_states, weights, biases=None, activation=None, cache_seqlens=None, *,
+                               residual: bool = False, outs=None):
+    """Several independent decode steps in one kernel launch: ``causal_conv1d_update(xs[i], conv_states[i],
+    weights[i], biases[i], activation)`` for every i (see UpdateTable, which this builds and launches once;
+    keep the table when the same buffers are stepped again).  The states are updated in place; returns the
+    list of outputs, bit-equal to the separate calls."""
+    return UpdateTable(xs, conv_states, weights, biases, activation, cache_seqlens, residual=residual,
+                       outs=outs).launch()
+
+
 def causal_conv1d_update_bwd(
     x: torch.Tensor,
     conv_state: torch.Tensor,
@@ -924,42 +1003,10 @@ def _update_fast(x, conv_state, weight, bias, activation, cache_seqlens, residua
     return out, key
 
 
-def _update_forward(
-    x: torch.Tensor,
-    conv_state: torch.Tensor,
-    weight: torch.Tensor,
-    bias: Optional[torch.Tensor] = None,
-    activation: Optional[str] = None,
-    cache_seqlens: Optional[torch.Tensor] = None,
-    *,
-    residual: bool = False,
-    out: Optional[torch.Tensor] = None,
-    kernel: Optional[str] = None,
-    block_threads: int = 0,
-) -> torch.Tensor:
-    """Single-token causal conv step against a rolling ``conv_state`` (decode).
-
-    ``cat = [conv_state | x]``; ``y = act(bias + cat[..., -W:] . weight)``;
-    ``conv_state <- cat[..., -state_len:]`` **in place**; returns ``y`` shaped like ``x``.
-    Matches the reference call at model/model.py:305-311 and the PyTorch step at
-    model/model.py:372-398 for any ``state_len >= width-1`` (the reference's CUDA branch uses
-    ``state_len == width``, its fallback 8).
-
-    x ``[batch, dim]`` (or ``[batch, dim, 1]``), conv_state ``[batch, dim, state_len]``.
-    ``cache_seqlens[batch]`` (int32) switches to the circular-buffer state of
-    causal-conv1d-mps (causal_conv1d.metal:586-664): write position ``cache_seqlens[b] % state_len``.
-    ``residual=True`` adds ``x`` to the result (causal_conv1d.metal:655-658).
-    """
-    squeeze = False
-    if x.dim() == 3 and x.shape[-1] == 1:
-        x = x.squeeze(-1)
-        squeeze = True
-    fast_key = None
-    if cache_seqlens is None and x.is_cuda and conv_state.is_cuda and weight.is_cuda and (bias is None or bias.is_cuda):
-        y, fast_key = _update_fast(x, conv_state, weight, bias, activation, cache_seqlens, residual, out, kernel,
-                                   block_threads)
-        if y is not None:
-            return y.unsqueeze(-1) if squeeze else y
+def _build_update_args(x, conv_state, weight, bias, activation, cache_seqlens, residual, out, kernel, block_threads):
+    """Validates one decode step and fills its argument struct.  Returns (struct, out, weight, bias,
+    cache_seqlens): the last three are the tensors whose memory the struct names (possibly converted copies,
+    which the caller has to keep alive until the launch is enqueued)."""
     if x.dim() != 2:
         raise ValueError(f"Expected 2D input tensor (batch, dim), got {x.dim()}D")
     if conv_state.dim() != 3:
@@ -978,7 +1025,6 @@ def _update_forward(
     act = _activation_code(activation)
     _require_cuda(x, "Input")
     _require_cuda(conv_state, "Convolution state")
-    weight_given, bias_given = weight, bias
     weight, bias = _align_weights(x, weight, bias)
 
     if out is None:
@@ -1016,6 +1062,48 @@ def _update_forward(
     a.kernel = _cabi.KERNEL_GENERIC if kernel == "generic" else _cabi.KERNEL_AUTO
     a.block_threads = int(block_threads)
 
+    return a, out, weight, bias, cache_seqlens
+
+
+def _update_forward(
+    x: torch.Tensor,
+    conv_state: torch.Tensor,
+    weight: torch.Tensor,
+    bias: Optional[torch.Tensor] = None,
+    activation: Optional[str] = None,
+    cache_seqlens: Optional[torch.Tensor] = None,
+    *,
+    residual: bool = False,
+    out: Optional[torch.Tensor] = None,
+    kernel: Optional[str] = None,
+    block_threads: int = 0,
+) -> torch.Tensor:
+    """Single-token causal conv step against a rolling ``conv_state`` (decode).
+
+    ``cat = [conv_state | x]``; ``y = act(bias + cat[..., -W:] . weight)``;
+    ``conv_state <- cat[..., -state_len:]`` **in place**; returns ``y`` shaped like ``x``.
+    Matches the reference call at model/model.py:305-311 and the PyTorch step at
+    model/model.py:372-398 for any ``state_len >= width-1`` (the reference's CUDA branch uses
+    ``state_len == width``, its fallback 8).
+
+    x ``[batch, dim]`` (or ``[batch, dim, 1]``), conv_state ``[batch, dim, state_len]``.
+    ``cache_seqlens[batch]`` (int32) switches to the circular-buffer state of
+    causal-conv1d-mps (causal_conv1d.metal:586-664): write position ``cache_seqlens[b] % state_len``.
+    ``residual=True`` adds ``x`` to the result (causal_conv1d.metal:655-658).
+    """
+    squeeze = False
+    if x.dim() == 3 and x.shape[-1] == 1:
+        x = x.squeeze(-1)
+        squeeze = True
+    fast_key = None
+    if cache_seqlens is None and x.is_cuda and conv_state.is_cuda and weight.is_cuda and (bias is None or bias.is_cuda):
+        y, fast_key = _update_fast(x, conv_state, weight, bias, activation, cache_seqlens, residual, out, kernel,
+                                   block_threads)
+        if y is not None:
+            return y.unsqueeze(-1) if squeeze else y
+    weight_given, bias_given = weight, bias
+    a, out, weight, bias, cache_seqlens = _build_update_args(x, conv_state, weight, bias, activation, cache_seqlens,
+                                                             residual, out, kernel, block_threads)
     if x.device.index != torch.cuda.current_device():
         with torch.cuda.device(x.device):
             st = _cabi.lib.vc1d_update(C.byref(a), _stream_handle(x.device))
