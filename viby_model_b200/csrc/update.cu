@@ -37,13 +37,13 @@ struct UParams {
 };
 
 template <int DT, int W, int L>
-__device__ __forceinline__ void update_vec_body(const UParams& p) {
+__device__ __forceinline__ void update_vec_body(const UParams& p, unsigned block) {
     using E = Elem<DT>;
     using T = typename E::type;
     using PK = Pack<DT>;
     constexpr int VEC = E::kVec;
     constexpr int UB = 2;  // sequences in flight per thread
-    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long g = (long long)block * blockDim.x + threadIdx.x;
     if (g >= p.total) return;
     const int lane = (int)(g % p.nvec);
     const long long grp = g / p.nvec;
@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(256, 2) k_update_vec(const UParams p) {
     // while the launch itself and the scheduling of the CTAs overlap the previous step's tail.
     griddep_wait();
     griddep_launch_dependents();
-    update_vec_body<DT, W, L>(p);
+    update_vec_body<DT, W, L>(p, blockIdx.x);
 }
 
 // One channel per lane, for states whose state_len columns of one channel are one or two 128-bit
@@ -303,10 +303,10 @@ __global__ void __launch_bounds__(256) k_update_lane(const UParams p) {
 
 // Scalar kernel: any strides, any state_len >= width-1, shifting or circular state.
 template <int DT>
-__device__ __forceinline__ void update_generic_body(const UParams& p) {
+__device__ __forceinline__ void update_generic_body(const UParams& p, unsigned block) {
     using E = Elem<DT>;
     using T = typename E::type;
-    const long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long g = (long long)block * blockDim.x + threadIdx.x;
     if (g >= p.total) return;
     const int d = (int)(g % p.D);
     const long long b = g / p.D;
@@ -358,26 +358,38 @@ __device__ __forceinline__ void update_generic_body(const UParams& p) {
 
 template <int DT>
 __global__ void __launch_bounds__(256) k_update_generic(const UParams p) {
-    update_generic_body<DT>(p);
+    update_generic_body<DT>(p, blockIdx.x);
 }
 
-// Several independent problems in one launch: blockIdx.y names the problem, whose parameters sit in the
-// kernel's parameter space.  A problem that fits the vectorised code for this instantiation's width and
-// state length takes it; every other one takes the scalar code.
+// Several independent problems in one launch.  Their parameters sit in the kernel's parameter space; the
+// blocks of all problems are numbered through (first_block[i] = blocks of the problems before i), so a
+// block finds its problem by bisection and no block is launched for nothing.  A problem that fits the
+// vectorised code for this instantiation's width and state length takes it; every other one takes the
+// scalar code.
 constexpr int kMultiMax = VC1D_UPDATE_MULTI_MAX;
 struct UMulti {
     UParams calls[kMultiMax];
+    unsigned first_block[kMultiMax + 1];
+    int n;
 };
 template <int DT, int W, int L>
 __global__ void __launch_bounds__(256, 2) k_update_multi(const __grid_constant__ UMulti m) {
     griddep_wait();
     griddep_launch_dependents();
-    const UParams& p = m.calls[blockIdx.y];
-    if ((long long)blockIdx.x * blockDim.x >= p.total) return;
+    int lo = 0, hi = m.n;  // the problem i with first_block[i] <= blockIdx.x < first_block[i + 1]
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (m.first_block[mid] <= blockIdx.x)
+            lo = mid;
+        else
+            hi = mid;
+    }
+    const UParams& p = m.calls[lo];
+    const unsigned block = blockIdx.x - m.first_block[lo];
     if (p.vec)
-        update_vec_body<DT, W, L>(p);
+        update_vec_body<DT, W, L>(p, block);
     else
-        update_generic_body<DT>(p);
+        update_generic_body<DT>(p, block);
 }
 
 UParams make_params(const vc1d_update_args& a) {
@@ -537,7 +549,8 @@ cudaError_t launch_update_multi(const vc1d_update_args* calls, int n, const unsi
     }
     static thread_local UMulti m;  // 15 KB: not on the stack
     const int block = 128;
-    long long max_blocks = 1;
+    long long n_blocks = 0;
+    m.n = n;
     for (int i = 0; i < n; ++i) {
         const vc1d_update_args& a = calls[i];
         UParams p = make_params(a);
@@ -550,13 +563,14 @@ cudaError_t launch_update_multi(const vc1d_update_args* calls, int n, const unsi
         } else {
             p.total = (long long)a.batch * a.dim;
         }
-        const long long blocks = (p.total + block - 1) / block;
-        if (blocks > max_blocks) max_blocks = blocks;
+        m.first_block[i] = (unsigned)n_blocks;
+        n_blocks += (p.total + block - 1) / block;
+        if (n_blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
         m.calls[i] = p;
     }
-    if (max_blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
+    m.first_block[n] = (unsigned)n_blocks;
     note_launch("update_multi");
-    const dim3 grid((unsigned)max_blocks, (unsigned)n);
+    const dim3 grid((unsigned)n_blocks);
     switch (calls[0].dtype) {
         case VC1D_F32: return launch_multi_dt<VC1D_F32>(m, best_w, best_l, grid, block, s);
         case VC1D_BF16: return launch_multi_dt<VC1D_BF16>(m, best_w, best_l, grid, block, s);
