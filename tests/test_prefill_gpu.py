@@ -588,10 +588,12 @@ def test_tma_scheduling_variants_agree(mask_dtype, D, mask_kind, tma):
     assert V.tma_timeouts() == 0
 
 
-def test_tma_class_table_of_a_very_long_batch():
-    """More tiles than the byte-per-tile class table a CTA keeps in shared memory (16384): the table
-    is kept at two bits per tile.  19200 tiles here; against the register-window kernel."""
-    B, T, D = 300, 4096, 256
+@pytest.mark.parametrize("B", [64, 65, 300])
+def test_tma_class_table_of_a_very_long_batch(B):
+    """The three forms in which a CTA holds the pre-pass's result: the ordered tile list (up to 4096 tiles:
+    batch 64 here is exactly that many), a class byte per tile (4160 tiles), and, beyond the 16384 bytes a
+    CTA spends on that, two bits per tile (19200 tiles).  Against the register-window kernel."""
+    T, D = 4096, 256
     g = torch.Generator(device=DEV).manual_seed(3)
     x = torch.randn(B, T, D, generator=g, device=DEV).bfloat16()
     w = dev(O.seeded((D, 4), 5, "uniform", torch.bfloat16))
