@@ -694,6 +694,29 @@ def test_tile_classes_are_kept_while_the_mask_is_unchanged():
     assert V.tma_timeouts() == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("mask_dtype", [torch.bool, torch.int64, torch.float32])
+def test_ordered_tile_list_in_the_other_dtypes(dtype, mask_dtype):
+    """The ordered tile list and its reuse for fp32 and fp16 tensors (other channel counts per slab) and for
+    masks of other types: pre-pass on the first launch only, results bit-equal to the register-window kernel."""
+    B, T, D, W = 48, 1000, 520, 4
+    g = torch.Generator(device=DEV).manual_seed(17)
+    x = torch.randn(B, T, D, generator=g, device=DEV).to(dtype)
+    w = dev(O.seeded((D, W), 18, "uniform", dtype))
+    b = dev(O.seeded((D,), 19, "uniform", dtype))
+    m = dev(_mask_of_kind("right", B, T, 20).to(mask_dtype))
+    ref = V.causal_conv1d_fn(x.transpose(1, 2), w, b, activation="silu", attention_mask=m, kernel="channel_last")
+    counts = []
+    for _ in range(3):
+        before = V.launch_count()
+        y = V.causal_conv1d_fn(x.transpose(1, 2), w, b, activation="silu", attention_mask=m, kernel="tma")
+        counts.append(V.launch_count() - before)
+        assert V.last_kernel() == "tma" and torch.equal(y, ref)
+    assert counts == [2, 1, 1]
+    torch.cuda.synchronize()
+    assert V.tma_timeouts() == 0
+
+
 def test_kept_tile_classes_and_cuda_graphs():
     """A captured launch never relies on classes from outside its graph: replays stay correct after eager
     launches with other masks have used the stream's scratch memory."""
