@@ -344,7 +344,7 @@ def main():
     ap.add_argument("--no-ragged", action="store_true")
     ap.add_argument("--no-shapes", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--only", default=None, choices=["headline", "decode_saturating", "ragged", "backward", "model_prefill", "model_decode"],
+    ap.add_argument("--only", default=None, choices=["headline", "decode_saturating", "ragged", "backward", "model_prefill", "model_decode", "shapes"],
                     help="run one section and print its figures (for profiling: few launches, small footprint)")
     ap.add_argument("--state-len", type=int, default=3, help="state length of --only decode_saturating")
     ap.add_argument("--circular", action="store_true", help="circular state for --only decode_saturating")
@@ -404,6 +404,9 @@ def main():
         return
     if args.only == "model_prefill":
         emit({"model_prefill_step": bench_model_prefill_step(ctx)})
+        return
+    if args.only == "shapes":
+        emit({"shapes": bench_shapes(ctx)})
         return
     if args.only == "model_decode":
         emit({"model_decode_step": bench_model_decode_step(ctx)})
