@@ -18,6 +18,7 @@ from ._cabi import last_kernel, launch_count, library_path, set_pdl, tma_timeout
 from .ops import (UpdateTable, causal_conv1d_bwd, causal_conv1d_fn, causal_conv1d_fn_multi, causal_conv1d_update,
                   causal_conv1d_update_bwd, causal_conv1d_update_multi, reuse_tile_classes, seq_idx_from_lengths)
 from .short_conv import causal_conv1d_fwd, short_conv_fused, short_conv_update
+from . import canon_cache  # noqa: F401  (Canon states on a generation cache: accessors, beam reorder, device transfer)
 from . import compile_ops  # noqa: F401  (registers torch.ops.vc1d.* for torch.compile)
 
 __all__ = [
