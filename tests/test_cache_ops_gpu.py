@@ -84,3 +84,64 @@ def test_reordered_circular_state_keeps_its_positions():
         assert_close_to_oracle(y, ref, f"step {step}")
         assert torch.equal(bits(st.cpu()), bits(state))
         sl, seqlens = sl + 1, seqlens + 1
+
+
+def test_requests_decoded_side_by_side_from_their_caches():
+    """Two independent requests, each with its own cache of Canon states (viby_model_b200.canon_cache): one
+    table launch per token steps every state of both (UpdateTable), a beam reorder of one request in between;
+    bit-equal to a causal_conv1d_update call per state, with the oracle as the arbiter of the first step."""
+    import types
+
+    from viby_model_b200 import canon_cache as CC
+
+    dtype, W, L, layers = torch.bfloat16, 4, 4, 3
+    dims = {"a": 640, "b": 960, "c": 640, "d": 3456}
+    g = torch.Generator().manual_seed(77)
+    weights = {(pos, l): (torch.rand(D, W, generator=g) - 0.5).to(dtype) for pos, D in dims.items() for l in range(layers)}
+    requests = []
+    for batch in (5, 2):
+        cache, shadow = types.SimpleNamespace(_max_layers=layers), types.SimpleNamespace(_max_layers=layers)
+        for pos, D in dims.items():
+            for l in range(layers):
+                s = torch.randn(batch, D, L, generator=g).to(dtype)
+                CC.set_state(cache, pos, l, s.to(DEV))
+                CC.set_state(shadow, pos, l, s.clone().to(DEV))
+        requests.append((batch, cache, shadow))
+
+    def build_table():
+        xs, states, ws = [], [], []
+        for batch, cache, _ in requests:
+            for name, layer, state in CC.states(cache):
+                xs.append(torch.zeros(batch, state.shape[1], dtype=dtype, device=DEV))
+                states.append(state)
+                ws.append(weights[(name[-1], layer)].to(DEV))
+        return xs, V.UpdateTable(xs, states, ws, None, "silu")
+
+    xs, table = build_table()
+    assert len(table) == 2 * 4 * layers
+    gen = torch.Generator(device=DEV).manual_seed(78)
+    for step in range(4):
+        if step == 2:
+            # beam search picks other rows of the first request: the states are new tensors, so is the table
+            beam = torch.tensor([4, 4, 0, 1, 2], device=DEV)
+            CC.reorder(requests[0][1], beam)
+            CC.reorder(requests[0][2], beam)
+            xs, table = build_table()
+        for x in xs:
+            x.copy_(torch.randn(x.shape, generator=gen, device=DEV).to(dtype))
+        before = V.launch_count()
+        ys = table.launch()
+        assert V.launch_count() == before + 1
+        i = 0
+        for batch, cache, shadow in requests:
+            for name, layer, state in CC.states(cache):
+                w = weights[(name[-1], layer)]
+                twin = CC.get_state(shadow, name, layer)
+                if step == 0:
+                    cpu_state = twin.cpu().clone()
+                    ref = O.causal_conv1d_update_ref(xs[i].cpu(), cpu_state, w, None, "silu")
+                    assert_close_to_oracle(ys[i], ref, f"{name}[{layer}]")
+                want = V.causal_conv1d_update(xs[i], twin, w.to(DEV), None, "silu")
+                assert torch.equal(bits(ys[i]), bits(want)), (step, name, layer)
+                assert torch.equal(bits(state), bits(twin)), (step, name, layer)
+                i += 1
